@@ -1,0 +1,176 @@
+/*
+ * qmoe_sub1.h -- C ABI of the B200 (sm_100a) implementation of QMoE's compressed-expert
+ * inference path: fused dictionary decode + matvec / small-batch matmul, the encoder, and the
+ * grouped expert FFN of a top-1 MoE layer.
+ *
+ * Every entry point takes plain pointers and sizes.  Pointers named *_dev are device pointers on
+ * `device`; all work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream, which is what the reference launches on, sub1_cuda_kernel.cu:29).  Functions
+ * return QMOE_OK (0) or a negative status; qmoe_last_error() gives a message for the calling
+ * thread.  There is no CPU fallback: without a usable CUDA device the compute entry points fail.
+ *
+ * Reference citations are into IST-DASLab/qmoe.
+ */
+#ifndef QMOE_SUB1_H_
+#define QMOE_SUB1_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMOE_OK 0
+#define QMOE_ERR_INVALID_ARG (-1)   /* null pointer, negative size, odd width, ... */
+#define QMOE_ERR_CUDA (-2)          /* a CUDA runtime call or a launch failed */
+#define QMOE_ERR_UNSUPPORTED (-3)   /* shape or table outside what the kernels handle */
+#define QMOE_ERR_STREAM (-4)        /* a code stream failed validation (rows not tiled exactly) */
+#define QMOE_ERR_TIMEOUT (-5)       /* a bounded device-side wait gave up */
+
+#define QMOE_DICT_COUNT 65536       /* sub1.py:30 */
+#define QMOE_TRIE_ROOT 65536        /* sub1_cuda_kernel.cu:209 */
+
+/* Flags of qmoe_sub1_matmul / grouped calls. */
+#define QMOE_FLAG_ACCUMULATE 1      /* y += bf16(Wx) (sub1_cuda_kernel.cu:199-200); else y = bf16(Wx) */
+#define QMOE_FLAG_RELU 2            /* y = max(bf16(Wx), 0); the ReLU between wi and wo (sub1.py:317) */
+
+const char *qmoe_last_error(void);
+int qmoe_version(void);
+
+/* Host-side construction of the fixed dictionary: dec int32[2*65536] and trie int32[65537*9],
+ * bit-identical to setup() in sub1.py:29-102.  Both are host pointers. */
+int qmoe_sub1_build_dictionary(int32_t *dec_host, int32_t *trie_host);
+
+/* Replaces sub1matvec (sub1_cuda.cpp:35-45 -> sub1matvec_cuda, sub1_cuda_kernel.cu:70-88 ->
+ * Sub1MatVec, :129-202): y[r] += bf16(sum_c W[r,c] x[c]) for one compressed matrix and one bf16
+ * vector.  Any height >= 1 and even width >= 2 (width <= QMOE_MAX_WIDTH) is accepted, not only
+ * the reference's six hard-coded shapes.
+ *   dec_dev        int32[131072]   decoder table (sub1.py:60-72)
+ *   w_comp_dev     uint16[n_codes] code stream, rows concatenated
+ *   row_off_dev    int32[height+1] exclusive prefix sums of codes per row
+ *   ter_minmax_dev bf16[2*height]  interleaved (min_r, max_r)
+ *   x_dev          bf16[width], y_dev bf16[height] (read-modify-write) */
+int qmoe_sub1_matvec(const int32_t *dec_dev, const uint16_t *w_comp_dev, const int32_t *row_off_dev,
+                     const void *ter_minmax_dev, const void *x_dev, void *y_dev, int height,
+                     int width, int64_t n_codes, int device, void *stream);
+
+/* Replaces the per-token loop of Sub1Linear.forward (sub1.py:132-143): x[tokens, width] ->
+ * y[tokens, height] with the codes decoded once per group of tokens.  x rows are `x_stride`
+ * elements apart, y rows `y_stride`.  flags: QMOE_FLAG_*. */
+int qmoe_sub1_matmul(const int32_t *dec_dev, const uint16_t *w_comp_dev, const int32_t *row_off_dev,
+                     const void *ter_minmax_dev, const void *x_dev, void *y_dev, int height,
+                     int width, int64_t n_codes, int tokens, int64_t x_stride, int64_t y_stride,
+                     int flags, int device, void *stream);
+
+/* Decodes a compressed matrix to ternary symbols uint8[height, width] (0, 1 = row min, 2 = row
+ * max) with the same table walk the matvec kernels use; the GPU twin of decompress()
+ * (test.py:103-115).  status_dev (int32[1], may be NULL) receives the number of rows whose codes
+ * do not cover exactly `width` weights. */
+int qmoe_sub1_decode(const int32_t *dec_dev, const uint16_t *w_comp_dev, const int32_t *row_off_dev,
+                     uint8_t *sym_dev, int32_t *status_dev, int height, int width, int64_t n_codes,
+                     int device, void *stream);
+
+/* Replaces sub1pack (sub1_cuda.cpp:47-54 -> sub1pack_cuda, sub1_cuda_kernel.cu:92-126), split in
+ * two so that the caller owns the allocation of the output between the phases.
+ * prepare = row_off.zero_() + Sub1PreparePack (:211-239) + cumsum: greedy longest-match walk of
+ * every row; the row's codes overwrite the head of the row in w_tern (int32[height, width], values
+ * 0/1/2, clobbered exactly like the reference) and row_off (int32[height+1]) ends as exclusive
+ * prefix sums.  Any height >= 1 (the reference needs height % 32 == 0).
+ * emit = Sub1Pack (:241-250): compaction into w_comp_dev uint16[row_off[height]]. */
+int qmoe_sub1_pack_prepare(const int32_t *trie_dev, int32_t *w_tern_dev, int32_t *row_off_dev,
+                           int height, int width, int device, void *stream);
+int qmoe_sub1_pack_emit(const int32_t *w_tern_dev, const int32_t *row_off_dev, uint16_t *w_comp_dev,
+                        int height, int width, int device, void *stream);
+
+/* Batched encoder on uint8 symbols for `n_mat` matrices of one shape (sym_dev uint8[n_mat,
+ * height, width]); no host synchronisation.  count: codes_tmp_dev uint16[n_mat, height, width/2]
+ * receives each row's codes, row_len_dev int32[n_mat*height] the per-row counts.  The caller then
+ * prefix-sums row_len into per-matrix row_off and a per-matrix base (in codes), and calls gather:
+ * out_dev[mat_base[m] + row_off[m][r] + i] = codes of row r.  Same greedy rule as
+ * sub1_cuda_kernel.cu:211-239. */
+int qmoe_sub1_pack_u8_count(const int32_t *trie_dev, const uint8_t *sym_dev, uint16_t *codes_tmp_dev,
+                            int32_t *row_len_dev, int n_mat, int height, int width, int device,
+                            void *stream);
+int qmoe_sub1_pack_u8_gather(const uint16_t *codes_tmp_dev, const int32_t *row_off_dev,
+                             const int64_t *mat_base_dev, uint16_t *out_dev, int n_mat, int height,
+                             int width, int device, void *stream);
+
+/* Seeded synthetic ternary symbols for benchmarks: sym[i] = 0 with probability p_zero, else 1 or 2
+ * with equal probability, from a counter-based hash of (seed, first_index + i). */
+int qmoe_synth_ternary(uint8_t *sym_dev, int64_t count, uint64_t seed, uint64_t first_index,
+                       float p_zero, int device, void *stream);
+
+/* ---- Grouped expert FFN of one top-1 MoE layer (FasterMLP.forward, sub1.py:306-321) --------- */
+
+/* One compressed matrix inside an expert store.  All offsets are in elements of the store's
+ * arrays; code_base must be a multiple of 8 (16-byte aligned streams). */
+typedef struct {
+  int64_t code_base;    /* first code of the matrix in the store's uint16 code array */
+  int64_t n_codes;
+  int64_t rowoff_base;  /* first of the matrix's height+1 row offsets (relative to code_base) */
+  int64_t minmax_base;  /* first (min,max) pair of the matrix, in bf16x2 units */
+  int32_t height;
+  int32_t width;
+} qmoe_matrix_desc;
+
+/* Top-1 choice of the Switch router the reference calls at sub1.py:310 (transformers 4.28
+ * SwitchTransformersTop1Router): probabilities = softmax(logits) in fp32 rounded to bf16,
+ * choice = first index holding the largest bf16 probability, prob = that probability.
+ *   logits_dev float[n_tokens, n_experts]; choice_dev int32[n_tokens]; prob_dev bf16[n_tokens] */
+int qmoe_moe_route(const float *logits_dev, int32_t *choice_dev, void *prob_dev, int n_tokens,
+                   int n_experts, int device, void *stream);
+
+/* Capacity rule + stable ranking.  A token is kept when fewer than `capacity` earlier tokens of
+ * its own sequence (seq_len consecutive tokens; n_tokens % seq_len == 0) made the same choice --
+ * the router's cumsum(one_hot) <= expert_capacity mask.  Tokens whose choice is negative count as
+ * dropped already.
+ *   bucket_dev int32[n_tokens]  choice if kept, else -1 (must not alias choice_dev)
+ *   rank_dev   int32[n_tokens]  number of earlier kept tokens (whole batch) in the same bucket
+ *   counts_dev int32[n_buckets] kept tokens per bucket (overwritten)
+ * Deterministic: ranks follow token order. */
+int qmoe_moe_rank(const int32_t *choice_dev, int32_t *bucket_dev, int32_t *rank_dev, int32_t *counts_dev,
+                  int n_tokens, int n_buckets, int seq_len, int capacity, int device, void *stream);
+
+/* offsets[0..n] = exclusive prefix sums of counts[0..n) (offsets has n+1 entries). */
+int qmoe_moe_scan(const int32_t *counts_dev, int32_t *offsets_dev, int n, int device, void *stream);
+
+/* slot[token] = offsets[bucket] + rank (or -1 when bucket < 0) and xs[slot] = hidden[token]: the
+ * gather of kept tokens into bucket order.  hidden/xs are bf16 rows of d_model elements; hidden
+ * rows are hidden_stride elements apart, xs rows xs_stride. */
+int qmoe_moe_permute(const int32_t *bucket_dev, const int32_t *rank_dev, const int32_t *offsets_dev,
+                     int32_t *slot_dev, const void *hidden_dev, void *xs_dev, int n_tokens, int d_model,
+                     int64_t hidden_stride, int64_t xs_stride, int device, void *stream);
+
+/* out[i] = ys[slot[i]] for slot[i] >= 0; rows with slot < 0 are zero-filled. */
+int qmoe_moe_unpermute(const void *ys_dev, const int32_t *slot_dev, void *out_dev, int n_tokens, int d_model,
+                       int64_t ys_stride, int64_t out_stride, int device, void *stream);
+
+/* Grouped wo(ReLU(wi(x))) over every expert that received tokens: tokens are sorted by expert,
+ * expert e owns rows offsets[e]..offsets[e+1] of xs / hs / ys.  descs_dev[2e] is wi (height d_ff,
+ * width d_model), descs_dev[2e+1] is wo.  Everything is decided on the device from offsets_dev;
+ * no host synchronisation.  work_dev is caller-provided scratch of qmoe_moe_work_bytes() bytes.
+ *   xs_dev bf16[n_slots, d_model], hs_dev bf16[n_slots, d_ff], ys_dev bf16[n_slots, d_model] */
+int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff);
+int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                         const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
+                         const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,
+                         void *work_dev, int n_experts, int max_slots, int d_model, int d_ff,
+                         int device, void *stream);
+
+/* out[token] = bf16(prob[token] * (slot >= 0 ? ys[slot] : hidden[token])): the scatter back to
+ * token order, the pass-through of dropped tokens and the router-probability scaling of
+ * sub1.py:312,318. */
+int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev,
+                     const void *prob_dev, void *out_dev, int n_tokens, int d_model, int device,
+                     void *stream);
+
+/* Frees every per-device cache the library holds (derived decoder tables keyed by the dec pointer).
+ * Call it after overwriting a dec tensor in place, and before unloading. */
+int qmoe_sub1_release(int device);
+
+#define QMOE_MAX_WIDTH 8192
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QMOE_SUB1_H_ */

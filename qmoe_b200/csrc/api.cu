@@ -1,0 +1,435 @@
+// C ABI (include/qmoe_sub1.h): argument checks, per-device caches and the host-side dictionary
+// construction.  Kernels live in sub1_matmul.cu, sub1_pack.cu and moe_route.cu.
+#include "common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <utility>
+#include <vector>
+
+namespace qmoe {
+
+// ---- error plumbing -------------------------------------------------------------------------
+static thread_local char g_error[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+  return QMOE_ERR_CUDA;
+}
+
+int sm_count(int device) {
+  static int cached[64] = {0};
+  if (device < 0 || device >= 64) return 148;
+  if (cached[device] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
+    cached[device] = n;
+  }
+  return cached[device];
+}
+
+// ---- launchers defined in the kernel files ------------------------------------------------------
+int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cudaStream_t stream);
+int launch_matmul_uniform(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
+                          const int32_t *row_off, const void *minmax, const void *x, void *y, int height,
+                          int width, int64_t n_codes, int tokens, int64_t x_stride, int64_t y_stride,
+                          int flags, int device, cudaStream_t stream);
+int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *codes, const int32_t *row_off,
+                  uint8_t *sym, int32_t *status, int height, int width, int64_t n_codes, cudaStream_t stream);
+int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
+int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
+                       const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
+                       const int32_t *offsets, const void *xs, void *hs, void *ys, void *work, int n_experts,
+                       int max_slots, int d_model, int d_ff, int device, cudaStream_t stream);
+int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
+                        cudaStream_t stream);
+int launch_pack_emit(const int32_t *w_tern, const int32_t *row_off, uint16_t *w_comp, int height, int width,
+                     cudaStream_t stream);
+int launch_pack_u8_count(const int32_t *trie, const uint8_t *sym, uint16_t *codes_tmp, int32_t *row_len,
+                         int n_mat, int height, int width, cudaStream_t stream);
+int launch_pack_u8_gather(const uint16_t *codes_tmp, const int32_t *row_off, const int64_t *mat_base,
+                          uint16_t *out, int n_mat, int height, int width, cudaStream_t stream);
+int launch_synth_ternary(uint8_t *sym, int64_t count, uint64_t seed, uint64_t first_index, float p_zero,
+                         cudaStream_t stream);
+int launch_route(const float *logits, int32_t *choice, void *prob, int n_tokens, int n_experts,
+                 cudaStream_t stream);
+int launch_rank(const int32_t *choice, int32_t *bucket, int32_t *rank, int32_t *counts, int n_tokens,
+                int n_buckets, int seq_len, int capacity, cudaStream_t stream);
+int launch_scan(const int32_t *counts, int32_t *offsets, int n, cudaStream_t stream);
+int launch_permute(const int32_t *bucket, const int32_t *rank, const int32_t *offsets, int32_t *slot,
+                   const void *hidden, void *xs, int n_tokens, int d_model, int64_t hidden_stride,
+                   int64_t xs_stride, cudaStream_t stream);
+int launch_unpermute(const void *ys, const int32_t *slot, void *out, int n_tokens, int d_model,
+                     int64_t ys_stride, int64_t out_stride, cudaStream_t stream);
+int launch_combine(const void *ys, const void *hidden, const int32_t *slot, const void *prob, void *out,
+                   int n_tokens, int d_model, cudaStream_t stream);
+
+// ---- sparse table cache ---------------------------------------------------------------------------
+struct CachedTable {
+  uint32_t *entries;
+  bool conforming;
+};
+static std::mutex g_mutex;
+static std::map<std::pair<int, const void *>, CachedTable> g_tables;
+
+int get_sparse_table(const int32_t *dec_dev, int device, cudaStream_t stream, SparseTable *out) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  const auto key = std::make_pair(device, (const void *)dec_dev);
+  auto it = g_tables.find(key);
+  if (it == g_tables.end()) {
+    // First use of this table on this device: build the sparse form and learn whether any entry
+    // needs the digit-by-digit path.  This synchronises the stream once.
+    uint32_t *entries = nullptr;
+    int *flag = nullptr;
+    QMOE_CUDA(cudaMalloc(&entries, sizeof(uint32_t) * QMOE_DICT_COUNT));
+    cudaError_t e = cudaMalloc(&flag, sizeof(int));
+    if (e != cudaSuccess) {
+      cudaFree(entries);
+      return cuda_fail(e, "cudaMalloc(flag)");
+    }
+    int rc = launch_build_table(dec_dev, entries, flag, stream);
+    int host_flag = 0;
+    if (rc == QMOE_OK) {
+      e = cudaMemcpyAsync(&host_flag, flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+      if (e != cudaSuccess) rc = cuda_fail(e, "sparse table build");
+    }
+    cudaFree(flag);
+    if (rc != QMOE_OK) {
+      cudaFree(entries);
+      return rc;
+    }
+    it = g_tables.emplace(key, CachedTable{entries, host_flag == 0}).first;
+  }
+  out->entries = it->second.entries;
+  out->conforming = it->second.conforming;
+  return QMOE_OK;
+}
+
+static int release_tables(int device) {
+  std::lock_guard<std::mutex> lock(g_mutex);
+  for (auto it = g_tables.begin(); it != g_tables.end();) {
+    if (it->first.first == device) {
+      cudaFree(it->second.entries);
+      it = g_tables.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  return QMOE_OK;
+}
+
+// ---- dictionary construction (host) ---------------------------------------------------------------
+// Best-first enumeration of the 65 536 most probable sequences of 1..14 ternary pairs under
+// P(0) = 0.885, exactly as setup() orders them (sub1.py:29-57): priority = running float64 product
+// that starts at -1.0 and is multiplied by the pair probability at every extension; ties are broken
+// by comparing the pair lists lexicographically, a prefix sorting before its extensions.
+struct Candidate {
+  double prio;
+  int32_t parent;  // dictionary index of the sequence without its last pair (65536 = empty)
+  uint8_t len;
+  uint8_t seq[14];
+};
+struct CandidateAfter {
+  bool operator()(const Candidate &a, const Candidate &b) const {  // true if a pops after b
+    if (a.prio != b.prio) return a.prio > b.prio;
+    const int n = a.len < b.len ? a.len : b.len;
+    const int c = memcmp(a.seq, b.seq, n);
+    if (c != 0) return c > 0;
+    return a.len > b.len;
+  }
+};
+
+static int build_dictionary(int32_t *dec, int32_t *trie) {
+  const double zeros = .885;
+  const double q[3] = {zeros, (1 - zeros) / 2, (1 - zeros) / 2};
+  double pair_prob[9];
+  for (int hi = 0; hi < 3; hi++)
+    for (int lo = 0; lo < 3; lo++) pair_prob[3 * hi + lo] = (1. * q[hi]) * q[lo];
+
+  std::priority_queue<Candidate, std::vector<Candidate>, CandidateAfter> pq;
+  Candidate root{};
+  root.prio = -1.;
+  root.parent = -1;
+  root.len = 0;
+  pq.push(root);
+  for (int i = 0; i < (QMOE_DICT_COUNT + 1) * 9; i++) trie[i] = -1;
+  int count = 0;
+  while (count < QMOE_DICT_COUNT) {
+    if (pq.empty()) return QMOE_ERR_UNSUPPORTED;
+    const Candidate top = pq.top();
+    pq.pop();
+    int idx = QMOE_TRIE_ROOT;
+    if (top.len > 0) {
+      idx = count++;
+      // Table words (sub1.py:60-72): low nibble = length in pairs; pair j of each half at bits
+      // 4+4j..7+4j, first weight (p % 3) in the low two bits, second (p / 3) in the high two.
+      uint32_t words[2] = {0u, 0u};
+      for (int j = 0; j < top.len; j++) {
+        const uint32_t p = top.seq[j];
+        const uint32_t nib = (p % 3) | ((p / 3) << 2);
+        words[j / 7] |= nib << (4 + 4 * (j % 7));
+      }
+      dec[2 * idx + 0] = (int32_t)(words[0] | top.len);
+      dec[2 * idx + 1] = (int32_t)(words[1] | top.len);
+      trie[9 * top.parent + top.seq[top.len - 1]] = idx;  // sub1.py:86-97
+    }
+    if (top.len == 14) continue;
+    for (int p = 0; p < 9; p++) {
+      Candidate c = top;
+      c.prio = top.prio * pair_prob[p];
+      c.seq[c.len++] = (uint8_t)p;
+      c.parent = idx;
+      pq.push(c);
+    }
+  }
+  return QMOE_OK;
+}
+
+static cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}  // namespace qmoe
+
+using namespace qmoe;
+
+extern "C" {
+
+const char *qmoe_last_error(void) { return g_error; }
+int qmoe_version(void) { return 100; }
+
+int qmoe_sub1_build_dictionary(int32_t *dec_host, int32_t *trie_host) {
+  QMOE_REQUIRE(dec_host != nullptr && trie_host != nullptr, "null output pointer");
+  return build_dictionary(dec_host, trie_host);
+}
+
+static int check_matrix_args(const char *fn, const void *dec, const void *w_comp, const void *row_off,
+                             const void *minmax, int height, int width, int64_t n_codes) {
+  if (dec == nullptr || row_off == nullptr || minmax == nullptr || (w_comp == nullptr && n_codes > 0)) {
+    set_error("%s: null device pointer", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (height < 1 || width < 1 || n_codes < 0) {
+    set_error("%s: bad shape height=%d width=%d n_codes=%lld", fn, height, width, (long long)n_codes);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (width > QMOE_MAX_WIDTH) {
+    set_error("%s: width %d exceeds QMOE_MAX_WIDTH (%d)", fn, width, QMOE_MAX_WIDTH);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  if (n_codes >= (int64_t)1 << 31) {
+    set_error("%s: a single matrix is limited to 2^31-1 codes", fn);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  if ((reinterpret_cast<uintptr_t>(w_comp) & 1u) || (reinterpret_cast<uintptr_t>(row_off) & 3u) ||
+      (reinterpret_cast<uintptr_t>(minmax) & 3u)) {
+    set_error("%s: misaligned pointer (w_comp 2, row_off 4, ter_minmax 4 bytes)", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  return QMOE_OK;
+}
+
+int qmoe_sub1_matmul(const int32_t *dec_dev, const uint16_t *w_comp_dev, const int32_t *row_off_dev,
+                     const void *ter_minmax_dev, const void *x_dev, void *y_dev, int height, int width,
+                     int64_t n_codes, int tokens, int64_t x_stride, int64_t y_stride, int flags, int device,
+                     void *stream) {
+  int rc = check_matrix_args(__func__, dec_dev, w_comp_dev, row_off_dev, ter_minmax_dev, height, width, n_codes);
+  if (rc) return rc;
+  QMOE_REQUIRE(tokens >= 0, "negative token count");
+  if (tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(x_dev != nullptr && y_dev != nullptr, "null activation pointer");
+  QMOE_REQUIRE(x_stride >= width && y_stride >= height, "row stride smaller than the row");
+  QMOE_REQUIRE(((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev)) & 1u) == 0,
+               "misaligned bf16 pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  SparseTable tab;
+  rc = get_sparse_table(dec_dev, device, as_stream(stream), &tab);
+  if (rc) return rc;
+  return launch_matmul_uniform(tab, dec_dev, w_comp_dev, row_off_dev, ter_minmax_dev, x_dev, y_dev, height,
+                               width, n_codes, tokens, x_stride, y_stride, flags, device, as_stream(stream));
+}
+
+int qmoe_sub1_matvec(const int32_t *dec_dev, const uint16_t *w_comp_dev, const int32_t *row_off_dev,
+                     const void *ter_minmax_dev, const void *x_dev, void *y_dev, int height, int width,
+                     int64_t n_codes, int device, void *stream) {
+  return qmoe_sub1_matmul(dec_dev, w_comp_dev, row_off_dev, ter_minmax_dev, x_dev, y_dev, height, width,
+                          n_codes, 1, width, height, QMOE_FLAG_ACCUMULATE, device, stream);
+}
+
+int qmoe_sub1_decode(const int32_t *dec_dev, const uint16_t *w_comp_dev, const int32_t *row_off_dev,
+                     uint8_t *sym_dev, int32_t *status_dev, int height, int width, int64_t n_codes, int device,
+                     void *stream) {
+  int rc = check_matrix_args(__func__, dec_dev, w_comp_dev, row_off_dev, dec_dev, height, width, n_codes);
+  if (rc) return rc;
+  QMOE_REQUIRE(sym_dev != nullptr, "null output pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  SparseTable tab;
+  rc = get_sparse_table(dec_dev, device, as_stream(stream), &tab);
+  if (rc) return rc;
+  return launch_decode(tab, dec_dev, w_comp_dev, row_off_dev, sym_dev, status_dev, height, width, n_codes,
+                       as_stream(stream));
+}
+
+int qmoe_sub1_pack_prepare(const int32_t *trie_dev, int32_t *w_tern_dev, int32_t *row_off_dev, int height,
+                           int width, int device, void *stream) {
+  QMOE_REQUIRE(trie_dev != nullptr && w_tern_dev != nullptr && row_off_dev != nullptr, "null device pointer");
+  QMOE_REQUIRE(height >= 1 && width >= 1, "bad shape");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_pack_prepare(trie_dev, w_tern_dev, row_off_dev, height, width, as_stream(stream));
+}
+
+int qmoe_sub1_pack_emit(const int32_t *w_tern_dev, const int32_t *row_off_dev, uint16_t *w_comp_dev,
+                        int height, int width, int device, void *stream) {
+  QMOE_REQUIRE(w_tern_dev != nullptr && row_off_dev != nullptr && w_comp_dev != nullptr, "null device pointer");
+  QMOE_REQUIRE(height >= 1 && width >= 1, "bad shape");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_pack_emit(w_tern_dev, row_off_dev, w_comp_dev, height, width, as_stream(stream));
+}
+
+int qmoe_sub1_pack_u8_count(const int32_t *trie_dev, const uint8_t *sym_dev, uint16_t *codes_tmp_dev,
+                            int32_t *row_len_dev, int n_mat, int height, int width, int device, void *stream) {
+  QMOE_REQUIRE(trie_dev && sym_dev && codes_tmp_dev && row_len_dev, "null device pointer");
+  QMOE_REQUIRE(n_mat >= 1 && height >= 1 && width >= 2 && (width & 1) == 0, "bad shape (width must be even)");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_pack_u8_count(trie_dev, sym_dev, codes_tmp_dev, row_len_dev, n_mat, height, width,
+                              as_stream(stream));
+}
+
+int qmoe_sub1_pack_u8_gather(const uint16_t *codes_tmp_dev, const int32_t *row_off_dev,
+                             const int64_t *mat_base_dev, uint16_t *out_dev, int n_mat, int height, int width,
+                             int device, void *stream) {
+  QMOE_REQUIRE(codes_tmp_dev && row_off_dev && mat_base_dev && out_dev, "null device pointer");
+  QMOE_REQUIRE(n_mat >= 1 && height >= 1 && width >= 2 && (width & 1) == 0, "bad shape (width must be even)");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_pack_u8_gather(codes_tmp_dev, row_off_dev, mat_base_dev, out_dev, n_mat, height, width,
+                               as_stream(stream));
+}
+
+int qmoe_synth_ternary(uint8_t *sym_dev, int64_t count, uint64_t seed, uint64_t first_index, float p_zero,
+                       int device, void *stream) {
+  QMOE_REQUIRE(sym_dev != nullptr && count >= 0, "bad arguments");
+  QMOE_REQUIRE(p_zero >= 0.f && p_zero <= 1.f, "p_zero outside [0, 1]");
+  if (count == 0) return QMOE_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_synth_ternary(sym_dev, count, seed, first_index, p_zero, as_stream(stream));
+}
+
+int qmoe_moe_route(const float *logits_dev, int32_t *choice_dev, void *prob_dev, int n_tokens, int n_experts,
+                   int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && n_experts >= 1, "bad shape");
+  if (n_tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(logits_dev && choice_dev && prob_dev, "null device pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_route(logits_dev, choice_dev, prob_dev, n_tokens, n_experts, as_stream(stream));
+}
+
+int qmoe_moe_rank(const int32_t *choice_dev, int32_t *bucket_dev, int32_t *rank_dev, int32_t *counts_dev,
+                  int n_tokens, int n_buckets, int seq_len, int capacity, int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && n_buckets >= 1, "bad shape");
+  QMOE_REQUIRE(counts_dev != nullptr, "null counts pointer");
+  QMOE_REQUIRE((choice_dev && bucket_dev && rank_dev) || n_tokens == 0, "null device pointer");
+  QMOE_REQUIRE(choice_dev != bucket_dev || n_tokens == 0, "bucket_dev must not alias choice_dev");
+  QMOE_REQUIRE(seq_len >= 1 && n_tokens % seq_len == 0, "n_tokens must be a multiple of seq_len");
+  QMOE_REQUIRE(capacity >= 0, "negative capacity");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_rank(choice_dev, bucket_dev, rank_dev, counts_dev, n_tokens, n_buckets, seq_len, capacity,
+                     as_stream(stream));
+}
+
+int qmoe_moe_scan(const int32_t *counts_dev, int32_t *offsets_dev, int n, int device, void *stream) {
+  QMOE_REQUIRE(counts_dev && offsets_dev && n >= 1, "bad arguments");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_scan(counts_dev, offsets_dev, n, as_stream(stream));
+}
+
+int qmoe_moe_permute(const int32_t *bucket_dev, const int32_t *rank_dev, const int32_t *offsets_dev,
+                     int32_t *slot_dev, const void *hidden_dev, void *xs_dev, int n_tokens, int d_model,
+                     int64_t hidden_stride, int64_t xs_stride, int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && d_model >= 1, "bad shape");
+  if (n_tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(bucket_dev && rank_dev && offsets_dev && slot_dev && hidden_dev && xs_dev, "null device pointer");
+  QMOE_REQUIRE(hidden_stride >= d_model && xs_stride >= d_model, "row stride smaller than the row");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_permute(bucket_dev, rank_dev, offsets_dev, slot_dev, hidden_dev, xs_dev, n_tokens, d_model,
+                        hidden_stride, xs_stride, as_stream(stream));
+}
+
+int qmoe_moe_unpermute(const void *ys_dev, const int32_t *slot_dev, void *out_dev, int n_tokens, int d_model,
+                       int64_t ys_stride, int64_t out_stride, int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && d_model >= 1, "bad shape");
+  if (n_tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(ys_dev && slot_dev && out_dev, "null device pointer");
+  QMOE_REQUIRE(ys_stride >= d_model && out_stride >= d_model, "row stride smaller than the row");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_unpermute(ys_dev, slot_dev, out_dev, n_tokens, d_model, ys_stride, out_stride, as_stream(stream));
+}
+
+int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff) {
+  (void)n_experts;
+  if (max_slots < 0 || d_model < 1 || d_ff < 1) return QMOE_ERR_INVALID_ARG;
+  return moe_work_bytes(max_slots, d_model, d_ff);
+}
+
+int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                         const void *minmax_dev, const qmoe_matrix_desc *descs_dev, const int32_t *offsets_dev,
+                         const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
+                         int max_slots, int d_model, int d_ff, int device, void *stream) {
+  QMOE_REQUIRE(dec_dev && codes_dev && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev,
+               "null device pointer");
+  QMOE_REQUIRE(n_experts >= 1 && max_slots >= 0 && d_model >= 1 && d_ff >= 1, "bad shape");
+  if (d_model > QMOE_MAX_WIDTH || d_ff > QMOE_MAX_WIDTH) {
+    set_error("%s: d_model/d_ff exceed QMOE_MAX_WIDTH (%d)", __func__, QMOE_MAX_WIDTH);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  if (max_slots == 0) return QMOE_OK;
+  QMOE_REQUIRE(xs_dev && hs_dev && ys_dev, "null activation pointer");
+  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(codes_dev) & 15u) == 0, "code store must be 16-byte aligned");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  SparseTable tab;
+  int rc = get_sparse_table(dec_dev, device, as_stream(stream), &tab);
+  if (rc) return rc;
+  return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, offsets_dev, xs_dev,
+                            hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff, device,
+                            as_stream(stream));
+}
+
+int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev, const void *prob_dev,
+                     void *out_dev, int n_tokens, int d_model, int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && d_model >= 1, "bad shape");
+  if (n_tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(hidden_dev && slot_dev && prob_dev && out_dev, "null device pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_combine(ys_dev, hidden_dev, slot_dev, prob_dev, out_dev, n_tokens, d_model, as_stream(stream));
+}
+
+int qmoe_sub1_release(int device) {
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return release_tables(device);
+}
+
+}  // extern "C"

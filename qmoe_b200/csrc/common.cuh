@@ -1,0 +1,67 @@
+// Shared declarations of the sm_100a kernels behind the C ABI in include/qmoe_sub1.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "qmoe_sub1.h"
+
+namespace qmoe {
+
+// ---- error plumbing -------------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define QMOE_CUDA(call)                                   \
+  do {                                                    \
+    cudaError_t e__ = (call);                             \
+    if (e__ != cudaSuccess) return qmoe::cuda_fail(e__, #call); \
+  } while (0)
+
+#define QMOE_REQUIRE(cond, msg)                           \
+  do {                                                    \
+    if (!(cond)) {                                        \
+      qmoe::set_error("%s: %s", __func__, msg);           \
+      return QMOE_ERR_INVALID_ARG;                        \
+    }                                                     \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) return;
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) return;
+    ok = true;
+  }
+  ~DeviceGuard() {
+    if (ok && prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+int sm_count(int device);
+
+// ---- derived decoder table -------------------------------------------------------------------
+// The reference table `dec` (sub1.py:60-72) spends 8 bytes per code on a dense list of 2-bit
+// digits.  Every entry of the standard dictionary has at most three non-zero digits, so the
+// kernels use a 4-byte sparse form built once per device from `dec`:
+//   bits 0..4    number of weights the code covers (2 * length in pairs, 2..28); 0 marks an entry
+//                that does not fit the sparse form (more than three non-zeros or a malformed word)
+//                and is decoded from `dec` digit by digit instead
+//   for k = 0..2, field at bit 5 + 9k:
+//     bits 0..6  4 * position of the k-th non-zero inside the code (a byte offset into fp32 x)
+//     bit  7     digit == 1 (row min)
+//     bit  8     digit == 2 (row max)
+//   absent non-zeros have an all-zero field.
+__host__ __device__ constexpr int kEntryFieldShift(int k) { return 5 + 9 * k; }
+
+struct SparseTable {
+  const uint32_t *entries = nullptr;  // uint32[65536] on the device
+  bool conforming = false;            // no entry needs the digit-by-digit path
+};
+
+// Returns the cached sparse table for (device, dec pointer), building it on `stream` on first use.
+int get_sparse_table(const int32_t *dec_dev, int device, cudaStream_t stream, SparseTable *out);
+
+}  // namespace qmoe

@@ -1,0 +1,462 @@
+// Fused dictionary decode + matvec / small-batch matmul for sm_100a, and the decode-to-symbols
+// kernel.  Replaces Sub1MatVec (sub1_cuda_kernel.cu:129-202) and the per-token launch loop of
+// Sub1Linear.forward (sub1.py:132-143).
+//
+// Design (differs from the reference on purpose):
+//  * one THREAD per row instead of one warp per row: codes are streamed with aligned 128-bit
+//    loads, the running column position is a private register, nothing is shuffled or synchronised
+//    inside a row, and all 32 lanes do useful work;
+//  * a derived 4-byte sparse dictionary (common.cuh) turns a code into at most three gathers from
+//    the activation vector instead of 28 multiply-adds:
+//        y[r] = min_r * sum_{digit 1} x[c] + max_r * sum_{digit 2} x[c];
+//  * the activations of up to four tokens are interleaved in shared memory so that one decode
+//    serves all of them (one 4/8/16-byte shared load per non-zero);
+//  * a work list of (matrix, row block, token group) items lets one launch cover every active
+//    expert of a MoE layer.
+#include "common.cuh"
+#include "sub1_walk.cuh"
+
+namespace qmoe {
+
+constexpr int kRowsPerItem = 256;  // threads per CTA == rows per work item
+constexpr int kMaxGroup = 4;       // tokens decoded together
+constexpr int kPad = 32;           // zero entries after x: a code spans at most 28 positions
+
+static inline int rows_per_chunk(int height) {
+  const int chunks = (height + kRowsPerItem - 1) / kRowsPerItem;
+  int rpc = (height + chunks - 1) / chunks;
+  rpc = (rpc + 31) / 32 * 32;
+  return rpc;
+}
+static inline int chunk_count(int height) {
+  const int rpc = rows_per_chunk(height);
+  return (height + rpc - 1) / rpc;
+}
+
+// ---- sinks ------------------------------------------------------------------------------------
+template <int T> struct VecT;
+template <> struct VecT<1> { using type = float; };
+template <> struct VecT<2> { using type = float2; };
+template <> struct VecT<4> { using type = float4; };
+
+template <int T>
+struct MatSink {
+  const char *xs;  // fp32 activations in shared memory, [position][T] interleaved
+  float s1[T], s2[T];
+
+  __device__ __forceinline__ void add(uint32_t f, const char *p) {
+    if (f & 0x180u) {
+      const typename VecT<T>::type v = *reinterpret_cast<const typename VecT<T>::type *>(p);
+      const float *vf = reinterpret_cast<const float *>(&v);
+      if (f & 0x80u) {
+#pragma unroll
+        for (int t = 0; t < T; t++) s1[t] += vf[t];
+      } else {
+#pragma unroll
+        for (int t = 0; t < T; t++) s2[t] += vf[t];
+      }
+    }
+  }
+  __device__ __forceinline__ void entry(uint32_t e, int pos) {
+    const char *base = xs + (size_t)pos * (4 * T);
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+      const uint32_t f = e >> kEntryFieldShift(k);
+      add(f, base + (f & 0x7cu) * T);
+    }
+  }
+  __device__ __forceinline__ void dense(int p, uint32_t digit) {
+    add(digit == 1u ? 0x80u : 0x100u, xs + (size_t)p * (4 * T));
+  }
+};
+
+struct SymbolSink {
+  uint8_t *row;  // width bytes, pre-zeroed
+  int width;
+  __device__ __forceinline__ void put(int p, uint8_t d) {
+    if (p < width) row[p] = d;
+  }
+  __device__ __forceinline__ void entry(uint32_t e, int pos) {
+#pragma unroll
+    for (int k = 0; k < 3; k++) {
+      const uint32_t f = e >> kEntryFieldShift(k);
+      if (f & 0x180u) put(pos + (int)((f & 0x7cu) >> 2), (f & 0x80u) ? 1 : 2);
+    }
+  }
+  __device__ __forceinline__ void dense(int p, uint32_t digit) { put(p, (uint8_t)digit); }
+};
+
+// ---- kernel arguments ---------------------------------------------------------------------------
+struct MatmulArgs {
+  const uint32_t *tab;
+  const int32_t *dec;
+  const uint16_t *codes;
+  const int32_t *row_off;
+  const __nv_bfloat162 *minmax;
+  const qmoe_matrix_desc *descs;  // grouped mode
+  qmoe_matrix_desc single;        // uniform mode
+  const __nv_bfloat16 *x;
+  __nv_bfloat16 *y;
+  long long x_stride, y_stride;
+  const int4 *items;  // grouped mode: {matrix, first row, first token, rows | tokens << 16}
+  int *header;        // grouped mode: header[0] = item count, header[1] = fetch counter
+  int chunks, rpc, tokens;  // uniform mode
+  int flags;
+};
+
+__device__ __forceinline__ float bf16_round(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+template <int T, bool GENERAL>
+__device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
+                                             int nrows, int tok0, int ntok, float *xs) {
+  const int tid = threadIdx.x;
+  const int W = d.width;
+  const int wlim = (W + 1) & ~1;
+
+  // Stage the token group: xs[c][t] = float(x[tok0 + t][c]), zero beyond the width / token count.
+  for (int c = tid; c < wlim + kPad; c += blockDim.x) {
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+      float v = 0.f;
+      if (c < W && t < ntok) v = __bfloat162float(a.x[(long long)(tok0 + t) * a.x_stride + c]);
+      xs[c * T + t] = v;
+    }
+  }
+  __syncthreads();
+
+  if (tid < nrows) {
+    const int row = row0 + tid;
+    const uint16_t *codes_m = a.codes + d.code_base;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
+    const uint16_t *codes_al = codes_m - mis;
+    const int32_t *ro = a.row_off + d.rowoff_base;
+    long long b = ro[row], e = ro[row + 1];
+    b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+    e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
+
+    MatSink<T> sink;
+    sink.xs = reinterpret_cast<const char *>(xs);
+#pragma unroll
+    for (int t = 0; t < T; t++) sink.s1[t] = sink.s2[t] = 0.f;
+    walk_row<GENERAL>(codes_al, (int)b + mis, (int)e + mis, a.tab, a.dec, wlim, sink);
+
+    const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
+    const float mn = __bfloat162float(mm.x), mx = __bfloat162float(mm.y);
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+      if (t < ntok) {
+        // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
+        float r = bf16_round(fmaf(mn, sink.s1[t], mx * sink.s2[t]));
+        __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
+        if (a.flags & QMOE_FLAG_ACCUMULATE) r = bf16_round(__bfloat162float(*yp) + r);
+        if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
+        *yp = __float2bfloat16_rn(r);
+      }
+    }
+  }
+}
+
+template <bool GENERAL>
+__device__ __forceinline__ void dispatch_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
+                                              int nrows, int tok0, int ntok, float *xs) {
+  if (ntok <= 1) process_item<1, GENERAL>(a, d, row0, nrows, tok0, ntok, xs);
+  else if (ntok == 2) process_item<2, GENERAL>(a, d, row0, nrows, tok0, ntok, xs);
+  else process_item<4, GENERAL>(a, d, row0, nrows, tok0, ntok, xs);
+}
+
+// One CTA per (row block, token group) of a single matrix.
+template <bool GENERAL>
+__global__ void __launch_bounds__(kRowsPerItem) k_matmul_uniform(const MatmulArgs a) {
+  extern __shared__ __align__(16) float xs[];
+  const int chunk = blockIdx.x % a.chunks;
+  const int group = blockIdx.x / a.chunks;
+  const int row0 = chunk * a.rpc;
+  const int nrows = min(a.rpc, a.single.height - row0);
+  const int tok0 = group * kMaxGroup;
+  const int ntok = min(kMaxGroup, a.tokens - tok0);
+  dispatch_item<GENERAL>(a, a.single, row0, nrows, tok0, ntok, xs);
+}
+
+// Persistent CTAs pulling items of a device-built work list.
+template <bool GENERAL>
+__global__ void __launch_bounds__(kRowsPerItem) k_matmul_grouped(const MatmulArgs a) {
+  extern __shared__ __align__(16) float xs[];
+  __shared__ int s_item;
+  const int n_items = a.header[0];
+  for (;;) {
+    if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
+    __syncthreads();
+    const int i = s_item;
+    if (i >= n_items) break;
+    const int4 it = a.items[i];
+    const qmoe_matrix_desc d = a.descs[it.x];
+    dispatch_item<GENERAL>(a, d, it.y, it.w & 0xffff, it.z, it.w >> 16, xs);
+    __syncthreads();  // xs and s_item are rewritten by the next round
+  }
+}
+
+// Decode to ternary symbols, one thread per row.
+template <bool GENERAL>
+__global__ void k_decode(const uint32_t *__restrict__ tab, const int32_t *__restrict__ dec,
+                         const uint16_t *__restrict__ codes, const int32_t *__restrict__ row_off,
+                         uint8_t *__restrict__ sym, int32_t *status, int height, int width,
+                         long long n_codes) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= height) return;
+  const int mis = (int)((reinterpret_cast<uintptr_t>(codes) & 15u) >> 1);
+  long long b = row_off[row], e = row_off[row + 1];
+  const bool span_ok = b >= 0 && e >= b && e <= n_codes;
+  b = b < 0 ? 0 : (b > n_codes ? n_codes : b);
+  e = e < b ? b : (e > n_codes ? n_codes : e);
+  SymbolSink sink{sym + (size_t)row * width, width};
+  const int wlim = (width + 1) & ~1;
+  const int pos = walk_row<GENERAL>(codes - mis, (int)b + mis, (int)e + mis, tab, dec, wlim + 2, sink);
+  if (status != nullptr && (pos != wlim || !span_ok)) atomicAdd(status, 1);
+}
+
+// ---- sparse table construction ------------------------------------------------------------------
+__global__ void k_build_table(const int32_t *__restrict__ dec, uint32_t *__restrict__ tab,
+                              int *nonconforming) {
+  const int code = blockIdx.x * blockDim.x + threadIdx.x;
+  if (code >= QMOE_DICT_COUNT) return;
+  const uint32_t w0 = (uint32_t)dec[2 * code], w1 = (uint32_t)dec[2 * code + 1];
+  const int len = (int)(w0 & 15u);
+  bool ok = len >= 1 && len <= 14 && (int)(w1 & 15u) == len;
+  uint32_t e = (uint32_t)(2 * len);
+  int nz = 0;
+  for (int t = 0; t < 28; t++) {
+    const uint32_t w = t < 14 ? w0 : w1;
+    const uint32_t digit = (w >> (4 + 2 * (t % 14))) & 3u;
+    if (digit == 0u) continue;
+    if (t >= 2 * len || digit == 3u || nz == 3) { ok = false; break; }
+    e |= ((uint32_t)(t << 2) | (digit == 1u ? 0x80u : 0x100u)) << kEntryFieldShift(nz);
+    nz++;
+  }
+  if (!ok) {
+    e = 0;  // decoded digit by digit from `dec`
+    atomicAdd(nonconforming, 1);
+  }
+  tab[code] = e;
+}
+
+// ---- launchers ----------------------------------------------------------------------------------
+static size_t smem_bytes(int width, int group) {
+  const int wlim = (width + 1) & ~1;
+  return (size_t)(wlim + kPad) * group * sizeof(float);
+}
+
+template <bool GENERAL>
+static int set_smem_limits() {
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_uniform<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  return QMOE_OK;
+}
+
+static int ensure_smem_limits(int device) {
+  static bool done[64] = {false};
+  if (device < 0 || device >= 64) {
+    set_error("device index %d out of range", device);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (!done[device]) {
+    int rc = set_smem_limits<false>();
+    if (rc) return rc;
+    rc = set_smem_limits<true>();
+    if (rc) return rc;
+    done[device] = true;
+  }
+  return QMOE_OK;
+}
+
+int launch_matmul_uniform(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
+                          const int32_t *row_off, const void *minmax, const void *x, void *y, int height,
+                          int width, int64_t n_codes, int tokens, int64_t x_stride, int64_t y_stride,
+                          int flags, int device, cudaStream_t stream) {
+  int rc = ensure_smem_limits(device);
+  if (rc) return rc;
+  MatmulArgs a{};
+  a.tab = tab.entries;
+  a.dec = dec;
+  a.codes = codes;
+  a.row_off = row_off;
+  a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
+  a.single.code_base = 0;
+  a.single.n_codes = n_codes;
+  a.single.rowoff_base = 0;
+  a.single.minmax_base = 0;
+  a.single.height = height;
+  a.single.width = width;
+  a.x = reinterpret_cast<const __nv_bfloat16 *>(x);
+  a.y = reinterpret_cast<__nv_bfloat16 *>(y);
+  a.x_stride = x_stride;
+  a.y_stride = y_stride;
+  a.chunks = chunk_count(height);
+  a.rpc = rows_per_chunk(height);
+  a.tokens = tokens;
+  a.flags = flags;
+  const int groups = (tokens + kMaxGroup - 1) / kMaxGroup;
+  const int group = tokens >= 3 ? 4 : tokens;
+  const size_t smem = smem_bytes(width, group);
+  const dim3 grid((unsigned)(a.chunks * groups));
+  if (tab.conforming)
+    k_matmul_uniform<false><<<grid, kRowsPerItem, smem, stream>>>(a);
+  else
+    k_matmul_uniform<true><<<grid, kRowsPerItem, smem, stream>>>(a);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *codes, const int32_t *row_off,
+                  uint8_t *sym, int32_t *status, int height, int width, int64_t n_codes,
+                  cudaStream_t stream) {
+  QMOE_CUDA(cudaMemsetAsync(sym, 0, (size_t)height * width, stream));
+  if (status != nullptr) QMOE_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+  const int threads = 128;
+  const int blocks = (height + threads - 1) / threads;
+  if (tab.conforming)
+    k_decode<false><<<blocks, threads, 0, stream>>>(tab.entries, dec, codes, row_off, sym, status, height,
+                                                    width, n_codes);
+  else
+    k_decode<true><<<blocks, threads, 0, stream>>>(tab.entries, dec, codes, row_off, sym, status, height,
+                                                   width, n_codes);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cudaStream_t stream) {
+  QMOE_CUDA(cudaMemsetAsync(nonconforming, 0, sizeof(int), stream));
+  k_build_table<<<QMOE_DICT_COUNT / 256, 256, 0, stream>>>(dec, tab, nonconforming);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+// ---- grouped expert FFN -------------------------------------------------------------------------
+// Work buffer layout: int header[16] | int4 items_wi[max_slots * chunks_wi] | int4 items_wo[...].
+// header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter.
+__global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
+                                                     int d_model, int d_ff, int rpc_wi, int chunks_wi,
+                                                     int rpc_wo, int chunks_wo, int max_slots,
+                                                     int *header, int4 *items_wi, int4 *items_wo) {
+  __shared__ int s_warp[32];
+  __shared__ int s_base;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
+    const int e = e0 + tid;
+    int first = 0, count = 0;
+    if (e < n_experts) {
+      first = offsets[e];
+      count = offsets[e + 1] - first;
+      count = count < 0 ? 0 : count;
+    }
+    const int groups = (count + kMaxGroup - 1) / kMaxGroup;
+    // exclusive scan of `groups` over the block
+    int incl = groups;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += v;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
+    for (int g = 0; g < groups; g++) {
+      const int gi = base + g;
+      if (gi >= max_slots) break;  // cannot happen while offsets[n_experts] <= max_slots
+      const int tok0 = first + g * kMaxGroup;
+      const int ntok = min(kMaxGroup, count - g * kMaxGroup);
+      for (int k = 0; k < chunks_wi; k++) {
+        const int row0 = k * rpc_wi;
+        items_wi[(size_t)gi * chunks_wi + k] = make_int4(2 * e, row0, tok0, min(rpc_wi, d_ff - row0) | (ntok << 16));
+      }
+      for (int k = 0; k < chunks_wo; k++) {
+        const int row0 = k * rpc_wo;
+        items_wo[(size_t)gi * chunks_wo + k] = make_int4(2 * e + 1, row0, tok0, min(rpc_wo, d_model - row0) | (ntok << 16));
+      }
+    }
+    __syncthreads();
+    if (tid == 0) s_base += s_warp[31];
+    __syncthreads();
+  }
+  if (tid == 0) {
+    const int total = min(s_base, max_slots);
+    header[0] = total * chunks_wi;
+    header[1] = 0;
+    header[2] = total * chunks_wo;
+    header[3] = 0;
+  }
+}
+
+int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
+  return 64 + (int64_t)max_slots * (chunk_count(d_ff) + chunk_count(d_model)) * (int64_t)sizeof(int4);
+}
+
+int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
+                       const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
+                       const int32_t *offsets, const void *xs, void *hs, void *ys, void *work, int n_experts,
+                       int max_slots, int d_model, int d_ff, int device, cudaStream_t stream) {
+  int rc = ensure_smem_limits(device);
+  if (rc) return rc;
+  const int chunks_wi = chunk_count(d_ff), chunks_wo = chunk_count(d_model);
+  const int rpc_wi = rows_per_chunk(d_ff), rpc_wo = rows_per_chunk(d_model);
+  int *header = reinterpret_cast<int *>(work);
+  int4 *items_wi = reinterpret_cast<int4 *>(reinterpret_cast<char *>(work) + 64);
+  int4 *items_wo = items_wi + (size_t)max_slots * chunks_wi;
+  k_build_work<<<1, 1024, 0, stream>>>(offsets, n_experts, d_model, d_ff, rpc_wi, chunks_wi, rpc_wo,
+                                       chunks_wo, max_slots, header, items_wi, items_wo);
+  QMOE_CUDA(cudaGetLastError());
+
+  MatmulArgs a{};
+  a.tab = tab.entries;
+  a.dec = dec;
+  a.codes = codes;
+  a.row_off = row_off;
+  a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
+  a.descs = descs;
+  const int sms = sm_count(device);
+
+  for (int phase = 0; phase < 2; phase++) {
+    const int width = phase == 0 ? d_model : d_ff;
+    a.x = reinterpret_cast<const __nv_bfloat16 *>(phase == 0 ? xs : hs);
+    a.y = reinterpret_cast<__nv_bfloat16 *>(phase == 0 ? hs : ys);
+    a.x_stride = width;
+    a.y_stride = phase == 0 ? d_ff : d_model;
+    a.items = phase == 0 ? items_wi : items_wo;
+    a.header = header + 2 * phase;
+    a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
+    const size_t smem = smem_bytes(width, kMaxGroup);
+    int per_sm = 0;
+    if (tab.conforming)
+      QMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_matmul_grouped<false>, kRowsPerItem, smem));
+    else
+      QMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_matmul_grouped<true>, kRowsPerItem, smem));
+    per_sm = per_sm < 1 ? 1 : per_sm;
+    const long long max_items = (long long)max_slots * (phase == 0 ? chunks_wi : chunks_wo);
+    long long grid = (long long)sms * per_sm;
+    grid = grid > max_items ? max_items : grid;
+    grid = grid < 1 ? 1 : grid;
+    if (tab.conforming)
+      k_matmul_grouped<false><<<(unsigned)grid, kRowsPerItem, smem, stream>>>(a);
+    else
+      k_matmul_grouped<true><<<(unsigned)grid, kRowsPerItem, smem, stream>>>(a);
+    QMOE_CUDA(cudaGetLastError());
+  }
+  return QMOE_OK;
+}
+
+}  // namespace qmoe

@@ -1,0 +1,327 @@
+"""Host side of the compressed-expert path, mirroring the reference's ``sub1.py`` interface.
+
+* :func:`setup` -- the fixed dictionary ``dec`` / ``trie`` (sub1.py:29-102), built by the native
+  library in a few tens of milliseconds instead of at import time;
+* :class:`Sub1Linear` -- same buffers (``w_comp``, ``row_off``, ``ter_minmax``, ``weight``), same
+  ``forward`` / ``make`` contract as sub1.py:114-166, but one batched launch per call instead of one
+  launch per token;
+* :class:`ExpertStore` -- every expert matrix of a sparse layer in three flat device arrays, the
+  layout the grouped kernels stream from;
+* :class:`FasterMLP` -- the top-1 MoE layer of sub1.py:299-321 on one GPU: route, group, grouped
+  FFN over all active experts, combine, without host synchronisation.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import _lib, sub1_cuda
+from ._lib import MatrixDesc
+
+# ---------------------------------------------------------------------------------------------
+# Dictionary (sub1.py:29-111): built lazily, uploaded per device on first use.
+# ---------------------------------------------------------------------------------------------
+_DICT: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+_DEC: Dict[int, torch.Tensor] = {}
+_TRIE: Dict[int, torch.Tensor] = {}
+
+
+def setup() -> Tuple[torch.Tensor, torch.Tensor]:
+    """(dec int32[131072], trie int32[65537, 9]) on the CPU, bit-identical to the reference's
+    ``setup()`` (sub1.py:29-102)."""
+    global _DICT
+    if _DICT is None:
+        dec = np.zeros(2 * _lib.DICT_COUNT, dtype=np.int32)
+        trie = np.zeros((_lib.DICT_COUNT + 1, 9), dtype=np.int32)
+        _lib.check(_lib.load().qmoe_sub1_build_dictionary(dec.ctypes.data, trie.ctypes.data))
+        _DICT = (torch.from_numpy(dec), torch.from_numpy(trie))
+    return _DICT
+
+
+def _dev_index(device) -> int:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError("the sub1 kernels run on CUDA devices only")
+    return torch.cuda.current_device() if device.index is None else device.index
+
+
+def DEC(device) -> torch.Tensor:
+    """The decoder table on ``device`` (the reference keeps one copy per GPU, sub1.py:110)."""
+    i = _dev_index(device)
+    if i not in _DEC:
+        _DEC[i] = setup()[0].to(torch.device("cuda", i))
+    return _DEC[i]
+
+
+def TRIE(device) -> torch.Tensor:
+    """The encoder trie on ``device`` (sub1.py:111)."""
+    i = _dev_index(device)
+    if i not in _TRIE:
+        _TRIE[i] = setup()[1].to(torch.device("cuda", i)).contiguous()
+    return _TRIE[i]
+
+
+# ---------------------------------------------------------------------------------------------
+# Sub1Linear (sub1.py:114-166)
+# ---------------------------------------------------------------------------------------------
+class Sub1Linear(nn.Module):
+    """One compressed ``[height, width]`` matrix.  Buffers and state-dict keys are the reference's
+    (sub1.py:118-130), so ``expNN.pt`` checkpoints load unchanged."""
+
+    def __init__(self, height: int, comp_size: int):
+        super().__init__()
+        self.register_buffer("w_comp", torch.zeros(comp_size, dtype=torch.int16))
+        self.register_buffer("row_off", torch.zeros(height + 1, dtype=torch.int32))
+        self.register_buffer("ter_minmax", torch.zeros(2 * height, dtype=torch.bfloat16))
+        # HuggingFace Switch checks `wi.weight.dtype`; the reference keeps an empty tensor for it.
+        self.register_buffer("weight", torch.zeros(0, dtype=torch.bfloat16))
+
+    @property
+    def height(self) -> int:
+        return self.row_off.shape[0] - 1
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """``x[t, width] -> y[t, height]`` bf16; equals the reference's zero-then-accumulate loop
+        (sub1.py:132-143) because ``0 + v`` is exact in bf16."""
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.bfloat16()
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        y = torch.empty((x2.shape[0], self.height), dtype=torch.bfloat16, device=x2.device)
+        if x2.shape[0]:
+            sub1_cuda.sub1matmul(DEC(self.w_comp.device), self.w_comp, self.row_off, self.ter_minmax, x2, y, 0)
+        return y.reshape(*lead, self.height)
+
+    def forward_per_token(self, x: torch.Tensor) -> torch.Tensor:
+        """The reference's literal protocol: zero ``y`` and call ``sub1matvec`` once per token."""
+        y = torch.zeros((x.shape[0], self.height), dtype=torch.bfloat16, device=x.device)
+        dec = DEC(self.w_comp.device)
+        for i in range(y.shape[0]):
+            sub1_cuda.sub1matvec(dec, self.w_comp, self.row_off, self.ter_minmax, x[i], y[i])
+        return y
+
+    @staticmethod
+    def make(w: torch.Tensor) -> "Sub1Linear":
+        """Compress a matrix whose rows hold at most three distinct values {min, 0, max}
+        (sub1.py:145-166): symbols 1 / 2 mark the row minimum / maximum."""
+        w = w.bfloat16()
+        ter_minmax = torch.column_stack((w.min(1)[0], w.max(1)[0])).flatten()
+        row_off = torch.zeros(w.shape[0] + 1, dtype=torch.int32, device=w.device)
+        w_tern = torch.zeros(w.shape, dtype=torch.int32, device=w.device)
+        w_tern[w == ter_minmax[0::2].reshape((-1, 1))] = 1
+        w_tern[w == ter_minmax[1::2].reshape((-1, 1))] = 2
+        w_comp = sub1_cuda.sub1pack(TRIE(w.device), w_tern, row_off)
+        linear = Sub1Linear(w.shape[0], w_comp.shape[0])
+        linear.w_comp = w_comp
+        linear.row_off = row_off
+        linear.ter_minmax = ter_minmax
+        linear.weight = linear.weight.to(w.device)
+        return linear
+
+
+# ---------------------------------------------------------------------------------------------
+# Expert store: all matrices of a sparse layer in flat arrays
+# ---------------------------------------------------------------------------------------------
+class ExpertStore:
+    """Matrices ``2e`` (wi, ``[d_ff, d_model]``) and ``2e + 1`` (wo, ``[d_model, d_ff]``) of the
+    local experts ``e`` of one sparse layer.
+
+    ``codes`` int16: every matrix's stream, each starting on a 16-byte boundary;
+    ``row_off`` int32: the matrices' ``height + 1`` offsets (relative to their own stream);
+    ``minmax`` bf16: interleaved (min, max) per row;
+    ``descs``: device array of ``qmoe_matrix_desc``."""
+
+    def __init__(self, codes: torch.Tensor, row_off: torch.Tensor, minmax: torch.Tensor,
+                 descs: Sequence[MatrixDesc], d_model: int, d_ff: int):
+        assert codes.dtype == torch.int16 and row_off.dtype == torch.int32 and minmax.dtype == torch.bfloat16
+        assert len(descs) % 2 == 0
+        self.codes, self.row_off, self.minmax = codes, row_off, minmax
+        self.d_model, self.d_ff = int(d_model), int(d_ff)
+        self.n_experts = len(descs) // 2
+        self.host_descs = list(descs)
+        arr = (MatrixDesc * len(descs))(*descs)
+        raw = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
+        self.descs = torch.from_numpy(raw).to(codes.device)
+        self.device = codes.device
+
+    @property
+    def compressed_bytes(self) -> int:
+        return self.codes.numel() * 2 + self.row_off.numel() * 4 + self.minmax.numel() * 2
+
+    def matrix_bytes(self, m: int) -> int:
+        """Algorithmic bytes of one matrix: codes + row offsets + (min, max) pairs."""
+        d = self.host_descs[m]
+        return 2 * d.n_codes + 4 * (d.height + 1) + 4 * d.height
+
+    def matrix(self, m: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(w_comp, row_off, ter_minmax) views of matrix ``m`` in the reference's per-matrix layout."""
+        d = self.host_descs[m]
+        return (self.codes[d.code_base:d.code_base + d.n_codes],
+                self.row_off[d.rowoff_base:d.rowoff_base + d.height + 1],
+                self.minmax[2 * d.minmax_base:2 * (d.minmax_base + d.height)])
+
+    @staticmethod
+    def from_linears(experts: Sequence[Tuple[Sub1Linear, Sub1Linear]], d_model: int, d_ff: int) -> "ExpertStore":
+        """Concatenate (wi, wo) pairs of :class:`Sub1Linear` into a store."""
+        parts = []
+        for wi, wo in experts:
+            parts.append((wi.w_comp, wi.row_off, wi.ter_minmax, d_ff, d_model))
+            parts.append((wo.w_comp, wo.row_off, wo.ter_minmax, d_model, d_ff))
+        return ExpertStore.from_matrices(parts, d_model, d_ff)
+
+    @staticmethod
+    def from_matrices(parts: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int, int]],
+                      d_model: int, d_ff: int) -> "ExpertStore":
+        dev = parts[0][0].device
+        descs: List[MatrixDesc] = []
+        code_base = rowoff_base = minmax_base = 0
+        for w_comp, row_off, minmax, h, w in parts:
+            assert row_off.numel() == h + 1 and minmax.numel() == 2 * h
+            descs.append(MatrixDesc(code_base, w_comp.numel(), rowoff_base, minmax_base, h, w))
+            code_base += (w_comp.numel() + 7) // 8 * 8
+            rowoff_base += h + 1
+            minmax_base += h
+        codes = torch.zeros(max(code_base, 8), dtype=torch.int16, device=dev)
+        row_offs = torch.empty(rowoff_base, dtype=torch.int32, device=dev)
+        minmaxs = torch.empty(2 * minmax_base, dtype=torch.bfloat16, device=dev)
+        for d, (w_comp, row_off, minmax, h, w) in zip(descs, parts):
+            codes[d.code_base:d.code_base + d.n_codes] = w_comp.view(torch.int16)
+            row_offs[d.rowoff_base:d.rowoff_base + h + 1] = row_off
+            minmaxs[2 * d.minmax_base:2 * (d.minmax_base + h)] = minmax
+        return ExpertStore(codes, row_offs, minmaxs, descs, d_model, d_ff)
+
+
+# ---------------------------------------------------------------------------------------------
+# Device-side MoE plumbing shared by the single-GPU and the expert-parallel layer
+# ---------------------------------------------------------------------------------------------
+def _s(dev: torch.device) -> int:
+    return int(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def route_top1(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(choice int32[n], prob bf16[n]) from fp32 logits ``[n, E]``."""
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    n, e = logits.shape
+    dev = logits.device
+    choice = torch.empty(n, dtype=torch.int32, device=dev)
+    prob = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    _lib.check(_lib.load().qmoe_moe_route(logits.data_ptr(), choice.data_ptr(), prob.data_ptr(), n, e,
+                                          dev.index, _s(dev)))
+    return choice, prob
+
+
+def rank_buckets(choice: torch.Tensor, n_buckets: int, seq_len: int, capacity: int):
+    """(bucket, rank, counts, offsets): capacity rule, stable ranks, bucket sizes and their
+    exclusive prefix sums (``offsets`` has ``n_buckets + 1`` entries)."""
+    assert choice.is_cuda and choice.dtype == torch.int32 and choice.is_contiguous()
+    n = choice.numel()
+    dev = choice.device
+    bucket = torch.empty(n, dtype=torch.int32, device=dev)
+    rank = torch.empty(n, dtype=torch.int32, device=dev)
+    counts = torch.empty(n_buckets, dtype=torch.int32, device=dev)
+    offsets = torch.empty(n_buckets + 1, dtype=torch.int32, device=dev)
+    L = _lib.load()
+    _lib.check(L.qmoe_moe_rank(choice.data_ptr(), bucket.data_ptr(), rank.data_ptr(), counts.data_ptr(), n,
+                               n_buckets, max(int(seq_len), 1), int(capacity), dev.index, _s(dev)))
+    _lib.check(L.qmoe_moe_scan(counts.data_ptr(), offsets.data_ptr(), n_buckets, dev.index, _s(dev)))
+    return bucket, rank, counts, offsets
+
+
+def permute_rows(bucket, rank, offsets, hidden: torch.Tensor, xs: torch.Tensor) -> torch.Tensor:
+    """``xs[offsets[bucket] + rank] = hidden[token]``; returns slot int32[n] (-1 = dropped)."""
+    n, d = hidden.shape
+    dev = hidden.device
+    slot = torch.empty(n, dtype=torch.int32, device=dev)
+    _lib.check(_lib.load().qmoe_moe_permute(bucket.data_ptr(), rank.data_ptr(), offsets.data_ptr(),
+                                            slot.data_ptr(), hidden.data_ptr(), xs.data_ptr(), n, d,
+                                            hidden.stride(0), xs.stride(0), dev.index, _s(dev)))
+    return slot
+
+
+def unpermute_rows(ys: torch.Tensor, slot: torch.Tensor, out: torch.Tensor) -> None:
+    n, d = out.shape
+    dev = out.device
+    _lib.check(_lib.load().qmoe_moe_unpermute(ys.data_ptr(), slot.data_ptr(), out.data_ptr(), n, d,
+                                              ys.stride(0), out.stride(0), dev.index, _s(dev)))
+
+
+def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max_slots: int,
+                work: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``wo(ReLU(wi(x)))`` for tokens sorted by local expert (``offsets`` int32[E+1]); returns
+    ``ys`` bf16[max_slots, d_model].  Rows past ``offsets[E]`` are left untouched."""
+    dev = store.device
+    L = _lib.load()
+    hs = torch.empty((max_slots, store.d_ff), dtype=torch.bfloat16, device=dev)
+    ys = torch.empty((max_slots, store.d_model), dtype=torch.bfloat16, device=dev)
+    if max_slots == 0:
+        return ys
+    nbytes = int(L.qmoe_moe_work_bytes(store.n_experts, max_slots, store.d_model, store.d_ff))
+    if work is None or work.numel() < nbytes:
+        work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    assert xs.is_contiguous() and xs.shape[1] == store.d_model
+    _lib.check(L.qmoe_moe_grouped_ffn(DEC(dev).data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(),
+                                      store.minmax.data_ptr(), store.descs.data_ptr(), offsets.data_ptr(),
+                                      xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(),
+                                      store.n_experts, max_slots, store.d_model, store.d_ff, dev.index, _s(dev)))
+    return ys
+
+
+def combine(ys: torch.Tensor, hidden: torch.Tensor, slot: torch.Tensor, prob: torch.Tensor) -> torch.Tensor:
+    """``out[t] = prob[t] * (ys[slot[t]] if slot[t] >= 0 else hidden[t])`` (sub1.py:312,317-318)."""
+    n, d = hidden.shape
+    dev = hidden.device
+    out = torch.empty_like(hidden)
+    assert hidden.is_contiguous() and (ys.numel() == 0 or ys.is_contiguous())
+    _lib.check(_lib.load().qmoe_moe_combine(ys.data_ptr(), hidden.data_ptr(), slot.data_ptr(), prob.data_ptr(),
+                                            out.data_ptr(), n, d, dev.index, _s(dev)))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# FasterMLP (sub1.py:299-321): the single-GPU top-1 MoE layer
+# ---------------------------------------------------------------------------------------------
+class FasterMLP(nn.Module):
+    """Top-1 MoE layer over compressed experts.
+
+    ``router_weight``: the router classifier ``[n_experts, d_model]`` (no bias, as in HF Switch);
+    ``store``: the layer's :class:`ExpertStore`; ``expert_capacity``: tokens of one sequence an
+    expert accepts before the router drops them (dropped tokens pass through scaled by their router
+    probability, sub1.py:312,318).  Unlike the reference there is no loop over active experts and
+    no host synchronisation: one grouped launch per linear covers every expert that got tokens."""
+
+    def __init__(self, router_weight: Optional[torch.Tensor], store: ExpertStore, expert_capacity: int = 1024):
+        super().__init__()
+        self.store = store
+        self.expert_capacity = int(expert_capacity)
+        self.router_weight = None if router_weight is None else router_weight.to(store.device, torch.float32)
+
+    def router_logits(self, hidden2d: torch.Tensor) -> torch.Tensor:
+        # The Switch router computes its logits in fp32 from the bf16 hidden states.
+        return hidden2d.float() @ self.router_weight.t()
+
+    def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
+        shape = hidden_states.shape
+        seq_len = shape[-2] if hidden_states.dim() >= 3 else shape[0]
+        hidden = hidden_states.reshape(-1, shape[-1]).to(self.store.device)
+        if hidden.dtype != torch.bfloat16 or not hidden.is_contiguous():
+            hidden = hidden.bfloat16().contiguous()
+        n = hidden.shape[0]
+        if router_logits is None:
+            router_logits = self.router_logits(hidden)
+        logits2d = router_logits.reshape(n, -1).float().contiguous()
+        choice, prob = route_top1(logits2d)
+        bucket, rank, _counts, offsets = rank_buckets(choice, self.store.n_experts, seq_len, self.expert_capacity)
+        xs = torch.empty_like(hidden)
+        slot = permute_rows(bucket, rank, offsets, hidden, xs)
+        ys = grouped_ffn(self.store, offsets, xs, n)
+        out = combine(ys, hidden, slot, prob)
+        expert_index = torch.clamp(bucket, min=0).to(torch.int64)
+        lead = shape[:-1]
+        return (out.reshape(shape).to(hidden_states.device),
+                (router_logits.reshape(*lead, -1), expert_index.reshape(lead)))
