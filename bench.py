@@ -1,0 +1,382 @@
+"""Benchmark of the compressed-expert MoE layer (one step = one forward pass of one layer).
+
+    python bench.py --gpus N --steps K --warmup W            # this implementation
+    python bench.py --impl reference --gpus N --steps K ...  # CPU baseline arm (rank 0 only)
+
+Workload (default ``switch-c-2048``): one Switch-c-2048-shaped sparse layer -- d_model 2080, d_ff
+6144, 2048 experts of ternary weights (P(0) = 0.90) compressed with the reference's dictionary
+encoder (~4.6 GB), 2048 bf16 tokens ~ N(0,1) routed top-1 by a seeded random router -- expert-parallel
+over N GPUs of one node (2048 / N experts and 2048 / N tokens per rank).  Weights are synthetic and
+seeded (the Switch checkpoints are not available offline); they are generated and packed on the GPU.
+
+The one JSON line printed by rank 0 carries: ``value`` = tokens/s with inputs resident in HBM (CUDA
+events, max over ranks); ``e2e`` = tokens/s with pinned-host inputs and outputs (H2D + layer + D2H in
+the timed region); ``roofline`` for the grouped decode-matvec kernel (algorithmic compressed bytes /
+event-timed launch duration, against the measured HBM copy bandwidth); ``cpu_baseline`` = the CPU
+oracle on a bounded sample of the same experts.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+SEED = 0
+FALLBACK_HBM_GBS = 6650.0
+
+WORKLOADS = {
+    # name: (d_model, d_ff, experts, tokens)
+    "switch-c-2048": (2080, 6144, 2048, 2048),
+    "switch-large-128": (1024, 4096, 128, 512),
+    "switch-base-128": (768, 3072, 128, 128),
+}
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default="switch-c-2048", choices=sorted(WORKLOADS))
+    p.add_argument("--experts", type=int, default=0, help="override the expert count (debugging)")
+    p.add_argument("--tokens", type=int, default=0, help="override the token count (debugging)")
+    p.add_argument("--cpu-seconds", type=float, default=12.0, help="target duration of the CPU baseline sample")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    return p.parse_args()
+
+
+def workload_dims(args):
+    d_model, d_ff, experts, tokens = WORKLOADS[args.workload]
+    return d_model, d_ff, args.experts or experts, args.tokens or tokens
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples every 200 ms while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons = [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    out["sm_max_mhz"] = float(f[2])
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            out["sm_mhz"] = sm[len(sm) // 2]
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def recorded_traffic_ratio():
+    """DRAM bytes per algorithmic byte of the grouped kernel, from the committed ncu summary."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "k_matmul_grouped.traffic.json")) as f:
+            return float(json.load(f)["dram_bytes_per_algorithmic_byte"])
+    except Exception:
+        return None
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline (the oracle: C port of the reference's CPU decode + matmul path)
+# ---------------------------------------------------------------------------------------------
+def cpu_sample_experts(d_model, d_ff, expert_ids):
+    """Build the same seeded experts on the CPU (oracle generator + oracle encoder)."""
+    import numpy as np
+    from oracle import oracle as O
+    from qmoe_b200 import synth
+    _, trie = O.build_dictionary()
+    out = []
+    for e in expert_ids:
+        mats = []
+        for which, (h, w) in enumerate(((d_ff, d_model), (d_model, d_ff))):
+            m = 2 * e + which
+            sym = O.synth_ternary(h * w, SEED, synth.matrix_first_index(m), 0.9).reshape(h, w)
+            codes, row_off = O.encode_matrix(trie, sym)
+            mm = synth.row_scales(h, SEED, m)
+            mats.append((codes, row_off, mm.view(__import__("torch").int16).numpy().view(np.uint16)))
+        out.append(mats)
+    return out
+
+
+def cpu_time_sample(d_model, d_ff, experts, x_bits):
+    """Seconds to push one token through each sampled expert with the oracle (all host threads)."""
+    from oracle import oracle as O
+    dec, _ = O.build_dictionary()
+    t0 = time.perf_counter()
+    for i, (wi, wo) in enumerate(experts):
+        O.expert_ffn(dec, wi, wo, x_bits[i % x_bits.shape[0]:i % x_bits.shape[0] + 1], d_model, d_ff)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(args, d_model, d_ff, n_experts):
+    import numpy as np
+    from oracle import oracle as O
+    from qmoe_b200 import synth
+    x = synth.tokens(64, d_model, SEED)
+    x_bits = x.view(__import__("torch").int16).numpy().view(np.uint16)
+    probe = cpu_sample_experts(d_model, d_ff, [0])
+    cpu_time_sample(d_model, d_ff, probe, x_bits)
+    per = max(cpu_time_sample(d_model, d_ff, probe, x_bits), 1e-4)
+    count = int(max(2, min(n_experts, 256, args.cpu_seconds / per)))
+    experts = probe + cpu_sample_experts(d_model, d_ff, list(range(1, count)))
+    secs = cpu_time_sample(d_model, d_ff, experts, x_bits)
+    return {
+        "value": count / secs, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+        "sample": f"{count} experts x 1 token each ({args.workload} shapes), C port of the reference's CPU "
+                  f"decode (test.py:103-115) + matmul, OpenMP over rows, {secs:.2f} s",
+    }
+
+
+def run_reference(args):
+    """CPU arm: rank 0 alone times the oracle port on bounded samples of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    from qmoe_b200 import synth
+    O.build()
+    d_model, d_ff, n_experts, n_tokens = workload_dims(args)
+    x = synth.tokens(64, d_model, SEED)
+    x_bits = x.view(__import__("torch").int16).numpy().view(np.uint16)
+    probe = cpu_sample_experts(d_model, d_ff, [0])
+    cpu_time_sample(d_model, d_ff, probe, x_bits)
+    per = max(cpu_time_sample(d_model, d_ff, probe, x_bits), 1e-4)
+    budget = 90.0 / max(args.steps + args.warmup, 1)           # whole run within a few minutes
+    count = int(max(2, min(n_experts, 64, budget / per)))
+    experts = probe + cpu_sample_experts(d_model, d_ff, list(range(1, count)))
+    for _ in range(args.warmup):
+        cpu_time_sample(d_model, d_ff, experts, x_bits)
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_time_sample(d_model, d_ff, experts, x_bits)
+    value = count * args.steps / t
+    sample = (f"{count} experts x 1 token per step ({args.workload} shapes); C port of the reference's CPU "
+              f"decode (test.py:103-115) + matmul; OpenMP over rows")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded ternary experts, P(0)=0.90)",
+        "config": {"workload": args.workload, "d_model": d_model, "d_ff": d_ff, "experts": n_experts,
+                   "tokens": n_tokens, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
+# this implementation
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from qmoe_b200 import _lib, sub1, synth
+    from qmoe_b200.ep import ExpertParallelMLP
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU path for the sub1 kernels")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    d_model, d_ff, n_experts, n_tokens = workload_dims(args)
+    assert n_experts % world == 0 and n_tokens % world == 0
+    e_local, t_local = n_experts // world, n_tokens // world
+    lib = _lib.load()
+
+    t_setup = time.perf_counter()
+    store = synth.build_store(d_model, d_ff, list(range(rank * e_local, (rank + 1) * e_local)), SEED, dev)
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t_setup
+
+    g = torch.Generator().manual_seed(SEED * 31 + 5)
+    router_weight = (torch.randn(n_experts, d_model, generator=g) / d_model ** 0.5).bfloat16().float()
+    hidden_all = synth.tokens(n_tokens, d_model, SEED)
+    hidden_host = hidden_all[rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
+    out_host = torch.empty_like(hidden_host).pin_memory()
+    hidden_dev = hidden_host.to(dev)
+    if world > 1:
+        layer = ExpertParallelMLP(router_weight, store, n_experts, expert_capacity=1024)
+        step = lambda h: layer(h, seq_len=t_local)[0]  # noqa: E731
+    else:
+        layer = sub1.FasterMLP(router_weight, store, expert_capacity=1024)
+        step = lambda h: layer(h.unsqueeze(0))[0].squeeze(0)  # noqa: E731
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        ms = torch.tensor([start.elapsed_time(end)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # warm-up (also builds the per-device sparse table and sizes the allocator's pools)
+    for _ in range(max(args.warmup, 3)):
+        step(hidden_dev)
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.qmoe_launch_count()
+    lib.qmoe_profile_enable(1)
+    ms_total = timed(lambda: step(hidden_dev), args.steps)
+    lib.qmoe_profile_enable(0)
+    launches = (lib.qmoe_launch_count() - launches0) // max(args.steps, 1)
+    import ctypes
+    wi_ms, wo_ms, n_calls = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
+    _lib.check(lib.qmoe_profile_read(ctypes.byref(wi_ms), ctypes.byref(wo_ms), ctypes.byref(n_calls)))
+
+    def e2e_step():
+        hidden_dev.copy_(hidden_host, non_blocking=True)
+        out_host.copy_(step(hidden_dev), non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # algorithmic bytes of the grouped kernel on rank 0: matrices of experts that received tokens
+    logits = hidden_all.to(dev).float() @ router_weight.to(dev).t()
+    choice, _ = sub1.route_top1(logits.contiguous())
+    counts = torch.bincount(choice.long(), minlength=n_experts)[rank * e_local:(rank + 1) * e_local].cpu().tolist()
+    bytes_wi = bytes_wo = 0
+    active = 0
+    for e, c in enumerate(counts):
+        if c > 0:
+            active += 1
+            bytes_wi += store.matrix_bytes(2 * e) + 2 * c * (d_model + d_ff)
+            bytes_wo += store.matrix_bytes(2 * e + 1) + 2 * c * (d_model + d_ff)
+
+    if rank == 0:
+        peak, peak_kind = measured_hbm_peak()
+        calls = max(n_calls.value, 1)
+        kernel_ms = (wi_ms.value + wo_ms.value) / (2 * calls)          # average launch of k_matmul_grouped
+        alg_bytes = (bytes_wi + bytes_wo) / 2                          # average algorithmic bytes per launch
+        achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9 if kernel_ms > 0 else 0.0
+        ratio = recorded_traffic_ratio()
+        line = {
+            "metric": METRIC, "value": n_tokens * args.steps / (ms_total * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded ternary experts P(0)=0.90 packed by the GPU encoder; N(0,1) tokens; random router)",
+            "config": {
+                "workload": args.workload, "d_model": d_model, "d_ff": d_ff, "experts": n_experts,
+                "tokens": n_tokens, "parallelism": f"ep{world}", "experts_per_gpu": e_local,
+                "compressed_bytes_per_gpu": store.compressed_bytes, "active_experts_rank0": active,
+                "l2": f"inputs larger than L2 ({(bytes_wi + bytes_wo) / 1e6:.0f} MB of compressed experts "
+                      "streamed per GPU per step)",
+                "setup_s": round(setup_s, 1),
+            },
+            "e2e": {"value": n_tokens * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": n_tokens * d_model * 2, "d2h_bytes_per_step": n_tokens * d_model * 2},
+            "gpu_launches": int(launches),
+            "roofline": {
+                "kernel": "k_matmul_grouped (wi and wo launches)", "bound": "hbm", "achieved": achieved,
+                "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": kernel_ms,
+                "wi_ms": wi_ms.value / calls, "wo_ms": wo_ms.value / calls,
+                "traffic": None if ratio is None else ratio * alg_bytes,
+            },
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args, d_model, d_ff, n_experts)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -164,6 +164,17 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
                      const void *prob_dev, void *out_dev, int n_tokens, int d_model, int device,
                      void *stream);
 
+/* Number of kernels this library has launched in the calling process (all devices, all entry points). */
+int64_t qmoe_launch_count(void);
+
+/* Optional timing of the two grouped launches inside qmoe_moe_grouped_ffn, for roofline reports.
+ * qmoe_profile_enable(1) makes every later qmoe_moe_grouped_ffn call record CUDA events around its
+ * wi launch and its wo launch on the call's stream (at most 256 calls are kept; later ones are not
+ * recorded).  qmoe_profile_read synchronises on the recorded events, returns the summed durations in
+ * milliseconds and the number of recorded calls, and clears the record. */
+int qmoe_profile_enable(int on);
+int qmoe_profile_read(float *wi_ms, float *wo_ms, int *n_calls);
+
 /* Frees every per-device cache the library holds (derived decoder tables keyed by the dec pointer).
  * Call it after overwriting a dec tensor in place, and before unloading. */
 int qmoe_sub1_release(int device);

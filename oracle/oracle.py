@@ -65,6 +65,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_matvec.restype = I
         L.oracle_expert_ffn.argtypes = [P] * 10 + [I, I, I]
         L.oracle_expert_ffn.restype = I
+        L.oracle_synth_ternary.argtypes = [P, ctypes.c_int64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_float]
+        L.oracle_synth_ternary.restype = None
         L.oracle_num_threads.argtypes = []
         L.oracle_num_threads.restype = I
         _lib = L
@@ -151,6 +153,13 @@ def expert_ffn(dec, wi, wo, x_bits, d_model: int, d_ff: int) -> np.ndarray:
     if rc != 0:
         raise ValueError("code stream does not tile the rows exactly")
     return y
+
+
+def synth_ternary(count: int, seed: int, first_index: int, p_zero: float) -> np.ndarray:
+    """Seeded synthetic symbols uint8[count]; same stream as the GPU generator of the benchmark."""
+    sym = np.empty(count, dtype=np.uint8)
+    lib().oracle_synth_ternary(_p(sym), count, seed & ((1 << 64) - 1), first_index, p_zero)
+    return sym
 
 
 def num_threads() -> int:

@@ -301,6 +301,29 @@ int oracle_expert_ffn(const int32_t *dec,
   return 0;
 }
 
+/* CPU twin of the benchmark's seeded symbol generator (splitmix64 of (seed, index / 4) gives four
+ * 16-bit uniforms; u < t0 -> 0, the rest split evenly between 1 and 2).  Not part of the reference:
+ * it only lets the CPU baseline build the same synthetic experts without a GPU. */
+static inline uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+void oracle_synth_ternary(uint8_t *sym, int64_t count, uint64_t seed, uint64_t first_index, float p_zero) {
+  const uint32_t t0 = (uint32_t)((double)p_zero * 65536.0 + 0.5);
+  const uint32_t t1 = t0 + (65536u - (t0 > 65536u ? 65536u : t0)) / 2u;
+  const uint64_t base = seed * 0xD1342543DE82EF95ull;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < count; i++) {
+    const uint64_t idx = first_index + (uint64_t)i;
+    const uint64_t h = splitmix64(base + (idx >> 2));
+    const uint32_t u = (uint32_t)(h >> (16 * (idx & 3))) & 0xffffu;
+    sym[i] = u < t0 ? 0 : (u < t1 ? 1 : 2);
+  }
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -73,6 +73,9 @@ SIGNATURES = {
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "qmoe_launch_count": (_L, []),
+    "qmoe_profile_enable": (_I, [_I]),
+    "qmoe_profile_read": (_I, [_P, _P, _P]),
     "qmoe_sub1_release": (_I, [_I]),
 }
 

@@ -2,6 +2,7 @@
 // construction.  Kernels live in sub1_matmul.cu, sub1_pack.cu and moe_route.cu.
 #include "common.cuh"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -26,6 +27,35 @@ void set_error(const char *fmt, ...) {
 int cuda_fail(cudaError_t e, const char *what) {
   set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
   return QMOE_ERR_CUDA;
+}
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ---- optional event timing of the grouped launches ----------------------------------------------
+static std::mutex g_profile_mutex;
+static bool g_profile_on = false;
+struct ProfileCall {
+  cudaEvent_t ev[4];
+  int device;
+};
+static std::vector<ProfileCall> g_profile_calls;
+constexpr size_t kMaxProfileCalls = 256;
+
+bool profile_begin(int device, cudaEvent_t **events) {
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  if (!g_profile_on || g_profile_calls.size() >= kMaxProfileCalls) return false;
+  ProfileCall c{};
+  c.device = device;
+  for (int i = 0; i < 4; i++) {
+    if (cudaEventCreate(&c.ev[i]) != cudaSuccess) {
+      for (int j = 0; j < i; j++) cudaEventDestroy(c.ev[j]);
+      return false;
+    }
+  }
+  g_profile_calls.push_back(c);
+  *events = g_profile_calls.back().ev;
+  return true;
 }
 
 int sm_count(int device) {
@@ -424,6 +454,42 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   return launch_combine(ys_dev, hidden_dev, slot_dev, prob_dev, out_dev, n_tokens, d_model, as_stream(stream));
+}
+
+int64_t qmoe_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+
+int qmoe_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  g_profile_on = on != 0;
+  if (g_profile_on) g_profile_calls.reserve(kMaxProfileCalls);  // event pointers handed out stay valid
+  return QMOE_OK;
+}
+
+int qmoe_profile_read(float *wi_ms, float *wo_ms, int *n_calls) {
+  QMOE_REQUIRE(wi_ms && wo_ms && n_calls, "null output pointer");
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  float wi = 0.f, wo = 0.f;
+  int n = 0;
+  int rc = QMOE_OK;
+  for (auto &c : g_profile_calls) {
+    float a = 0.f, b = 0.f;
+    cudaError_t e = cudaEventSynchronize(c.ev[3]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&a, c.ev[0], c.ev[1]);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&b, c.ev[2], c.ev[3]);
+    if (e == cudaSuccess) {
+      wi += a;
+      wo += b;
+      n++;
+    } else {
+      rc = cuda_fail(e, "profile events");
+    }
+    for (int i = 0; i < 4; i++) cudaEventDestroy(c.ev[i]);
+  }
+  g_profile_calls.clear();
+  *wi_ms = wi;
+  *wo_ms = wo;
+  *n_calls = n;
+  return rc;
 }
 
 int qmoe_sub1_release(int device) {

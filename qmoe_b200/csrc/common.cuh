@@ -42,6 +42,18 @@ struct DeviceGuard {
 
 int sm_count(int device);
 
+// Event timing of the grouped launches (qmoe_profile_enable): returns true and four fresh events
+// when the next grouped call should be timed.
+bool profile_begin(int device, cudaEvent_t **events);
+
+// Every kernel launch of the library goes through QMOE_LAUNCH so that qmoe_launch_count() is exact.
+void count_launch();
+#define QMOE_LAUNCH(kernel, grid, block, smem, stream, ...) \
+  do {                                                      \
+    kernel<<<grid, block, smem, stream>>>(__VA_ARGS__);     \
+    qmoe::count_launch();                                   \
+  } while (0)
+
 // ---- derived decoder table -------------------------------------------------------------------
 // The reference table `dec` (sub1.py:60-72) spends 8 bytes per code on a dense list of 2-bit
 // digits.  Every entry of the standard dictionary has at most three non-zero digits, so the

@@ -188,8 +188,7 @@ int launch_route(const float *logits, int32_t *choice, void *prob, int n_tokens,
   if (n_tokens == 0) return QMOE_OK;
   const int threads = 128;
   const long long total = (long long)n_tokens * 32;
-  k_route_choose<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
-      logits, choice, reinterpret_cast<__nv_bfloat16 *>(prob), n_tokens, n_experts);
+  QMOE_LAUNCH(k_route_choose, (unsigned)((total + threads - 1) / threads), threads, 0, stream, logits, choice, reinterpret_cast<__nv_bfloat16 *>(prob), n_tokens, n_experts);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -200,15 +199,15 @@ int launch_rank(const int32_t *choice, int32_t *bucket, int32_t *rank, int32_t *
   if (n_tokens == 0) return QMOE_OK;
   const int threads = 256;
   const int blocks = (n_tokens + threads - 1) / threads;
-  k_capacity<<<blocks, threads, 0, stream>>>(choice, bucket, n_tokens, n_buckets, seq_len, capacity);
+  QMOE_LAUNCH(k_capacity, blocks, threads, 0, stream, choice, bucket, n_tokens, n_buckets, seq_len, capacity);
   QMOE_CUDA(cudaGetLastError());
-  k_rank<<<blocks, threads, 0, stream>>>(bucket, rank, counts, n_tokens);
+  QMOE_LAUNCH(k_rank, blocks, threads, 0, stream, bucket, rank, counts, n_tokens);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
 
 int launch_scan(const int32_t *counts, int32_t *offsets, int n, cudaStream_t stream) {
-  k_exclusive_scan<<<1, 1024, 0, stream>>>(counts, offsets, n);
+  QMOE_LAUNCH(k_exclusive_scan, 1, 1024, 0, stream, counts, offsets, n);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -217,10 +216,7 @@ int launch_permute(const int32_t *bucket, const int32_t *rank, const int32_t *of
                    const void *hidden, void *xs, int n_tokens, int d_model, int64_t hidden_stride,
                    int64_t xs_stride, cudaStream_t stream) {
   if (n_tokens == 0) return QMOE_OK;
-  k_permute<<<n_tokens, 128, 0, stream>>>(bucket, rank, offsets, slot,
-                                          reinterpret_cast<const __nv_bfloat16 *>(hidden),
-                                          reinterpret_cast<__nv_bfloat16 *>(xs), d_model, hidden_stride,
-                                          xs_stride);
+  QMOE_LAUNCH(k_permute, n_tokens, 128, 0, stream, bucket, rank, offsets, slot, reinterpret_cast<const __nv_bfloat16 *>(hidden), reinterpret_cast<__nv_bfloat16 *>(xs), d_model, hidden_stride, xs_stride);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -228,19 +224,14 @@ int launch_permute(const int32_t *bucket, const int32_t *rank, const int32_t *of
 int launch_unpermute(const void *ys, const int32_t *slot, void *out, int n_tokens, int d_model,
                      int64_t ys_stride, int64_t out_stride, cudaStream_t stream) {
   if (n_tokens == 0) return QMOE_OK;
-  k_unpermute<<<n_tokens, 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(ys), slot,
-                                            reinterpret_cast<__nv_bfloat16 *>(out), d_model, ys_stride,
-                                            out_stride);
+  QMOE_LAUNCH(k_unpermute, n_tokens, 128, 0, stream, reinterpret_cast<const __nv_bfloat16 *>(ys), slot, reinterpret_cast<__nv_bfloat16 *>(out), d_model, ys_stride, out_stride);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
 
 int launch_combine(const void *ys, const void *hidden, const int32_t *slot, const void *prob, void *out,
                    int n_tokens, int d_model, cudaStream_t stream) {
-  k_combine<<<n_tokens, 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16 *>(ys),
-                                          reinterpret_cast<const __nv_bfloat16 *>(hidden), slot,
-                                          reinterpret_cast<const __nv_bfloat16 *>(prob),
-                                          reinterpret_cast<__nv_bfloat16 *>(out), d_model);
+  QMOE_LAUNCH(k_combine, n_tokens, 128, 0, stream, reinterpret_cast<const __nv_bfloat16 *>(ys), reinterpret_cast<const __nv_bfloat16 *>(hidden), slot, reinterpret_cast<const __nv_bfloat16 *>(prob), reinterpret_cast<__nv_bfloat16 *>(out), d_model);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

@@ -303,9 +303,9 @@ int launch_matmul_uniform(const SparseTable &tab, const int32_t *dec, const uint
   const size_t smem = smem_bytes(width, group);
   const dim3 grid((unsigned)(a.chunks * groups));
   if (tab.conforming)
-    k_matmul_uniform<false><<<grid, kRowsPerItem, smem, stream>>>(a);
+    QMOE_LAUNCH(k_matmul_uniform<false>, grid, kRowsPerItem, smem, stream, a);
   else
-    k_matmul_uniform<true><<<grid, kRowsPerItem, smem, stream>>>(a);
+    QMOE_LAUNCH(k_matmul_uniform<true>, grid, kRowsPerItem, smem, stream, a);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -318,18 +318,16 @@ int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *co
   const int threads = 128;
   const int blocks = (height + threads - 1) / threads;
   if (tab.conforming)
-    k_decode<false><<<blocks, threads, 0, stream>>>(tab.entries, dec, codes, row_off, sym, status, height,
-                                                    width, n_codes);
+    QMOE_LAUNCH(k_decode<false>, blocks, threads, 0, stream, tab.entries, dec, codes, row_off, sym, status, height, width, n_codes);
   else
-    k_decode<true><<<blocks, threads, 0, stream>>>(tab.entries, dec, codes, row_off, sym, status, height,
-                                                   width, n_codes);
+    QMOE_LAUNCH(k_decode<true>, blocks, threads, 0, stream, tab.entries, dec, codes, row_off, sym, status, height, width, n_codes);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
 
 int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cudaStream_t stream) {
   QMOE_CUDA(cudaMemsetAsync(nonconforming, 0, sizeof(int), stream));
-  k_build_table<<<QMOE_DICT_COUNT / 256, 256, 0, stream>>>(dec, tab, nonconforming);
+  QMOE_LAUNCH(k_build_table, QMOE_DICT_COUNT / 256, 256, 0, stream, dec, tab, nonconforming);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -417,8 +415,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   int *header = reinterpret_cast<int *>(work);
   int4 *items_wi = reinterpret_cast<int4 *>(reinterpret_cast<char *>(work) + 64);
   int4 *items_wo = items_wi + (size_t)max_slots * chunks_wi;
-  k_build_work<<<1, 1024, 0, stream>>>(offsets, n_experts, d_model, d_ff, rpc_wi, chunks_wi, rpc_wo,
-                                       chunks_wo, max_slots, header, items_wi, items_wo);
+  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, d_model, d_ff, rpc_wi, chunks_wi, rpc_wo, chunks_wo, max_slots, header, items_wi, items_wo);
   QMOE_CUDA(cudaGetLastError());
 
   MatmulArgs a{};
@@ -429,6 +426,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
   a.descs = descs;
   const int sms = sm_count(device);
+  cudaEvent_t *events = nullptr;
+  const bool timed = profile_begin(device, &events);
 
   for (int phase = 0; phase < 2; phase++) {
     const int width = phase == 0 ? d_model : d_ff;
@@ -450,11 +449,13 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     long long grid = (long long)sms * per_sm;
     grid = grid > max_items ? max_items : grid;
     grid = grid < 1 ? 1 : grid;
+    if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
     if (tab.conforming)
-      k_matmul_grouped<false><<<(unsigned)grid, kRowsPerItem, smem, stream>>>(a);
+      QMOE_LAUNCH(k_matmul_grouped<false>, (unsigned)grid, kRowsPerItem, smem, stream, a);
     else
-      k_matmul_grouped<true><<<(unsigned)grid, kRowsPerItem, smem, stream>>>(a);
+      QMOE_LAUNCH(k_matmul_grouped<true>, (unsigned)grid, kRowsPerItem, smem, stream, a);
     QMOE_CUDA(cudaGetLastError());
+    if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }
   return QMOE_OK;
 }

@@ -178,10 +178,9 @@ __global__ void k_synth_ternary(uint8_t *__restrict__ sym, long long count, uint
 int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
                         cudaStream_t stream) {
   const int threads = 64;
-  k_pack_prepare<<<(height + threads - 1) / threads, threads, 0, stream>>>(trie, w_tern, row_off + 1, height,
-                                                                           width);
+  QMOE_LAUNCH(k_pack_prepare, (height + threads - 1) / threads, threads, 0, stream, trie, w_tern, row_off + 1, height, width);
   QMOE_CUDA(cudaGetLastError());
-  k_offsets_from_lengths<<<1, 1024, 0, stream>>>(row_off, height);
+  QMOE_LAUNCH(k_offsets_from_lengths, 1, 1024, 0, stream, row_off, height);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -190,8 +189,7 @@ int launch_pack_emit(const int32_t *w_tern, const int32_t *row_off, uint16_t *w_
                      cudaStream_t stream) {
   const int threads = 256;
   const long long total = (long long)height * 32;
-  k_pack_emit<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(w_tern, row_off, w_comp,
-                                                                                  height, width);
+  QMOE_LAUNCH(k_pack_emit, (unsigned)((total + threads - 1) / threads), threads, 0, stream, w_tern, row_off, w_comp, height, width);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -200,8 +198,7 @@ int launch_pack_u8_count(const int32_t *trie, const uint8_t *sym, uint16_t *code
                          int n_mat, int height, int width, cudaStream_t stream) {
   const long long n_rows = (long long)n_mat * height;
   const int threads = 64;
-  k_pack_u8_count<<<(unsigned)((n_rows + threads - 1) / threads), threads, 0, stream>>>(trie, sym, codes_tmp,
-                                                                                       row_len, n_rows, width);
+  QMOE_LAUNCH(k_pack_u8_count, (unsigned)((n_rows + threads - 1) / threads), threads, 0, stream, trie, sym, codes_tmp, row_len, n_rows, width);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -211,8 +208,7 @@ int launch_pack_u8_gather(const uint16_t *codes_tmp, const int32_t *row_off, con
   const long long n_rows = (long long)n_mat * height;
   const int threads = 256;
   const long long total = n_rows * 32;
-  k_pack_u8_gather<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
-      codes_tmp, row_off, mat_base, out, n_rows, height, width);
+  QMOE_LAUNCH(k_pack_u8_gather, (unsigned)((total + threads - 1) / threads), threads, 0, stream, codes_tmp, row_off, mat_base, out, n_rows, height, width);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
@@ -227,8 +223,7 @@ int launch_synth_ternary(uint8_t *sym, int64_t count, uint64_t seed, uint64_t fi
   const uint32_t t1 = t0 + (65536u - (t0 > 65536u ? 65536u : t0)) / 2u;
   const long long groups = (count + 3) / 4;
   const int threads = 256;
-  k_synth_ternary<<<(unsigned)((groups + threads - 1) / threads), threads, 0, stream>>>(
-      sym, count, seed, first_index, t0, t1);
+  QMOE_LAUNCH(k_synth_ternary, (unsigned)((groups + threads - 1) / threads), threads, 0, stream, sym, count, seed, first_index, t0, t1);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

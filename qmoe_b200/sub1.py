@@ -204,6 +204,33 @@ def _s(dev: torch.device) -> int:
     return int(torch.cuda.current_stream(dev).cuda_stream)
 
 
+_MM_OUT_DTYPE_OK: Optional[bool] = None
+
+
+class RouterClassifier:
+    """The router's bias-free classifier, evaluated in fp32 as the Switch router does (its
+    ``hidden_states.to(float32)`` + fp32 classifier).  When every weight is exactly representable in
+    bf16 (checkpoints store the classifier in bf16) the product of bf16 inputs with fp32
+    accumulation gives the same logits up to summation order, so the bf16 tensor-core GEMM with an
+    fp32 result is used; otherwise a plain fp32 matmul."""
+
+    def __init__(self, weight: torch.Tensor, device):
+        self.w32 = weight.to(device, torch.float32).contiguous()
+        w16 = self.w32.bfloat16()
+        self.w16 = w16.contiguous() if bool((w16.float() == self.w32).all()) else None
+
+    def __call__(self, hidden_bf16: torch.Tensor) -> torch.Tensor:
+        global _MM_OUT_DTYPE_OK
+        if self.w16 is not None and hidden_bf16.dtype == torch.bfloat16 and _MM_OUT_DTYPE_OK is not False:
+            try:
+                out = torch.mm(hidden_bf16, self.w16.t(), out_dtype=torch.float32)
+                _MM_OUT_DTYPE_OK = True
+                return out
+            except (TypeError, RuntimeError):
+                _MM_OUT_DTYPE_OK = False
+        return hidden_bf16.float() @ self.w32.t()
+
+
 def route_top1(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """(choice int32[n], prob bf16[n]) from fp32 logits ``[n, E]``."""
     assert logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
@@ -299,11 +326,10 @@ class FasterMLP(nn.Module):
         super().__init__()
         self.store = store
         self.expert_capacity = int(expert_capacity)
-        self.router_weight = None if router_weight is None else router_weight.to(store.device, torch.float32)
+        self.router = None if router_weight is None else RouterClassifier(router_weight, store.device)
 
     def router_logits(self, hidden2d: torch.Tensor) -> torch.Tensor:
-        # The Switch router computes its logits in fp32 from the bf16 hidden states.
-        return hidden2d.float() @ self.router_weight.t()
+        return self.router(hidden2d)
 
     def forward(self, hidden_states: torch.Tensor, router_logits: Optional[torch.Tensor] = None):
         shape = hidden_states.shape

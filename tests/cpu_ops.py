@@ -1,0 +1,71 @@
+"""Torch-CPU re-statement of the device ops the expert-parallel layer calls (route, rank, permute,
+grouped FFN via the oracle, unpermute, combine).  A TEST DOUBLE: it lets world_size-2 gloo ranks
+exercise the exchange logic and index arithmetic of qmoe_b200.ep without a GPU."""
+import torch
+
+from util import reference_router
+
+
+class CpuStore:
+    def __init__(self, experts):
+        self.experts = experts
+        self.n_experts = len(experts)
+        self.d_model, self.d_ff = experts[0].d_model, experts[0].d_ff
+        self.device = torch.device("cpu")
+
+
+def route_top1(logits):
+    mask, probs = reference_router(logits.unsqueeze(0), capacity=10 ** 9)
+    return mask[0].argmax(-1).to(torch.int32), probs.reshape(-1)
+
+
+def rank_buckets(choice, n_buckets, seq_len, capacity):
+    n = choice.numel()
+    bucket = torch.full((n,), -1, dtype=torch.int32)
+    rank = torch.zeros(n, dtype=torch.int32)
+    counts = torch.zeros(n_buckets, dtype=torch.int32)
+    seen_seq = {}
+    for t in range(n):
+        c = int(choice[t])
+        if c < 0 or c >= n_buckets:
+            continue
+        key = (t // seq_len, c)
+        before = seen_seq.get(key, 0)
+        seen_seq[key] = before + 1
+        if before < capacity:
+            bucket[t] = c
+            rank[t] = counts[c]
+            counts[c] += 1
+    offsets = torch.zeros(n_buckets + 1, dtype=torch.int32)
+    offsets[1:] = torch.cumsum(counts, 0)
+    return bucket, rank, counts, offsets
+
+
+def permute_rows(bucket, rank, offsets, hidden, xs):
+    slot = torch.where(bucket >= 0, offsets[bucket.clamp(min=0).long()] + rank, torch.full_like(rank, -1))
+    for t in range(hidden.shape[0]):
+        if slot[t] >= 0:
+            xs[int(slot[t])] = hidden[t]
+    return slot.to(torch.int32)
+
+
+def unpermute_rows(ys, slot, out):
+    for t in range(out.shape[0]):
+        out[t] = ys[int(slot[t])] if slot[t] >= 0 else 0
+
+
+def grouped_ffn(store, offsets, xs, max_slots):
+    ys = torch.zeros((max_slots, store.d_model), dtype=torch.bfloat16)
+    for e in range(store.n_experts):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            ys[a:b] = store.experts[e].oracle_ffn(xs[a:b].contiguous())
+    return ys
+
+
+def combine(ys, hidden, slot, prob):
+    out = torch.empty_like(hidden)
+    for t in range(hidden.shape[0]):
+        src = ys[int(slot[t])] if slot[t] >= 0 else hidden[t]
+        out[t] = (prob[t].float() * src.float()).bfloat16()
+    return out

@@ -1,0 +1,96 @@
+"""GPU parity of the top-1 MoE layer (route, group, grouped expert FFN, combine) against the
+reference's FasterMLP semantics evaluated on the CPU with the oracle as expert FFN."""
+import numpy as np
+import pytest
+import torch
+
+from qmoe_b200 import sub1, synth
+from util import Expert, reference_moe, reference_router, rel_err, store_from_experts
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.fixture(scope="module")
+def small_layer(dev):
+    d_model, d_ff, n_exp = 128, 320, 8
+    experts = [Expert(d_model, d_ff, seed=0, expert_id=e) for e in range(n_exp)]
+    return experts, store_from_experts(experts, dev)
+
+
+def test_route_matches_switch_router(dev):
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(3, 40, 16, generator=g)
+    logits[0, 0, :] = 0.0                       # exact tie: first index wins
+    logits[0, 1, 3] = logits[0, 1, 9] = 5.0     # two-way tie
+    choice, prob = sub1.route_top1(logits.reshape(-1, 16).to(dev).contiguous())
+    mask, probs = reference_router(logits, capacity=10 ** 6)
+    assert torch.equal(choice.cpu().long(), mask.argmax(-1).reshape(-1))
+    assert torch.equal(prob.cpu(), probs.reshape(-1))
+    for cap in (1, 2, 5):
+        mask, _ = reference_router(logits, capacity=cap)
+        bucket, rank, counts, offsets = sub1.rank_buckets(choice, 16, seq_len=40, capacity=cap)
+        kept = mask.sum(-1).reshape(-1).bool()
+        assert torch.equal(bucket.cpu() >= 0, kept)
+        assert torch.equal(counts.cpu().long(), mask.sum(dim=(0, 1)))
+        assert offsets.cpu().tolist() == [0] + torch.cumsum(mask.sum(dim=(0, 1)), 0).tolist()
+        # ranks are stable: token order inside every bucket
+        b, r = bucket.cpu().numpy(), rank.cpu().numpy()
+        for e in range(16):
+            assert r[b == e].tolist() == list(range(int((b == e).sum())))
+
+
+@pytest.mark.parametrize("batch,seq,capacity", [(1, 24, 1024), (2, 16, 1024), (2, 16, 2), (1, 1, 1024)])
+def test_moe_layer_matches_reference(dev, small_layer, batch, seq, capacity):
+    experts, store = small_layer
+    hidden = synth.tokens(batch * seq, store.d_model, seed=batch * 100 + seq).reshape(batch, seq, -1)
+    logits = synth.router_logits(batch * seq, store.n_experts, seed=seq).reshape(batch, seq, -1)
+    layer = sub1.FasterMLP(None, store, expert_capacity=capacity)
+    out, (lg, index) = layer(hidden.to(dev), router_logits=logits.to(dev))
+    ref = reference_moe(hidden, logits, experts, capacity)
+    assert out.shape == hidden.shape and out.dtype == torch.bfloat16
+    assert rel_err(out, ref) <= TOL
+    mask, _ = reference_router(logits, capacity)
+    assert torch.equal(index.cpu(), mask.argmax(-1))
+
+
+def test_moe_layer_skewed_router_and_idle_experts(dev, small_layer):
+    experts, store = small_layer
+    n = 40
+    hidden = synth.tokens(n, store.d_model, seed=5).reshape(1, n, -1)
+    logits = synth.router_logits(n, store.n_experts, seed=6, hot_experts=2, hot_fraction=0.75).reshape(1, n, -1)
+    logits[..., 5:] -= 30.0                     # experts 5..7 receive nothing
+    out, _ = sub1.FasterMLP(None, store)(hidden.to(dev), router_logits=logits.to(dev))
+    assert rel_err(out, reference_moe(hidden, logits, experts, 1024)) <= TOL
+
+
+def test_moe_layer_with_router_weight(dev, small_layer):
+    experts, store = small_layer
+    g = torch.Generator().manual_seed(3)
+    wr = torch.randn(store.n_experts, store.d_model, generator=g) * 0.5
+    hidden = synth.tokens(12, store.d_model, seed=9).reshape(1, 12, -1)
+    layer = sub1.FasterMLP(wr, store)
+    out, (lg, _) = layer(hidden.to(dev))
+    logits = hidden.float() @ wr.t()
+    assert rel_err(lg, logits) <= 1e-3
+    assert rel_err(out, reference_moe(hidden, lg.cpu(), experts, 1024)) <= TOL
+
+
+def test_grouped_ffn_direct_with_empty_and_large_groups(dev, small_layer):
+    """offsets with empty experts and a 9-token expert (three token groups)."""
+    experts, store = small_layer
+    counts = [0, 9, 1, 0, 4, 0, 2, 0]
+    n = sum(counts)
+    xs = synth.tokens(n, store.d_model, seed=2)
+    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+    ys = sub1.grouped_ffn(store, offsets, xs.to(dev), n + 3)        # max_slots larger than used
+    pos = 0
+    for e, c in enumerate(counts):
+        if c:
+            assert rel_err(ys[pos:pos + c], experts[e].oracle_ffn(xs[pos:pos + c])) <= TOL
+        pos += c
