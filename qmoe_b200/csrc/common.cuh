@@ -58,15 +58,13 @@ void count_launch();
 // The reference table `dec` (sub1.py:60-72) spends 8 bytes per code on a dense list of 2-bit
 // digits.  Every entry of the standard dictionary has at most three non-zero digits, so the
 // kernels use a 4-byte sparse form built once per device from `dec`:
-//   bits 0..4    number of weights the code covers (2 * length in pairs, 2..28); 0 marks an entry
-//                that does not fit the sparse form (more than three non-zeros or a malformed word)
-//                and is decoded from `dec` digit by digit instead
-//   for k = 0..2, field at bit 5 + 9k:
-//     bits 0..6  4 * position of the k-th non-zero inside the code (a byte offset into fp32 x)
-//     bit  7     digit == 1 (row min)
-//     bit  8     digit == 2 (row max)
-//   absent non-zeros have an all-zero field.
-__host__ __device__ constexpr int kEntryFieldShift(int k) { return 5 + 9 * k; }
+//   byte 0   bits 0..3  length of the code in pairs (1..14; 0 in the null entry)
+//            bits 4..6  bit 4+k set: the k-th non-zero is digit 2 (row max); clear: digit 1 (row min)
+//            bit 7      the entry does not fit this form (more than three non-zeros or a malformed
+//                       word) and is decoded from `dec` digit by digit instead
+//   byte 1+k position (0..27) of the k-th non-zero inside the code, or 0x80 when there is none
+constexpr uint32_t kEntryNull = 0x80808000u;   // covers nothing, contributes nothing
+constexpr uint32_t kEntryDense = 0x80808080u;  // "decode me from dec"
 
 struct SparseTable {
   const uint32_t *entries = nullptr;  // uint32[65536] on the device

@@ -16,71 +16,122 @@
 #include "common.cuh"
 #include "sub1_walk.cuh"
 
+#include <type_traits>
+
 namespace qmoe {
 
-constexpr int kRowsPerItem = 256;  // threads per CTA == rows per work item
-constexpr int kMaxGroup = 4;       // tokens decoded together
-constexpr int kPad = 32;           // zero entries after x: a code spans at most 28 positions
+constexpr int kRowsPerItem = 256;     // single-matrix kernel: threads per CTA == rows per work item
+constexpr int kGroupedThreads = 1024; // grouped kernel: one persistent CTA per SM, rows per work item
+constexpr int kMaxGroup = 4;          // tokens decoded together
+constexpr int kPad = 32;              // zero entries after x: a code spans at most 28 positions
 
-static inline int rows_per_chunk(int height) {
-  const int chunks = (height + kRowsPerItem - 1) / kRowsPerItem;
+static inline int rows_per_chunk(int height, int rows_per_item) {
+  const int chunks = (height + rows_per_item - 1) / rows_per_item;
   int rpc = (height + chunks - 1) / chunks;
   rpc = (rpc + 31) / 32 * 32;
   return rpc;
 }
-static inline int chunk_count(int height) {
-  const int rpc = rows_per_chunk(height);
+static inline int chunk_count(int height, int rows_per_item) {
+  const int rpc = rows_per_chunk(height, rows_per_item);
   return (height + rpc - 1) / rpc;
 }
 
 // ---- sinks ------------------------------------------------------------------------------------
-template <int T> struct VecT;
-template <> struct VecT<1> { using type = float; };
-template <> struct VecT<2> { using type = float2; };
-template <> struct VecT<4> { using type = float4; };
+// Shared loads that execute only where the non-zero exists; absent lanes keep zeros (and cost no
+// shared-memory bandwidth), so the adds that follow need no presence test.
+__device__ __forceinline__ void lds_pred_b16(uint32_t &v, uint32_t addr, uint32_t pos_byte) {
+  asm("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %2, 128;\n\tmov.b32 %0, 0;\n\t"
+      "@p ld.shared.u16 %0, [%1];\n\t}" : "=r"(v) : "r"(addr), "r"(pos_byte));
+}
+__device__ __forceinline__ void lds_pred_b32(uint32_t &v, uint32_t addr, uint32_t pos_byte) {
+  asm("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %2, 128;\n\tmov.b32 %0, 0;\n\t"
+      "@p ld.shared.b32 %0, [%1];\n\t}" : "=r"(v) : "r"(addr), "r"(pos_byte));
+}
+__device__ __forceinline__ void lds_pred_b64(uint32_t &v0, uint32_t &v1, uint32_t addr, uint32_t pos_byte) {
+  asm("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %3, 128;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
+      "@p ld.shared.v2.b32 {%0, %1}, [%2];\n\t}" : "=r"(v0), "=r"(v1) : "r"(addr), "r"(pos_byte));
+}
+__device__ __forceinline__ void lds_pred_b128(uint32_t (&v)[4], uint32_t addr, uint32_t pos_byte) {
+  asm("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %5, 128;\n\tmov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\t"
+      "mov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t@p ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr), "r"(pos_byte));
+}
 
-template <int T>
+constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v / 2); }
+
+// Accumulates, for T tokens, s1 = sum of x over digit-1 positions and s2 = sum over digit-2
+// positions of a row.  x lives in shared memory as [position][T], fp32 (F32) or bf16.
+template <int T, bool F32>
 struct MatSink {
-  const char *xs;  // fp32 activations in shared memory, [position][T] interleaved
+  using elem = typename std::conditional<F32, float, __nv_bfloat16>::type;
+  static constexpr int kShift = ilog2(T * (F32 ? 4 : 2));  // log2(bytes per position)
+  static __device__ __forceinline__ elem stage(__nv_bfloat16 v) {
+    if constexpr (F32) return __bfloat162float(v);
+    else return v;
+  }
+  uint32_t xs_addr;  // shared-space byte address of x
   float s1[T], s2[T];
 
-  __device__ __forceinline__ void add(uint32_t f, const char *p) {
-    if (f & 0x180u) {
-      const typename VecT<T>::type v = *reinterpret_cast<const typename VecT<T>::type *>(p);
-      const float *vf = reinterpret_cast<const float *>(&v);
-      if (f & 0x80u) {
+  __device__ __forceinline__ void load(float (&vf)[T], uint32_t addr, uint32_t pos_byte) {
+    if constexpr (F32) {
+      uint32_t v[4] = {0u, 0u, 0u, 0u};
+      if constexpr (T == 1) lds_pred_b32(v[0], addr, pos_byte);
+      else if constexpr (T == 2) lds_pred_b64(v[0], v[1], addr, pos_byte);
+      else lds_pred_b128(v, addr, pos_byte);
 #pragma unroll
-        for (int t = 0; t < T; t++) s1[t] += vf[t];
-      } else {
-#pragma unroll
-        for (int t = 0; t < T; t++) s2[t] += vf[t];
+      for (int t = 0; t < T; t++) vf[t] = __uint_as_float(v[t]);
+    } else {
+      uint32_t v0 = 0u, v1 = 0u;
+      if constexpr (T == 1) lds_pred_b16(v0, addr, pos_byte);
+      else if constexpr (T == 2) lds_pred_b32(v0, addr, pos_byte);
+      else lds_pred_b64(v0, v1, addr, pos_byte);
+      vf[0] = __uint_as_float(v0 << 16);
+      if constexpr (T >= 2) vf[1] = __uint_as_float(v0 & 0xffff0000u);
+      if constexpr (T >= 4) {
+        vf[2] = __uint_as_float(v1 << 16);
+        vf[3] = __uint_as_float(v1 & 0xffff0000u);
       }
     }
   }
-  __device__ __forceinline__ void entry(uint32_t e, int pos) {
-    const char *base = xs + (size_t)pos * (4 * T);
+  __device__ __forceinline__ void entry(uint32_t e, uint32_t posb) {
+    const uint32_t base = xs_addr + posb;
 #pragma unroll
     for (int k = 0; k < 3; k++) {
-      const uint32_t f = e >> kEntryFieldShift(k);
-      add(f, base + (f & 0x7cu) * T);
+      const uint32_t o = entry_nz_pos(e, k);
+      float vf[T];
+      load(vf, base + (o << kShift), o);
+      if (e & (0x10u << k)) {
+#pragma unroll
+        for (int t = 0; t < T; t++) s2[t] += vf[t];
+      } else {
+#pragma unroll
+        for (int t = 0; t < T; t++) s1[t] += vf[t];
+      }
     }
   }
   __device__ __forceinline__ void dense(int p, uint32_t digit) {
-    add(digit == 1u ? 0x80u : 0x100u, xs + (size_t)p * (4 * T));
+    float vf[T];
+    load(vf, xs_addr + ((uint32_t)p << kShift), 0u);
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+      if (digit == 1u) s1[t] += vf[t];
+      else s2[t] += vf[t];
+    }
   }
 };
 
 struct SymbolSink {
+  static constexpr int kShift = 0;
   uint8_t *row;  // width bytes, pre-zeroed
   int width;
   __device__ __forceinline__ void put(int p, uint8_t d) {
     if (p < width) row[p] = d;
   }
-  __device__ __forceinline__ void entry(uint32_t e, int pos) {
+  __device__ __forceinline__ void entry(uint32_t e, uint32_t pos) {
 #pragma unroll
     for (int k = 0; k < 3; k++) {
-      const uint32_t f = e >> kEntryFieldShift(k);
-      if (f & 0x180u) put(pos + (int)((f & 0x7cu) >> 2), (f & 0x80u) ? 1 : 2);
+      const uint32_t o = entry_nz_pos(e, k);
+      if (o < 0x80u) put((int)(pos + o), (e & (0x10u << k)) ? 2 : 1);
     }
   }
   __device__ __forceinline__ void dense(int p, uint32_t digit) { put(p, (uint8_t)digit); }
@@ -108,20 +159,21 @@ __device__ __forceinline__ float bf16_round(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-template <int T, bool GENERAL>
+template <int T, bool GENERAL, class SinkT, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
-                                             int nrows, int tok0, int ntok, float *xs) {
+                                             int nrows, int tok0, int ntok, typename SinkT::elem *xs,
+                                             const Lookup &lookup) {
   const int tid = threadIdx.x;
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
 
-  // Stage the token group: xs[c][t] = float(x[tok0 + t][c]), zero beyond the width / token count.
+  // Stage the token group: xs[c][t] = x[tok0 + t][c], zero beyond the width / token count.
   for (int c = tid; c < wlim + kPad; c += blockDim.x) {
 #pragma unroll
     for (int t = 0; t < T; t++) {
-      float v = 0.f;
-      if (c < W && t < ntok) v = __bfloat162float(a.x[(long long)(tok0 + t) * a.x_stride + c]);
-      xs[c * T + t] = v;
+      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+      if (c < W && t < ntok) v = a.x[(long long)(tok0 + t) * a.x_stride + c];
+      xs[c * T + t] = SinkT::stage(v);
     }
   }
   __syncthreads();
@@ -136,11 +188,11 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
     e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
 
-    MatSink<T> sink;
-    sink.xs = reinterpret_cast<const char *>(xs);
+    SinkT sink;
+    sink.xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
 #pragma unroll
     for (int t = 0; t < T; t++) sink.s1[t] = sink.s2[t] = 0.f;
-    walk_row<GENERAL>(codes_al, (int)b + mis, (int)e + mis, a.tab, a.dec, wlim, sink);
+    walk_row<GENERAL>(codes_al, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
 
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     const float mn = __bfloat162float(mm.x), mx = __bfloat162float(mm.y);
@@ -158,41 +210,52 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
   }
 }
 
-template <bool GENERAL>
-__device__ __forceinline__ void dispatch_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
-                                              int nrows, int tok0, int ntok, float *xs) {
-  if (ntok <= 1) process_item<1, GENERAL>(a, d, row0, nrows, tok0, ntok, xs);
-  else if (ntok == 2) process_item<2, GENERAL>(a, d, row0, nrows, tok0, ntok, xs);
-  else process_item<4, GENERAL>(a, d, row0, nrows, tok0, ntok, xs);
-}
-
-// One CTA per (row block, token group) of a single matrix.
+// One CTA per (row block, token group) of a single matrix; the sparse table is read through L1/L2.
 template <bool GENERAL>
 __global__ void __launch_bounds__(kRowsPerItem) k_matmul_uniform(const MatmulArgs a) {
-  extern __shared__ __align__(16) float xs[];
+  extern __shared__ __align__(16) float xs_f32[];
   const int chunk = blockIdx.x % a.chunks;
   const int group = blockIdx.x / a.chunks;
   const int row0 = chunk * a.rpc;
   const int nrows = min(a.rpc, a.single.height - row0);
   const int tok0 = group * kMaxGroup;
   const int ntok = min(kMaxGroup, a.tokens - tok0);
-  dispatch_item<GENERAL>(a, a.single, row0, nrows, tok0, ntok, xs);
+  const GlobalLookup lookup{a.tab};
+  if (ntok <= 1) process_item<1, GENERAL, MatSink<1, true>>(a, a.single, row0, nrows, tok0, ntok, xs_f32, lookup);
+  else if (ntok == 2) process_item<2, GENERAL, MatSink<2, true>>(a, a.single, row0, nrows, tok0, ntok, xs_f32, lookup);
+  else process_item<4, GENERAL, MatSink<4, true>>(a, a.single, row0, nrows, tok0, ntok, xs_f32, lookup);
 }
 
-// Persistent CTAs pulling items of a device-built work list.
+// Persistent CTAs (one per SM) pulling items of a device-built work list.  Shared memory holds the
+// hot part of the sparse table (loaded once per CTA) followed by the bf16 activations of the
+// current item.
 template <bool GENERAL>
-__global__ void __launch_bounds__(kRowsPerItem) k_matmul_grouped(const MatmulArgs a) {
-  extern __shared__ __align__(16) float xs[];
+__global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const MatmulArgs a) {
+  extern __shared__ __align__(16) uint32_t smem_u32[];
   __shared__ int s_item;
+  uint32_t *hot = smem_u32;
+  void *xs = smem_u32 + kHotSlots;
   const int n_items = a.header[0];
+  if (n_items <= 0) return;
+  for (uint32_t i = threadIdx.x; i < kHotSlots; i += blockDim.x)
+    hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
+  const HotLookup lookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
   for (;;) {
     if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
-    __syncthreads();
+    __syncthreads();  // also orders the table fill before the first lookups
     const int i = s_item;
     if (i >= n_items) break;
     const int4 it = a.items[i];
     const qmoe_matrix_desc d = a.descs[it.x];
-    dispatch_item<GENERAL>(a, d, it.y, it.w & 0xffff, it.z, it.w >> 16, xs);
+    const int nrows = it.w & 0xffff, ntok = it.w >> 16;
+    // one or two tokens: fp32 activations (no conversion per gather); four: bf16, half the footprint
+    if (ntok <= 1)
+      process_item<1, GENERAL, MatSink<1, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+    else if (ntok == 2)
+      process_item<2, GENERAL, MatSink<2, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+    else
+      process_item<4, GENERAL, MatSink<4, false>>(a, d, it.y, nrows, it.z, ntok,
+                                                  reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
     __syncthreads();  // xs and s_item are rewritten by the next round
   }
 }
@@ -212,7 +275,7 @@ __global__ void k_decode(const uint32_t *__restrict__ tab, const int32_t *__rest
   e = e < b ? b : (e > n_codes ? n_codes : e);
   SymbolSink sink{sym + (size_t)row * width, width};
   const int wlim = (width + 1) & ~1;
-  const int pos = walk_row<GENERAL>(codes - mis, (int)b + mis, (int)e + mis, tab, dec, wlim + 2, sink);
+  const int pos = walk_row<GENERAL>(codes - mis, (int)b + mis, (int)e + mis, GlobalLookup{tab}, dec, wlim + 2, sink);
   if (status != nullptr && (pos != wlim || !span_ok)) atomicAdd(status, 1);
 }
 
@@ -224,18 +287,20 @@ __global__ void k_build_table(const int32_t *__restrict__ dec, uint32_t *__restr
   const uint32_t w0 = (uint32_t)dec[2 * code], w1 = (uint32_t)dec[2 * code + 1];
   const int len = (int)(w0 & 15u);
   bool ok = len >= 1 && len <= 14 && (int)(w1 & 15u) == len;
-  uint32_t e = (uint32_t)(2 * len);
+  uint32_t e = kEntryNull | (uint32_t)len;
   int nz = 0;
   for (int t = 0; t < 28; t++) {
     const uint32_t w = t < 14 ? w0 : w1;
     const uint32_t digit = (w >> (4 + 2 * (t % 14))) & 3u;
     if (digit == 0u) continue;
     if (t >= 2 * len || digit == 3u || nz == 3) { ok = false; break; }
-    e |= ((uint32_t)(t << 2) | (digit == 1u ? 0x80u : 0x100u)) << kEntryFieldShift(nz);
+    e &= ~(0xffu << (8 + 8 * nz));
+    e |= (uint32_t)t << (8 + 8 * nz);
+    if (digit == 2u) e |= 0x10u << nz;
     nz++;
   }
   if (!ok) {
-    e = 0;  // decoded digit by digit from `dec`
+    e = kEntryDense;  // decoded digit by digit from `dec`
     atomicAdd(nonconforming, 1);
   }
   tab[code] = e;
@@ -246,13 +311,17 @@ static size_t smem_bytes(int width, int group) {
   const int wlim = (width + 1) & ~1;
   return (size_t)(wlim + kPad) * group * sizeof(float);
 }
+static size_t grouped_smem_bytes(int width, int group) {
+  const int wlim = (width + 1) & ~1;
+  return sizeof(uint32_t) * kHotSlots + (size_t)(wlim + kPad) * group * sizeof(__nv_bfloat16);
+}
 
 template <bool GENERAL>
 static int set_smem_limits() {
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_uniform<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+                                 (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   return QMOE_OK;
 }
 
@@ -294,8 +363,8 @@ int launch_matmul_uniform(const SparseTable &tab, const int32_t *dec, const uint
   a.y = reinterpret_cast<__nv_bfloat16 *>(y);
   a.x_stride = x_stride;
   a.y_stride = y_stride;
-  a.chunks = chunk_count(height);
-  a.rpc = rows_per_chunk(height);
+  a.chunks = chunk_count(height, kRowsPerItem);
+  a.rpc = rows_per_chunk(height, kRowsPerItem);
   a.tokens = tokens;
   a.flags = flags;
   const int groups = (tokens + kMaxGroup - 1) / kMaxGroup;
@@ -401,7 +470,8 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
 }
 
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
-  return 64 + (int64_t)max_slots * (chunk_count(d_ff) + chunk_count(d_model)) * (int64_t)sizeof(int4);
+  return 64 + (int64_t)max_slots * (chunk_count(d_ff, kGroupedThreads) + chunk_count(d_model, kGroupedThreads)) *
+                  (int64_t)sizeof(int4);
 }
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
@@ -410,8 +480,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                        int max_slots, int d_model, int d_ff, int device, cudaStream_t stream) {
   int rc = ensure_smem_limits(device);
   if (rc) return rc;
-  const int chunks_wi = chunk_count(d_ff), chunks_wo = chunk_count(d_model);
-  const int rpc_wi = rows_per_chunk(d_ff), rpc_wo = rows_per_chunk(d_model);
+  const int chunks_wi = chunk_count(d_ff, kGroupedThreads), chunks_wo = chunk_count(d_model, kGroupedThreads);
+  const int rpc_wi = rows_per_chunk(d_ff, kGroupedThreads), rpc_wo = rows_per_chunk(d_model, kGroupedThreads);
   int *header = reinterpret_cast<int *>(work);
   int4 *items_wi = reinterpret_cast<int4 *>(reinterpret_cast<char *>(work) + 64);
   int4 *items_wo = items_wi + (size_t)max_slots * chunks_wi;
@@ -438,22 +508,16 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     a.items = phase == 0 ? items_wi : items_wo;
     a.header = header + 2 * phase;
     a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
-    const size_t smem = smem_bytes(width, kMaxGroup);
-    int per_sm = 0;
-    if (tab.conforming)
-      QMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_matmul_grouped<false>, kRowsPerItem, smem));
-    else
-      QMOE_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_matmul_grouped<true>, kRowsPerItem, smem));
-    per_sm = per_sm < 1 ? 1 : per_sm;
+    const size_t smem = grouped_smem_bytes(width, kMaxGroup);
     const long long max_items = (long long)max_slots * (phase == 0 ? chunks_wi : chunks_wo);
-    long long grid = (long long)sms * per_sm;
+    long long grid = sms;  // the 160 KB table allows one CTA per SM
     grid = grid > max_items ? max_items : grid;
     grid = grid < 1 ? 1 : grid;
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
     if (tab.conforming)
-      QMOE_LAUNCH(k_matmul_grouped<false>, (unsigned)grid, kRowsPerItem, smem, stream, a);
+      QMOE_LAUNCH(k_matmul_grouped<false>, (unsigned)grid, kGroupedThreads, smem, stream, a);
     else
-      QMOE_LAUNCH(k_matmul_grouped<true>, (unsigned)grid, kRowsPerItem, smem, stream, a);
+      QMOE_LAUNCH(k_matmul_grouped<true>, (unsigned)grid, kGroupedThreads, smem, stream, a);
     QMOE_CUDA(cudaGetLastError());
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }

@@ -5,21 +5,65 @@
 // [row_off[r], row_off[r+1]) of the code stream: it streams the span with aligned 128-bit loads
 // (8 codes), looks every code up in the sparse table and keeps a running column position.  There
 // is no cross-lane dependency, no shuffle and no barrier inside a row.
+//
+// The inner loop is written for instruction count: a code costs one table load, one position
+// update and, per possible non-zero, one byte extract, one predicated shared load and two
+// predicated adds.  Full chunks of eight codes take a path without per-code range checks.
 #pragma once
 
 #include "common.cuh"
 
 namespace qmoe {
 
-// Field accessors of a sparse-table entry (layout in common.cuh).
-__device__ __forceinline__ int entry_weights(uint32_t e) { return (int)(e & 31u); }
+__device__ __forceinline__ uint32_t entry_len(uint32_t e) { return e & 15u; }
+__device__ __forceinline__ uint32_t entry_nz_pos(uint32_t e, int k) {  // 0..27, or >= 0x80 if absent
+  return __byte_perm(e, 0u, 0x4441u + (uint32_t)k);
+}
+
+// Table lookups.  GlobalLookup reads the 256 KB sparse table through L1/L2.  HotLookup keeps the
+// codes [0, kHotLow) and [kHotHigh, 65536) -- 40 960 entries, 160 KB, about 90 % of the codes the
+// greedy encoder emits at 90 % sparsity -- in shared memory and falls back to global memory for the
+// rest.  The high range is stored right after the low one, so both are read with the code itself as
+// index and a per-range base.
+constexpr uint32_t kHotLow = 24576;
+constexpr uint32_t kHotHigh = 49152;
+constexpr uint32_t kHotSlots = kHotLow + (65536 - kHotHigh);
+
+struct GlobalLookup {
+  const uint32_t *__restrict__ tab;
+  __device__ __forceinline__ uint32_t operator()(uint32_t code) const { return __ldg(tab + code); }
+};
+
+struct HotLookup {
+  uint32_t hot_addr;                 // shared-space byte address of the kHotSlots entries
+  const uint32_t *__restrict__ tab;  // global memory, all 65 536 entries
+  // Exactly one of three predicated loads executes per lane; no branch, no divergence.
+  __device__ __forceinline__ uint32_t operator()(uint32_t code) const {
+    uint32_t e;
+    const uint32_t saddr = hot_addr + code * 4u;
+    const uint32_t *gaddr = tab + code;
+    asm("{\n\t"
+        ".reg .pred plo, phi, pmid;\n\t"
+        "setp.lt.u32 plo, %1, 24576;\n\t"
+        "setp.ge.u32 phi, %1, 49152;\n\t"
+        "setp.ge.and.u32 pmid, %1, 24576, !phi;\n\t"
+        "@plo ld.shared.b32 %0, [%2];\n\t"
+        "@phi ld.shared.b32 %0, [%2 + -98304];\n\t"
+        "@pmid ld.global.nc.b32 %0, [%3];\n\t"
+        "}"
+        : "=r"(e)
+        : "r"(code), "r"(saddr), "l"(gaddr));
+    return e;
+  }
+};
+static_assert(kHotLow == 24576 && kHotHigh == 49152 && (kHotHigh - kHotLow) * 4 == 98304,
+              "HotLookup's inline PTX hard-codes the hot ranges");
 
 // Digit-by-digit decode of one code from the reference table (sub1_cuda_kernel.cu:153-154,
 // 188-189): position t lives in word t / 14 at bit 4 + 2 * (t % 14).  Used only for entries that
-// do not fit the sparse form.
+// do not fit the sparse form.  Returns the number of weights the code covers.
 template <class Sink>
-__device__ __forceinline__ int dense_code(const int32_t *__restrict__ dec, uint32_t code, int pos,
-                                          Sink &sink) {
+__device__ __noinline__ int dense_code(const int32_t *__restrict__ dec, uint32_t code, int pos, Sink &sink) {
   const uint32_t w0 = (uint32_t)__ldg(dec + 2 * code);
   const uint32_t w1 = (uint32_t)__ldg(dec + 2 * code + 1);
   int len = (int)(w0 & 15u);
@@ -33,36 +77,51 @@ __device__ __forceinline__ int dense_code(const int32_t *__restrict__ dec, uint3
   return 2 * len;
 }
 
+__device__ __forceinline__ uint32_t chunk_code(const uint32_t (&w)[4], int j) {
+  return (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+}
+
 // Walks codes [b_al, e_al) (indices relative to the 16-byte aligned pointer codes_al) and feeds
-// every entry to the sink.  `pos_limit` clamps the running position so that a corrupt stream can
-// never index past the zero padding that follows x in shared memory.  Returns the final position
-// (== padded width for a well-formed row).
-template <bool GENERAL, class Sink>
+// every entry to the sink.  Positions are kept scaled by the sink's element size
+// (pos << Sink::kShift) so that they are shared-memory byte offsets; `pos_limit` (in weights)
+// clamps the running position so that a corrupt stream can never index past the zero padding that
+// follows x in shared memory.  Returns the final position in weights (== padded width for a
+// well-formed row).
+template <bool GENERAL, class Lookup, class Sink>
 __device__ __forceinline__ int walk_row(const uint16_t *__restrict__ codes_al, int b_al, int e_al,
-                                        const uint32_t *__restrict__ tab,
-                                        const int32_t *__restrict__ dec, int pos_limit, Sink &sink) {
-  int pos = 0;
+                                        const Lookup &lookup, const int32_t *__restrict__ dec,
+                                        int pos_limit, Sink &sink) {
+  constexpr int S = Sink::kShift;
+  uint32_t posb = 0;
+  const uint32_t limit_b = (uint32_t)pos_limit << S;
   for (int c = b_al & ~7; c < e_al; c += 8) {
     const uint4 q = __ldg(reinterpret_cast<const uint4 *>(codes_al + c));
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t e[8];
+    if (c >= b_al && c + 8 <= e_al) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) e[j] = lookup(chunk_code(w, j));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int idx = c + j;
+        e[j] = (idx >= b_al && idx < e_al) ? lookup(chunk_code(w, j)) : kEntryNull;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-      const int idx = c + j;
-      const bool valid = idx >= b_al && idx < e_al;
-      const uint32_t code = (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
-      uint32_t e = 0;
-      if (valid) e = __ldg(tab + code);
       if (GENERAL) {
-        if (valid && entry_weights(e) == 0) {
-          pos = min(pos + dense_code(dec, code, pos, sink), pos_limit);
+        if ((e[j] & 0xffu) == 0x80u) {
+          const int pos = (int)(posb >> S);
+          posb = min(((uint32_t)(pos + dense_code(dec, chunk_code(w, j), pos, sink))) << S, limit_b);
           continue;
         }
       }
-      sink.entry(e, pos);
-      pos = min(pos + entry_weights(e), pos_limit);
+      sink.entry(e[j], posb);
+      posb = min(posb + (entry_len(e[j]) << (S + 1)), limit_b);
     }
   }
-  return pos;
+  return (int)(posb >> S);
 }
 
 }  // namespace qmoe

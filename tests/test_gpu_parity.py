@@ -147,14 +147,16 @@ def test_nonconforming_table_uses_digit_path(dev, oracle_dict):
     a decode done straight from that table."""
     dec_np = oracle_dict[0].copy()
     digits, nweights = O.numpy_entry_digits(dec_np)
-    code = int(np.where((nweights == 28) & ((digits != 0).sum(1) == 3))[0][0])
-    free = int(np.where(digits[code] == 0)[0][0])
+    code = int(np.where((nweights >= 8) & ((digits != 0).sum(1) == 3))[0][0])
+    free = int(np.where(digits[code][:nweights[code]] == 0)[0][0])
     word, bit = free // 14, 4 + 2 * (free % 14)
     dec_np[2 * code + word] = np.int32(np.uint32(dec_np[2 * code + word]) | np.uint32(2 << bit))
     dec2 = torch.from_numpy(dec_np).to(dev)
-    h, w = 8, 56
+    h, w = 8, int(nweights[code]) + 28
     codes = np.full((h, 2), code, dtype=np.uint16)
-    codes[::2, 1] = 13               # mix with a conforming all-zero entry of 28 weights
+    zeros28 = int(np.where((nweights == 28) & ((digits != 0).sum(1) == 0))[0][0])
+    codes[::2, 1] = zeros28          # a conforming all-zero entry of 28 weights after / before it
+    codes[1::2, 0] = zeros28
     row_off = (np.arange(h + 1) * 2).astype(np.int32)
     want = O.numpy_decode_matrix(dec_np, codes.reshape(-1), row_off, h, w)
     d_codes = torch.from_numpy(codes.reshape(-1).view(np.int16)).to(dev)
