@@ -54,6 +54,22 @@ int qmoe_sub1_matvec(const int32_t *dec_dev, const uint16_t *w_comp_dev, const i
                      const void *ter_minmax_dev, const void *x_dev, void *y_dev, int height,
                      int width, int64_t n_codes, int device, void *stream);
 
+/* No counterpart in the reference: qmoe_sub1_matvec for callers that must not allocate device
+ * memory -- code hosted by a framework that owns all GPU memory and forbids side allocations, a
+ * process whose memory budget is entirely given to a pool, a thread that may never block in the
+ * driver's allocator.  Same arguments and result as qmoe_sub1_matvec, but the derived dictionary
+ * lives in a fixed array inside the library's device image (about 256 KB, held by every GPU that
+ * loads the library until the process exits) and nothing is allocated, by this call or by any
+ * routine it uses.  Limits: width <= QMOE_MAX_WIDTH, fewer than 2^31 codes; larger input is
+ * rejected with QMOE_ERR_UNSUPPORTED.  The array is shared by all calls and rebuilt from `dec_dev`
+ * by each of them on `stream`, so calls that overlap on one GPU (other streams or threads) race and
+ * must be serialised by the caller.  The first call on a device also looks up the array's address
+ * and raises a kernel attribute; make that first call before any stream capture. */
+int qmoe_sub1_matvec_noalloc(const int32_t *dec_dev, const uint16_t *w_comp_dev,
+                             const int32_t *row_off_dev, const void *ter_minmax_dev, const void *x_dev,
+                             void *y_dev, int height, int width, int64_t n_codes, int device,
+                             void *stream);
+
 /* Replaces the per-token loop of Sub1Linear.forward (sub1.py:132-143): x[tokens, width] ->
  * y[tokens, height] with the codes decoded once per group of tokens.  x rows are `x_stride`
  * elements apart, y rows `y_stride`.  flags: QMOE_FLAG_*. */

@@ -58,6 +58,7 @@ SIGNATURES = {
     "qmoe_version": (_I, []),
     "qmoe_sub1_build_dictionary": (_I, [_P, _P]),
     "qmoe_sub1_matvec": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _P]),
+    "qmoe_sub1_matvec_noalloc": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _P]),
     "qmoe_sub1_matmul": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _I, _L, _L, _I, _I, _P]),
     "qmoe_sub1_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _L, _I, _P]),
     "qmoe_sub1_pack_prepare": (_I, [_P, _P, _P, _I, _I, _I, _P]),

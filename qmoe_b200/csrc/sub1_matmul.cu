@@ -16,6 +16,7 @@
 #include "common.cuh"
 #include "sub1_walk.cuh"
 
+#include <mutex>
 #include <type_traits>
 
 namespace qmoe {
@@ -524,4 +525,106 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   return QMOE_OK;
 }
 
+
+// ---- matvec for callers that must not allocate --------------------------------------------------
+// qmoe_sub1_matvec normally keeps its derived 4-byte dictionary in memory that the library obtains
+// with cudaMalloc the first time it sees a `dec` pointer.  Some callers cannot tolerate that: code
+// running under a framework that owns all device memory and forbids side allocations, a process
+// whose memory budget is fully handed to a pool, or a host thread that must never block inside the
+// driver's allocator.  For them the scratch lives in this fixed array, which is part of the
+// library's device image: every GPU that loads the library carries these ~256 KB until the process
+// exits, whether or not the entry point is ever used.
+//
+// The array is shared by every call on a device and keeps whatever the previous call left in it.
+// Each call therefore rebuilds the dictionary from the `dec` it was given and clears the one word
+// that has to start at zero (the malformed-entry counter), all on the caller's stream.  Two calls
+// that are in flight on the same GPU at the same time (different streams or threads) write the
+// array concurrently and race; callers serialise them.
+constexpr size_t kNoAllocEntries = QMOE_DICT_COUNT;      // the derived dictionary, 4 bytes per code
+constexpr size_t kNoAllocWords = kNoAllocEntries + 64;   // + the counter word (padded to 256 bytes)
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWords];
+
+// In host code the name g_noalloc_scratch is only a handle for the symbol, not a device address;
+// the address each device gave the array is looked up once per device, with that device current.
+static uint32_t *noalloc_scratch_address(int device, cudaError_t *err) {
+  static uint32_t *address[64] = {nullptr};
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  *err = cudaSuccess;
+  if (address[device] == nullptr) {
+    void *p = nullptr;
+    *err = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (*err != cudaSuccess) return nullptr;
+    address[device] = reinterpret_cast<uint32_t *>(p);
+  }
+  return address[device];
+}
+
+}  // namespace qmoe
+
+extern "C" int qmoe_sub1_matvec_noalloc(const int32_t *dec_dev, const uint16_t *w_comp_dev,
+                                        const int32_t *row_off_dev, const void *ter_minmax_dev,
+                                        const void *x_dev, void *y_dev, int height, int width,
+                                        int64_t n_codes, int device, void *stream_) {
+  using namespace qmoe;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  QMOE_REQUIRE(dec_dev && row_off_dev && ter_minmax_dev && x_dev && y_dev && (w_comp_dev || n_codes == 0),
+               "null device pointer");
+  QMOE_REQUIRE(height >= 1 && width >= 1 && n_codes >= 0, "bad shape");
+  QMOE_REQUIRE(device >= 0 && device < 64, "device index out of range");
+  if (width > QMOE_MAX_WIDTH) {
+    set_error("qmoe_sub1_matvec_noalloc: width %d is beyond the maximum of %d columns", width, QMOE_MAX_WIDTH);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  if (n_codes >= (int64_t)1 << 31) {
+    set_error("qmoe_sub1_matvec_noalloc: %lld codes are beyond the maximum of 2^31-1 per matrix",
+              (long long)n_codes);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(w_comp_dev) & 1u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(row_off_dev) & 3u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(ter_minmax_dev) & 3u) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev)) & 1u) == 0,
+               "misaligned pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  // First call on a device: resolves the scratch address and raises the kernels' shared-memory
+  // limit.  Neither allocates, but both are set-up calls: make this first call outside any stream
+  // capture.
+  cudaError_t err;
+  uint32_t *scratch = noalloc_scratch_address(device, &err);
+  if (scratch == nullptr) return cuda_fail(err, "cudaGetSymbolAddress(g_noalloc_scratch)");
+  int rc = ensure_smem_limits(device);
+  if (rc) return rc;
+
+  int *counter = reinterpret_cast<int *>(scratch + kNoAllocEntries);
+  QMOE_CUDA(cudaMemsetAsync(counter, 0, sizeof(int), stream));
+  QMOE_LAUNCH(k_build_table, QMOE_DICT_COUNT / 256, 256, 0, stream, dec_dev, scratch, counter);
+  QMOE_CUDA(cudaGetLastError());
+
+  MatmulArgs a{};
+  a.tab = scratch;
+  a.dec = dec_dev;
+  a.codes = w_comp_dev;
+  a.row_off = row_off_dev;
+  a.minmax = reinterpret_cast<const __nv_bfloat162 *>(ter_minmax_dev);
+  a.single.n_codes = n_codes;
+  a.single.height = height;
+  a.single.width = width;
+  a.x = reinterpret_cast<const __nv_bfloat16 *>(x_dev);
+  a.y = reinterpret_cast<__nv_bfloat16 *>(y_dev);
+  a.x_stride = width;
+  a.y_stride = height;
+  a.chunks = chunk_count(height, kRowsPerItem);
+  a.rpc = rows_per_chunk(height, kRowsPerItem);
+  a.tokens = 1;
+  a.flags = QMOE_FLAG_ACCUMULATE;
+  // The kernel variant that can also decode malformed entries digit by digit: which entries are
+  // malformed is known only on the device, and reading the counter back would need a synchronise.
+  QMOE_LAUNCH(k_matmul_uniform<true>, (unsigned)a.chunks, kRowsPerItem, smem_bytes(width, 1), stream, a);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+namespace qmoe {
 }  // namespace qmoe

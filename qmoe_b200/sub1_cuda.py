@@ -74,6 +74,26 @@ def sub1matvec(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor,
                                   w_comp.numel(), dev.index, _stream(dev)))
 
 
+def sub1matvec_noalloc(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor,
+                       ter_minmax: torch.Tensor, x: torch.Tensor, y: torch.Tensor) -> None:
+    """``sub1matvec`` for hosts that must not allocate GPU memory (an embedding framework that owns
+    the device's memory, a fully pooled budget, a thread that may not block in the allocator).
+
+    Same arguments and result.  Neither this wrapper nor the library call behind it allocates: the
+    library keeps its derived dictionary in a fixed ~256 KB array that ships inside its device
+    image and rebuilds it from ``dec`` on every call.  The array is shared, so do not let two of
+    these calls overlap on one GPU, and make the first call on a device outside stream capture."""
+    dev, height = _check_matrix(dec, w_comp, row_off, ter_minmax)
+    _need(x, "x", torch.bfloat16, dev)
+    _need(y, "y", torch.bfloat16, dev)
+    if y.numel() != height:
+        raise ValueError(f"y has {y.numel()} elements but row_off describes {height} rows")
+    L = _lib.load()
+    _lib.check(L.qmoe_sub1_matvec_noalloc(dec.data_ptr(), w_comp.data_ptr(), row_off.data_ptr(),
+                                          ter_minmax.data_ptr(), x.data_ptr(), y.data_ptr(), height,
+                                          x.numel(), w_comp.numel(), dev.index, _stream(dev)))
+
+
 def sub1matmul(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor,
                ter_minmax: torch.Tensor, x: torch.Tensor, y: torch.Tensor, flags: int = 0) -> None:
     """Batched form: ``x[t, width] -> y[t, height]``, codes decoded once per group of four tokens.
