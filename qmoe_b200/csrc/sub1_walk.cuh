@@ -94,18 +94,22 @@ __device__ __forceinline__ int walk_row(const uint16_t *__restrict__ codes_al, i
   constexpr int S = Sink::kShift;
   uint32_t posb = 0;
   const uint32_t limit_b = (uint32_t)pos_limit << S;
-  for (int c = b_al & ~7; c < e_al; c += 8) {
-    const uint4 q = __ldg(reinterpret_cast<const uint4 *>(codes_al + c));
+  int c = b_al & ~7;
+  if (c >= e_al) return 0;
+  uint4 q = __ldg(reinterpret_cast<const uint4 *>(codes_al + c));
+  for (; c < e_al; c += 8) {
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    if (c + 8 < e_al) q = __ldg(reinterpret_cast<const uint4 *>(codes_al + c + 8));  // next chunk in flight
     uint32_t e[8];
-    if (c >= b_al && c + 8 <= e_al) {
+    // Every 16-bit value is a valid table index, so the lookups are unconditional; slots outside
+    // the row (first and last chunk only) are then replaced by the null entry.
 #pragma unroll
-      for (int j = 0; j < 8; j++) e[j] = lookup(chunk_code(w, j));
-    } else {
+    for (int j = 0; j < 8; j++) e[j] = lookup(chunk_code(w, j));
+    if (c < b_al || c + 8 > e_al) {
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const int idx = c + j;
-        e[j] = (idx >= b_al && idx < e_al) ? lookup(chunk_code(w, j)) : kEntryNull;
+        e[j] = (idx >= b_al && idx < e_al) ? e[j] : kEntryNull;
       }
     }
 #pragma unroll
