@@ -53,6 +53,9 @@ def parse_args():
     p.add_argument("--tokens", type=int, default=0, help="override the token count (debugging)")
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="target duration of the CPU baseline sample")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--mode", default="moe", choices=["moe", "layers"],
+                   help="moe: the MoE-layer benchmark (default); layers: the reference's per-layer matvec "
+                        "benchmark (test.py --benchmark) on its six shapes")
     return p.parse_args()
 
 
@@ -370,9 +373,91 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------
+# per-layer matvec latency: the reference's own benchmark (test.py:117-126,139-176)
+# ---------------------------------------------------------------------------------------------
+LAYER_SHAPES = [(768, 3072), (3072, 768), (1024, 4096), (4096, 1024), (2080, 6144), (6144, 2080)]
+
+
+def run_layers(args):
+    """One JSON line per shape.  ``--impl ours``: the new sub1matvec and the dense bf16 matvec of
+    test.py:176; ``--impl reference``: the reference's own kernel built unmodified into oracle/_ref.
+    Two protocols: the reference's (100 warm-up + 1000 calls, host sync after every call, wall clock)
+    and back-to-back launches timed with CUDA events."""
+    import torch
+    from qmoe_b200 import sub1, sub1_cuda, synth
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    dev = torch.device("cuda", 0)
+    ref = None
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import build_ref
+        ref = build_ref.load()
+        if ref is None:
+            print(json.dumps({"impl": "reference", "mode": "layers",
+                              "unavailable": "oracle/_ref not built (python oracle/build_ref.py)"}))
+            return
+    dec, trie = sub1.DEC(dev), sub1.TRIE(dev)
+    iters = max(args.steps, 1) * 50
+
+    def sync_protocol(f):
+        for _ in range(100):
+            f()
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            f()
+            torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / iters * 1e6
+
+    def event_protocol(f):
+        for _ in range(20):
+            f()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(iters):
+            f()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / iters * 1e3
+
+    for h, w in LAYER_SHAPES:
+        sym = synth.ternary_cuda(h * w, SEED, synth.matrix_first_index(7 * h + w), 0.9, dev).reshape(h, w)
+        codes, row_off, _, _ = sub1_cuda.sub1pack_u8(trie, sym)
+        row_off = row_off[0].contiguous()
+        codes = codes[: int(row_off[-1])].contiguous()
+        minmax = synth.row_scales(h, SEED, 7 * h + w).to(dev)
+        x = synth.tokens(1, w, SEED)[0].to(dev)
+        y = torch.zeros(h, dtype=torch.bfloat16, device=dev)
+        n_bytes = 2 * codes.numel() + 4 * (h + 1) + 4 * h + 2 * w + 4 * h
+        line = {"mode": "layers", "impl": args.impl, "shape": [h, w], "n_codes": int(codes.numel()),
+                "bits_per_weight": 16 * codes.numel() / (h * w), "algorithmic_bytes": n_bytes,
+                "iters": iters, "unit": "us per call"}
+        if ref is not None:
+            f = lambda: ref.sub1matvec(dec, codes, row_off, minmax, x, y)  # noqa: E731
+            line["sub1_sync_us"] = sync_protocol(f)
+            line["sub1_events_us"] = event_protocol(f)
+        else:
+            f = lambda: sub1_cuda.sub1matvec(dec, codes, row_off, minmax, x, y)  # noqa: E731
+            line["sub1_sync_us"] = sync_protocol(f)
+            line["sub1_events_us"] = event_protocol(f)
+            deq = torch.stack([torch.zeros(h, device=dev), minmax[0::2].float(), minmax[1::2].float()], 1)
+            dense = torch.gather(deq, 1, sym.long()).bfloat16()
+            xc, yc = x.reshape(-1, 1), torch.zeros(h, 1, dtype=torch.bfloat16, device=dev)
+            g = lambda: torch.matmul(dense, xc, out=yc)  # noqa: E731
+            line["dense_sync_us"] = sync_protocol(g)
+            line["dense_events_us"] = event_protocol(g)
+        line["sub1_gbs_events"] = n_bytes / line["sub1_events_us"] / 1e3
+        print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
-    if args.impl == "reference":
+    if args.mode == "layers":
+        run_layers(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -1,0 +1,54 @@
+"""Builds the REFERENCE's own CUDA extension, unmodified, as a GPU-side oracle / baseline.
+
+    python oracle/build_ref.py            # needs the reference checkout (default /root/reference)
+
+The two source files are compiled where they lie (``sub1_cuda.cpp`` and ``sub1_cuda_kernel.cu`` of
+IST-DASLab/qmoe); nothing is copied and nothing is written outside ``oracle/_ref/``.  The recipe is
+ours (torch's JIT extension builder with an explicit sm_100 target), not the reference's
+``setup_cuda.py``.  The result, ``oracle/_ref/sub1_cuda.so``, is a torch extension module exposing
+the reference's ``sub1matvec`` and ``sub1pack``; TEST INFRASTRUCTURE ONLY: the tests use it to check
+the new kernels against the reference kernel on the same inputs, and the layer benchmark times it
+next to them.  Load it with :func:`load` (it is NOT put on ``sys.path``).
+"""
+import glob
+import importlib.util
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT = os.path.join(HERE, "_ref")
+REF = os.environ.get("QMOE_REFERENCE", "/root/reference")
+
+
+def built_path():
+    hits = sorted(glob.glob(os.path.join(OUT, "sub1_cuda*.so")))
+    return hits[0] if hits else None
+
+
+def build() -> str:
+    srcs = [os.path.join(REF, "sub1_cuda.cpp"), os.path.join(REF, "sub1_cuda_kernel.cu")]
+    if not all(os.path.exists(s) for s in srcs):
+        raise FileNotFoundError(f"reference sources not found under {REF}")
+    os.makedirs(OUT, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
+    os.environ.setdefault("MAX_JOBS", "4")
+    from torch.utils import cpp_extension
+    cpp_extension.load(name="sub1_cuda", sources=srcs, build_directory=OUT, verbose=True,
+                       is_python_module=False)
+    return built_path()
+
+
+def load():
+    """The reference extension module, or None if it has not been built."""
+    path = built_path()
+    if path is None:
+        return None
+    import torch  # noqa: F401  (the extension links against torch)
+    spec = importlib.util.spec_from_file_location("sub1_cuda", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+if __name__ == "__main__":
+    print(build())

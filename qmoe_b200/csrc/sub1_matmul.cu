@@ -227,6 +227,121 @@ __global__ void __launch_bounds__(kRowsPerItem) k_matmul_uniform(const MatmulArg
   else process_item<4, GENERAL, MatSink<4, true>>(a, a.single, row0, nrows, tok0, ntok, xs_f32, lookup);
 }
 
+// ---- single matrix, one WARP per row --------------------------------------------------------------
+// A lone 0.2-1.1 MB matrix is a latency problem, not a bandwidth one: with one thread per row a
+// 768 x 3072 matrix offers 768 threads that each walk 132 codes in sequence.  Here a warp shares a
+// row: lane i takes code base + i, the lanes' column positions come from a warp prefix sum of the
+// code lengths, and the two partial sums are reduced with shuffles at the end of the row.  The
+// serial depth of a row drops from its number of codes to that number / 32.
+constexpr int kWarpRowThreads = 256;
+
+template <int T, bool GENERAL>
+__device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nrows, int tok0, int ntok, float *xs) {
+  using SinkT = MatSink<T, true>;
+  const qmoe_matrix_desc &d = a.single;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int W = d.width;
+  const int wlim = (W + 1) & ~1;
+  for (int c = tid; c < wlim + kPad; c += blockDim.x) {
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+      float v = 0.f;
+      if (c < W && t < ntok) v = __bfloat162float(a.x[(long long)(tok0 + t) * a.x_stride + c]);
+      xs[c * T + t] = v;
+    }
+  }
+  __syncthreads();
+
+  constexpr int S = SinkT::kShift;
+  const uint32_t limit = (uint32_t)wlim;
+  for (int r = warp; r < nrows; r += nwarps) {
+    const int row = row0 + r;
+    long long b = a.row_off[row], e = a.row_off[row + 1];
+    b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+    e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
+    SinkT sink;
+    sink.xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
+#pragma unroll
+    for (int t = 0; t < T; t++) sink.s1[t] = sink.s2[t] = 0.f;
+    uint32_t row_pos = 0;
+    // Two groups of 32 codes per iteration (both dictionary lookups in flight together), and the
+    // codes of the next iteration are requested before this one is processed.
+    uint32_t code0 = 0, code1 = 0;
+    if (b + lane < e) code0 = a.codes[b + lane];
+    if (b + 32 + lane < e) code1 = a.codes[b + 32 + lane];
+    for (long long base = b; base < e; base += 64) {
+      const bool v0 = base + lane < e, v1 = base + 32 + lane < e;
+      const uint32_t c0 = code0, c1 = code1;
+      uint32_t e0 = kEntryNull, e1 = kEntryNull;
+      if (v0) e0 = __ldg(a.tab + c0);
+      if (v1) e1 = __ldg(a.tab + c1);
+      if (base + 64 + lane < e) code0 = a.codes[base + 64 + lane];
+      if (base + 96 + lane < e) code1 = a.codes[base + 96 + lane];
+      uint32_t len0 = 2u * entry_len(e0), len1 = 2u * entry_len(e1);
+      bool d0 = false, d1 = false;
+      if (GENERAL) {
+        d0 = (e0 & 0xffu) == 0x80u;
+        d1 = (e1 & 0xffu) == 0x80u;
+        if (d0) len0 = 2u * min((uint32_t)__ldg(a.dec + 2 * c0) & 15u, 14u);
+        if (d1) len1 = 2u * min((uint32_t)__ldg(a.dec + 2 * c1) & 15u, 14u);
+      }
+      uint32_t i0 = len0, i1 = len1;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t u0 = __shfl_up_sync(0xffffffffu, i0, o);
+        const uint32_t u1 = __shfl_up_sync(0xffffffffu, i1, o);
+        if (lane >= o) {
+          i0 += u0;
+          i1 += u1;
+        }
+      }
+      const uint32_t total0 = __shfl_sync(0xffffffffu, i0, 31), total1 = __shfl_sync(0xffffffffu, i1, 31);
+      const uint32_t p0 = min(row_pos + i0 - len0, limit);
+      const uint32_t p1 = min(row_pos + total0 + i1 - len1, limit);
+      if (GENERAL && d0) dense_code(a.dec, c0, (int)p0, sink);
+      else sink.entry(e0, p0 << S);
+      if (GENERAL && d1) dense_code(a.dec, c1, (int)p1, sink);
+      else sink.entry(e1, p1 << S);
+      row_pos = min(row_pos + total0 + total1, limit);
+    }
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        sink.s1[t] += __shfl_xor_sync(0xffffffffu, sink.s1[t], o);
+        sink.s2[t] += __shfl_xor_sync(0xffffffffu, sink.s2[t], o);
+      }
+    }
+    if (lane == 0) {
+      const __nv_bfloat162 mm = a.minmax[row];
+      const float mn = __bfloat162float(mm.x), mx = __bfloat162float(mm.y);
+#pragma unroll
+      for (int t = 0; t < T; t++) {
+        if (t < ntok) {
+          float v = bf16_round(fmaf(mn, sink.s1[t], mx * sink.s2[t]));
+          __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
+          if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
+          if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
+          *yp = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+}
+
+// grid.x = row blocks of a.rpc rows, grid.y = token groups of kMaxGroup tokens.
+template <bool GENERAL>
+__global__ void __launch_bounds__(kWarpRowThreads) k_matmul_warp_rows(const MatmulArgs a) {
+  extern __shared__ __align__(16) float xs_f32[];
+  const int row0 = blockIdx.x * a.rpc;
+  const int nrows = min(a.rpc, a.single.height - row0);
+  const int tok0 = blockIdx.y * kMaxGroup;
+  const int ntok = min(kMaxGroup, a.tokens - tok0);
+  if (ntok <= 1) warp_rows<1, GENERAL>(a, row0, nrows, tok0, ntok, xs_f32);
+  else if (ntok == 2) warp_rows<2, GENERAL>(a, row0, nrows, tok0, ntok, xs_f32);
+  else warp_rows<4, GENERAL>(a, row0, nrows, tok0, ntok, xs_f32);
+}
+
 // Persistent CTAs (one per SM) pulling items of a device-built work list.  Shared memory holds the
 // hot part of the sparse table (loaded once per CTA) followed by the bf16 activations of the
 // current item.
@@ -321,6 +436,8 @@ template <bool GENERAL>
 static int set_smem_limits() {
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_uniform<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_warp_rows<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   return QMOE_OK;
@@ -364,18 +481,23 @@ int launch_matmul_uniform(const SparseTable &tab, const int32_t *dec, const uint
   a.y = reinterpret_cast<__nv_bfloat16 *>(y);
   a.x_stride = x_stride;
   a.y_stride = y_stride;
-  a.chunks = chunk_count(height, kRowsPerItem);
-  a.rpc = rows_per_chunk(height, kRowsPerItem);
   a.tokens = tokens;
   a.flags = flags;
   const int groups = (tokens + kMaxGroup - 1) / kMaxGroup;
   const int group = tokens >= 3 ? 4 : tokens;
   const size_t smem = smem_bytes(width, group);
-  const dim3 grid((unsigned)(a.chunks * groups));
+  // rows per CTA: a multiple of the CTA's eight warps, aiming at up to eight CTAs per SM
+  const int warps = kWarpRowThreads / 32;
+  const int target = 8 * sm_count(device);
+  int rpc = (height + target - 1) / target;
+  rpc = (rpc + warps - 1) / warps * warps;
+  a.rpc = rpc;
+  a.chunks = (height + rpc - 1) / rpc;
+  const dim3 grid((unsigned)a.chunks, (unsigned)groups);
   if (tab.conforming)
-    QMOE_LAUNCH(k_matmul_uniform<false>, grid, kRowsPerItem, smem, stream, a);
+    QMOE_LAUNCH(k_matmul_warp_rows<false>, grid, kWarpRowThreads, smem, stream, a);
   else
-    QMOE_LAUNCH(k_matmul_uniform<true>, grid, kRowsPerItem, smem, stream, a);
+    QMOE_LAUNCH(k_matmul_warp_rows<true>, grid, kWarpRowThreads, smem, stream, a);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

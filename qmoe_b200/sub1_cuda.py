@@ -56,22 +56,37 @@ def _check_matrix(dec, w_comp, row_off, ter_minmax) -> Tuple[torch.device, int]:
     return dev, height
 
 
+_MATVEC_CHECKED = {}
+
+
 def sub1matvec(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor,
                ter_minmax: torch.Tensor, x: torch.Tensor, y: torch.Tensor) -> None:
     """``y += bf16(W x)`` for one compressed matrix and one bf16 vector, in place.
 
     Same contract as the reference binding (sub1_cuda.cpp:35-45): height = ``y.numel()``, width =
     ``x.numel()`` (sub1_cuda_kernel.cu:78-79); unlike the reference, any height and any width up to
-    8192 works, and unsupported input raises instead of silently doing nothing."""
-    dev, height = _check_matrix(dec, w_comp, row_off, ter_minmax)
-    _need(x, "x", torch.bfloat16, dev)
-    _need(y, "y", torch.bfloat16, dev)
+    8192 works, and unsupported input raises instead of silently doing nothing.  The argument checks
+    of a (dec, w_comp, row_off, ter_minmax) quadruple are remembered by storage address and shape, so
+    the per-token loop of ``Sub1Linear`` pays them once."""
+    key = (dec.data_ptr(), w_comp.data_ptr(), row_off.data_ptr(), ter_minmax.data_ptr(),
+           w_comp.numel(), row_off.numel())
+    hit = _MATVEC_CHECKED.get(key)
+    if hit is None:
+        dev, height = _check_matrix(dec, w_comp, row_off, ter_minmax)
+        if len(_MATVEC_CHECKED) > 65536:
+            _MATVEC_CHECKED.clear()
+        hit = _MATVEC_CHECKED[key] = (dev, height, _lib.load().qmoe_sub1_matvec)
+    dev, height, fn = hit
+    if (x.dtype is not torch.bfloat16 or y.dtype is not torch.bfloat16 or x.device != dev or y.device != dev
+            or not x.is_contiguous() or not y.is_contiguous()):
+        _need(x, "x", torch.bfloat16, dev)
+        _need(y, "y", torch.bfloat16, dev)
     if y.numel() != height:
         raise ValueError(f"y has {y.numel()} elements but row_off describes {height} rows")
-    L = _lib.load()
-    _lib.check(L.qmoe_sub1_matvec(dec.data_ptr(), w_comp.data_ptr(), row_off.data_ptr(),
-                                  ter_minmax.data_ptr(), x.data_ptr(), y.data_ptr(), height, x.numel(),
-                                  w_comp.numel(), dev.index, _stream(dev)))
+    rc = fn(key[0], key[1], key[2], key[3], x.data_ptr(), y.data_ptr(), height, x.numel(), key[4], dev.index,
+            torch.cuda.current_stream(dev).cuda_stream)
+    if rc:
+        _lib.check(rc)
 
 
 def sub1matvec_noalloc(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor,
