@@ -54,6 +54,8 @@ def parse_args():
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="target duration of the CPU baseline sample")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
+    p.add_argument("--skew", type=int, default=0,
+                   help="skewed router: this many hot experts receive half of the tokens (config 3 uses 8)")
     p.add_argument("--mode", default="moe", choices=["moe", "layers"],
                    help="moe: the MoE-layer benchmark (default); layers: the reference's per-layer matvec "
                         "benchmark (test.py --benchmark) on its six shapes")
@@ -269,12 +271,18 @@ def run_ours(args):
     hidden_host = hidden_all[rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     out_host = torch.empty_like(hidden_host).pin_memory()
     hidden_dev = hidden_host.to(dev)
+    skew_logits_all = skew_logits = None
+    if args.skew > 0:   # logits given directly: N(0,1) plus a large bias that sends half the tokens to the hot experts
+        skew_logits_all = synth.router_logits(n_tokens, n_experts, SEED, hot_experts=args.skew, hot_fraction=0.5)
+        perm = torch.randperm(n_tokens, generator=torch.Generator().manual_seed(SEED))
+        skew_logits_all = skew_logits_all[perm].contiguous()      # spread the hot tokens over the ranks
+        skew_logits = skew_logits_all[rank * t_local:(rank + 1) * t_local].contiguous().to(dev)
     if world > 1:
         layer = ExpertParallelMLP(router_weight, store, n_experts, expert_capacity=1024)
-        step = lambda h: layer(h, seq_len=t_local)[0]  # noqa: E731
+        step = lambda h: layer(h, router_logits=skew_logits, seq_len=t_local)[0]  # noqa: E731
     else:
         layer = sub1.FasterMLP(router_weight, store, expert_capacity=1024)
-        step = lambda h: layer(h.unsqueeze(0))[0].squeeze(0)  # noqa: E731
+        step = lambda h: layer(h.unsqueeze(0), router_logits=skew_logits)[0].squeeze(0)  # noqa: E731
 
     def barrier():
         if world > 1:
@@ -348,7 +356,7 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # algorithmic bytes of the grouped kernel on rank 0: matrices of experts that received tokens
-    logits = hidden_all.to(dev).float() @ router_weight.to(dev).t()
+    logits = hidden_all.to(dev).float() @ router_weight.to(dev).t() if skew_logits_all is None else skew_logits_all.to(dev)
     choice, _ = sub1.route_top1(logits.contiguous())
     counts = torch.bincount(choice.long(), minlength=n_experts)[rank * e_local:(rank + 1) * e_local].cpu().tolist()
     bytes_wi = bytes_wo = 0
@@ -375,6 +383,8 @@ def run_ours(args):
             "config": {
                 "workload": args.workload, "d_model": d_model, "d_ff": d_ff, "experts": n_experts,
                 "tokens": n_tokens, "parallelism": f"ep{world}", "experts_per_gpu": e_local,
+                "router": f"skewed: {args.skew} experts get half of the tokens" if args.skew else "uniform top-1",
+                "max_tokens_per_expert_rank0": max(counts) if counts else 0,
                 "compressed_bytes_per_gpu": store.compressed_bytes, "active_experts_rank0": active,
                 "l2": f"inputs larger than L2 ({(bytes_wi + bytes_wo) / 1e6:.0f} MB of compressed experts "
                       "streamed per GPU per step)",

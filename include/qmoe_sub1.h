@@ -167,6 +167,14 @@ int qmoe_moe_unpermute(const void *ys_dev, const int32_t *slot_dev, void *out_de
  * no host synchronisation.  work_dev is caller-provided scratch of qmoe_moe_work_bytes() bytes.
  *   xs_dev bf16[n_slots, d_model], hs_dev bf16[n_slots, d_ff], ys_dev bf16[n_slots, d_model] */
 int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff);
+
+/* Inside qmoe_moe_grouped_ffn, experts with at least `tokens` tokens are multiplied on the tensor
+ * cores (tcgen05): their rows are decoded once into bf16 tiles in shared memory and multiplied with
+ * blocks of 64 tokens, instead of being re-decoded for every group of four tokens.  0 disables that
+ * path; values below 8 are raised to 8.  Default 128 (or the environment variable
+ * QMOE_TILE_MIN_TOKENS), the measured break-even.  Returns the previous value.  No counterpart in
+ * the reference, which runs one matvec per token (sub1.py:139-142). */
+int qmoe_moe_set_tile_min_tokens(int tokens);
 int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
                          const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
                          const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,

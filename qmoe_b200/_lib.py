@@ -72,6 +72,7 @@ SIGNATURES = {
     "qmoe_moe_permute": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _L, _I, _P]),
     "qmoe_moe_unpermute": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _P]),
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
+    "qmoe_moe_set_tile_min_tokens": (_I, [_I]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_launch_count": (_L, []),

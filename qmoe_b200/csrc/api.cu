@@ -78,6 +78,7 @@ int launch_matmul_uniform(const SparseTable &tab, const int32_t *dec, const uint
 int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *codes, const int32_t *row_off,
                   uint8_t *sym, int32_t *status, int height, int width, int64_t n_codes, cudaStream_t stream);
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
+int set_tile_min_tokens(int tokens);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const int32_t *offsets, const void *xs, void *hs, void *ys, void *work, int n_experts,
@@ -415,6 +416,8 @@ int qmoe_moe_unpermute(const void *ys_dev, const int32_t *slot_dev, void *out_de
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   return launch_unpermute(ys_dev, slot_dev, out_dev, n_tokens, d_model, ys_stride, out_stride, as_stream(stream));
 }
+
+int qmoe_moe_set_tile_min_tokens(int tokens) { return set_tile_min_tokens(tokens); }
 
 int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff) {
   (void)n_experts;

@@ -16,6 +16,8 @@
 #include "common.cuh"
 #include "sub1_walk.cuh"
 
+#include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -525,11 +527,13 @@ int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cu
 }
 
 // ---- grouped expert FFN -------------------------------------------------------------------------
-// Work buffer layout: int header[16] | int4 items_wi[max_slots * chunks_wi] | int4 items_wo[...].
-// header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter.
+// Work buffer layout: int header[16] | int4 items_wi[max_slots * chunks_wi] | int4 items_wo[...] |
+// tile items of wi | tile items of wo.
+// header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter,
+// [4] / [5] = tile items of wi / wo, [8] = timeouts seen by the tile kernels.
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
                                                      int d_model, int d_ff, int rpc_wi, int chunks_wi,
-                                                     int rpc_wo, int chunks_wo, int max_slots,
+                                                     int rpc_wo, int chunks_wo, int max_slots, int tile_min,
                                                      int *header, int4 *items_wi, int4 *items_wo) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
@@ -543,6 +547,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       first = offsets[e];
       count = offsets[e + 1] - first;
       count = count < 0 ? 0 : count;
+      if (tile_min > 0 && count >= tile_min) count = 0;  // handled by the tensor-core tile path
     }
     const int groups = (count + kMaxGroup - 1) / kMaxGroup;
     // exclusive scan of `groups` over the block
@@ -592,9 +597,41 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
   }
 }
 
+// Tensor-core tile path (sub1_tile.cu).
+int64_t tile_work_bytes(int max_slots, int d_model, int d_ff);
+int tile_cap_blocks(int max_slots);
+int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, int d_model, int d_ff,
+                           int max_slots, int *header, int4 *items_wi, int4 *items_wo, cudaStream_t stream);
+int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
+                      const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
+                      const int4 *items, const int *n_items, int *status, int flags, int max_items, int device,
+                      cudaStream_t stream);
+
+// Experts with at least this many tokens take the tile path (0 disables it).  The default is the
+// measured break-even on a switch-large-128 layer with a skewed router: at 32-37 tokens per hot expert
+// the per-row kernel (eight or nine passes of four tokens) is still faster, 0.31 ms against 0.43 ms per
+// layer; at about 140 tokens the two are level (0.82 ms); at about 560 tokens the tile path wins,
+// 2.49 ms against 2.92 ms.  The environment variable exists for such measurements.
+static std::atomic<int> g_tile_min{-1};  // -1: not yet initialised from the environment
+static int clamp_tile_min(int t) { return t <= 0 ? 0 : (t < 8 ? 8 : t); }
+static int tile_min_tokens() {
+  int v = g_tile_min.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char *s = getenv("QMOE_TILE_MIN_TOKENS");
+    v = clamp_tile_min(s ? atoi(s) : 128);
+    g_tile_min.store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+int set_tile_min_tokens(int tokens) {
+  const int before = tile_min_tokens();
+  g_tile_min.store(clamp_tile_min(tokens), std::memory_order_relaxed);
+  return before;
+}
+
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
   return 64 + (int64_t)max_slots * (chunk_count(d_ff, kGroupedThreads) + chunk_count(d_model, kGroupedThreads)) *
-                  (int64_t)sizeof(int4);
+                  (int64_t)sizeof(int4) + tile_work_bytes(max_slots, d_model, d_ff);
 }
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
@@ -608,8 +645,15 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   int *header = reinterpret_cast<int *>(work);
   int4 *items_wi = reinterpret_cast<int4 *>(reinterpret_cast<char *>(work) + 64);
   int4 *items_wo = items_wi + (size_t)max_slots * chunks_wi;
-  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, d_model, d_ff, rpc_wi, chunks_wi, rpc_wo, chunks_wo, max_slots, header, items_wi, items_wo);
+  const int tile_min = tab.conforming ? tile_min_tokens() : 0;
+  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, d_model, d_ff, rpc_wi, chunks_wi, rpc_wo, chunks_wo, max_slots, tile_min, header, items_wi, items_wo);
   QMOE_CUDA(cudaGetLastError());
+  int4 *tile_wi = items_wo + (size_t)max_slots * chunks_wo;
+  int4 *tile_wo = tile_wi + (size_t)tile_cap_blocks(max_slots) * ((d_ff + 127) / 128);
+  if (tile_min > 0) {
+    rc = launch_build_tile_work(offsets, n_experts, tile_min, d_model, d_ff, max_slots, header, tile_wi, tile_wo, stream);
+    if (rc) return rc;
+  }
 
   MatmulArgs a{};
   a.tab = tab.entries;
@@ -636,6 +680,13 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     long long grid = sms;  // the 160 KB table allows one CTA per SM
     grid = grid > max_items ? max_items : grid;
     grid = grid < 1 ? 1 : grid;
+    if (tile_min > 0) {
+      const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
+      rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
+                             phase == 0 ? tile_wi : tile_wo, header + 4 + phase, header + 8, a.flags,
+                             tile_cap_blocks(max_slots) * rows_blocks, device, stream);
+      if (rc) return rc;
+    }
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
     if (tab.conforming)
       QMOE_LAUNCH(k_matmul_grouped<false>, (unsigned)grid, kGroupedThreads, smem, stream, a);

@@ -90,8 +90,16 @@ def test_config3_switch_large_128_layer_uniform():
     _check_layer("switch-large-128", 512, sample=4)
 
 
-def test_config3_switch_large_128_layer_skewed_router():
-    counts = _check_layer("switch-large-128", 512, hot_experts=8, hot_fraction=0.5, sample=4)
+@pytest.mark.parametrize("tile_min", [0, 16])
+def test_config3_switch_large_128_layer_skewed_router(tile_min):
+    """Hot experts (32+ tokens) through the per-row kernel (tile path off) and through the
+    tensor-core tile path (threshold 16)."""
+    from qmoe_b200 import _lib
+    before = _lib.load().qmoe_moe_set_tile_min_tokens(tile_min)
+    try:
+        counts = _check_layer("switch-large-128", 512, hot_experts=8, hot_fraction=0.5, sample=4)
+    finally:
+        _lib.load().qmoe_moe_set_tile_min_tokens(before)
     assert int(counts.max()) >= 32          # the hot experts: many token groups per expert
 
 

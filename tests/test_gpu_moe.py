@@ -94,3 +94,30 @@ def test_grouped_ffn_direct_with_empty_and_large_groups(dev, small_layer):
         if c:
             assert rel_err(ys[pos:pos + c], experts[e].oracle_ffn(xs[pos:pos + c])) <= TOL
         pos += c
+
+
+def test_tensor_core_tile_path_for_heavily_loaded_experts(dev, small_layer):
+    """Experts with >= 16 tokens go through the tcgen05 tile kernel (64-token blocks, 128-row blocks,
+    partial last blocks in both directions); the others stay on the per-row kernel."""
+    from qmoe_b200 import _lib
+    experts, store = small_layer
+    counts = [0, 70, 1, 16, 0, 33, 3, 64]
+    n = sum(counts)
+    xs = synth.tokens(n, store.d_model, seed=11)
+    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+    nbytes = int(_lib.load().qmoe_moe_work_bytes(store.n_experts, n, store.d_model, store.d_ff))
+    work = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    before = _lib.load().qmoe_moe_set_tile_min_tokens(16)
+    try:
+        ys = sub1.grouped_ffn(store, offsets, xs.to(dev), n, work=work)
+        torch.cuda.synchronize()
+    finally:
+        _lib.load().qmoe_moe_set_tile_min_tokens(before)
+    header = work[:64].view(torch.int32).cpu()
+    assert int(header[8]) == 0                       # no bounded wait gave up
+    assert int(header[4]) == 5 * 3 and int(header[5]) == 5 * 1   # 2+1+1+1 token blocks x row blocks
+    pos = 0
+    for e, c in enumerate(counts):
+        if c:
+            assert rel_err(ys[pos:pos + c], experts[e].oracle_ffn(xs[pos:pos + c])) <= TOL, (e, c)
+        pos += c
