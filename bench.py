@@ -56,7 +56,7 @@ def parse_args():
     p.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
     p.add_argument("--skew", type=int, default=0,
                    help="skewed router: this many hot experts receive half of the tokens (config 3 uses 8)")
-    p.add_argument("--mode", default="moe", choices=["moe", "layers"],
+    p.add_argument("--mode", default="moe", choices=["moe", "layers", "generate"],
                    help="moe: the MoE-layer benchmark (default); layers: the reference's per-layer matvec "
                         "benchmark (test.py --benchmark) on its six shapes")
     return p.parse_args()
@@ -71,7 +71,7 @@ def workload_dims(args):
 # clocks
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples every 200 ms while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples every 50 ms while the timed region runs."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -88,7 +88,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                 "-lms", "50"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -508,9 +508,65 @@ def run_layers(args):
         print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------
+# end-to-end greedy generation through a Switch-c-2048-shaped decoder (benchmark configuration 5)
+# ---------------------------------------------------------------------------------------------
+def run_generate(args):
+    """15 MoE blocks of the switch-c-2048 layer with dense bf16 attention (32 heads), seeded random
+    weights, batch 1: 128 prompt ids, 128 greedily generated tokens; experts sharded over the ranks
+    (token stream replicated, one all-reduce per layer).  One JSON line: generated tokens/s."""
+    import torch
+    import torch.distributed as dist
+    from qmoe_b200.decoder import SwitchDecoderLM
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    d_model, d_ff, n_experts, _ = workload_dims(args)
+    layers, prompt_len, new_tokens = 15, 128, 128
+    t0 = time.perf_counter()
+    model = SwitchDecoderLM(d_model, d_ff, n_experts, layers, 32, 32128, prompt_len + new_tokens, dev, SEED,
+                            rank, world)
+    torch.cuda.synchronize()
+    setup_s = time.perf_counter() - t0
+    prompt = torch.randint(0, 32128, (prompt_len,), generator=torch.Generator().manual_seed(SEED))
+    times = []
+    for it in range(max(args.steps, 1) + 1):                 # first sample is warm-up (sub1.py:382)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = model.generate(prompt, new_tokens, use_graph=not args.no_graph)
+        torch.cuda.synchronize()
+        if it > 0:
+            times.append(time.perf_counter() - t0)
+    secs = sum(times) / len(times)
+    if rank == 0:
+        print(json.dumps({
+            "mode": "generate", "metric": "generated_tokens_per_s", "value": new_tokens / secs, "unit": "tokens/s",
+            "n_gpus": world, "seconds_per_sample": secs, "samples": len(times),
+            "config": {"workload": args.workload + " decoder", "layers": layers, "d_model": d_model, "d_ff": d_ff,
+                       "experts": n_experts, "heads": 32, "vocab": 32128, "prompt": prompt_len,
+                       "generated": new_tokens, "compressed_expert_bytes_per_gpu": model.compressed_bytes,
+                       "setup_s": round(setup_s, 1),
+                       "execution": "eager" if args.no_graph else "cuda-graph replay of the decode step"},
+            "data": "synthetic (seeded dense bf16 weights N(0,0.02), seeded ternary experts, random prompt ids)",
+            "first_tokens": out[:8].tolist()}), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def main():
     args = parse_args()
-    if args.mode == "layers":
+    if args.mode == "generate":
+        run_generate(args)
+    elif args.mode == "layers":
         run_layers(args)
     elif args.impl == "reference":
         run_reference(args)

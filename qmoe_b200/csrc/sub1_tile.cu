@@ -2,14 +2,15 @@
 // a compressed matrix are decoded ONCE into a dense bf16 tile in shared memory and multiplied with
 // up to 64 tokens by tcgen05.mma, instead of being re-decoded for every group of four tokens.
 //
-//   D[128 rows, 64 tokens] (fp32, tensor memory)  +=  A[128 rows, 64 cols] * B[64 tokens, 64 cols]^T
+//   D[128 rows, 64 tokens] (fp32, tensor memory)  +=  A[128 rows, 128 cols] * B[64 tokens, 128 cols]^T
 //
 // A holds the decoded weights {0, min_r, max_r} as bf16 (the reference's decode-then-bf16-matmul
 // semantics, test.py:176), B the tokens' activations; both are written by ordinary shared stores in
 // the K-major no-swizzle core-matrix layout (8 rows x 16 bytes per core matrix), so no tensor map
-// and no bulk copy is involved.  One CTA of 128 threads owns 128 rows: thread r decodes row r (the
-// same one-thread-per-row walk as the other kernels, restricted to a window of 64 columns per step)
-// and later reads row r of the accumulator from tensor memory.
+// and no bulk copy is involved.  One CTA owns 128 rows: thread r of its first warpgroup decodes row r
+// (the same one-thread-per-row walk as the other kernels, restricted to a window of 128 columns per
+// step) and later reads row r of the accumulator from tensor memory; a second warpgroup clears and
+// fills the tiles one window ahead.
 //
 // Every wait on the MMA-completion mbarrier is bounded; on a timeout the CTA records an error,
 // releases its tensor memory and returns.
@@ -113,44 +114,33 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 }
 
 // ---- kernel ---------------------------------------------------------------------------------------
-// Loads the activations of one 64-column window for this thread's share of the B tile (four 16-byte
-// units) into registers; rows past the token count and columns past the width read as zero.
-__device__ __forceinline__ void load_b_units(const TileArgs &a, int tok0, int ntok, int W, int k0, int tid,
-                                             uint4 (&v)[kTileChunks * kTileN / kTileM]) {
-#pragma unroll
-  for (int i = 0; i < kTileChunks * kTileN / kTileM; i++) {
-    const int u = tid + i * kTileM;
-    const int n = u & (kTileN - 1), c = u >> 6;
-    const int k = k0 + 8 * c;
-    v[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (n < ntok && k < W) {
-      const __nv_bfloat16 *src = a.x + (long long)(tok0 + n) * a.x_stride + k;
-      if (k + 8 <= W && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
-        v[i] = __ldg(reinterpret_cast<const uint4 *>(src));
-      } else {
-        uint16_t t[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) t[j] = (k + j < W) ? __bfloat16_as_ushort(src[j]) : (uint16_t)0;
-        v[i].x = t[0] | ((uint32_t)t[1] << 16);
-        v[i].y = t[2] | ((uint32_t)t[3] << 16);
-        v[i].z = t[4] | ((uint32_t)t[5] << 16);
-        v[i].w = t[6] | ((uint32_t)t[7] << 16);
-      }
-    }
-  }
+constexpr int kTileThreads = 2 * kTileM;  // warps 0-3 decode rows, warps 4-7 stage the tiles
+
+__device__ __forceinline__ void named_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// Two shared-memory stages: while the tensor core multiplies window w, the threads decode window
-// w + 1 into the other stage, and the activations of window w + 1 are already in registers.
-__global__ void __launch_bounds__(kTileM, 2) k_tile_matmul(const TileArgs a) {
+// Two warpgroups and two shared-memory stages.  For window w (128 columns) and stage s = w & 1:
+//   stagers  (threads 128..255): wait until the MMAs that read stage s two windows ago are complete,
+//            zero the A tile, copy the tokens' activations into the B tile, signal "stage s filled";
+//   decoders (threads 0..127):   wait for "stage s filled", scatter the non-zeros of their row into
+//            the A tile, synchronise among themselves, and one thread issues the eight K=16 MMAs and
+//            commits them to the stage's mbarrier.
+// The stagers run up to one window ahead of the decoders, and the tensor core runs behind both.
+__global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs a) {
   constexpr int kABytes = kTileChunks * kTileM * 16;  // [column chunk][row][8 bf16]
   constexpr int kBBytes = kTileChunks * kTileN * 16;  // [column chunk][token][8 bf16]
   constexpr int kBUnits = kTileChunks * kTileN / kTileM;
   extern __shared__ __align__(128) uint8_t tile_smem[];  // A stage 0 | A stage 1 | B stage 0 | B stage 1
   __shared__ __align__(8) uint64_t s_mbar[2];
   __shared__ uint32_t s_tmem;
-  __shared__ int s_fail;
+  __shared__ volatile int s_fail;
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool decoder = tid < kTileM;
+  const int t = decoder ? tid : tid - kTileM;  // index inside the warpgroup
   const uint32_t mbar0 = smem_u32(&s_mbar[0]), mbar1 = smem_u32(&s_mbar[1]);
 
   if (tid == 0) {
@@ -167,158 +157,185 @@ __global__ void __launch_bounds__(kTileM, 2) k_tile_matmul(const TileArgs a) {
   const uint32_t idesc = make_instr_desc(kTileM, kTileN);
   const int n_items = *a.n_items;
   uint32_t uses0 = 0u, uses1 = 0u;  // MMA batches committed per stage; batch n completes phase (n - 1) & 1
-  bool failed = false;
 
-  for (int item = blockIdx.x; item < n_items && !failed; item += gridDim.x) {
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int4 it = a.items[item];
     const qmoe_matrix_desc d = a.descs[it.x];
-    const int row = it.y + tid, tok0 = it.z, ntok = it.w;
+    const int tok0 = it.z, ntok = it.w;
     const int W = d.width;
-    const bool valid_row = row < d.height;
+    const int n_windows = (W + kTileK - 1) / kTileK;
 
-    // this thread's row: span of codes, running position, the (min, max) bf16 bit patterns
-    const uint16_t *codes = a.codes + d.code_base;
-    long long ci = 0, ce = 0;
-    uint32_t mn = 0, mx = 0;
-    if (valid_row) {
-      const int32_t *ro = a.row_off + d.rowoff_base;
-      ci = ro[row];
-      ce = ro[row + 1];
-      ci = ci < 0 ? 0 : (ci > d.n_codes ? d.n_codes : ci);
-      ce = ce < ci ? ci : (ce > d.n_codes ? d.n_codes : ce);
-      const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
-      mn = __bfloat16_as_ushort(mm.x);
-      mx = __bfloat16_as_ushort(mm.y);
-    }
-    int pos = 0, len = 0;
-    uint32_t e = kEntryNull;
-    bool have = false;
-    // Codes are fetched eight at a time (one aligned 128-bit load) and their table entries are looked
-    // up together.  Both loads run ahead of their use: while the entries of chunk c are consumed, the
-    // entries of chunk c + 1 and the codes of chunk c + 2 are already in flight, so the barrier of a
-    // window does not wait on a thread that has just crossed a chunk boundary.
-    const int mis = (int)((reinterpret_cast<uintptr_t>(codes) & 15u) >> 1);
-    const uint16_t *codes_al = codes - mis;
-    const long long end_al = ce + mis;
-    uint32_t ebuf[8], enext[8];
-    uint4 q2 = make_uint4(0u, 0u, 0u, 0u);
-    long long chunk = (ci + mis) >> 3;  // chunk whose entries are in ebuf
-    auto load_codes = [&](long long c) -> uint4 {
-      return (valid_row && c * 8 < end_al) ? __ldg(reinterpret_cast<const uint4 *>(codes_al + c * 8))
-                                           : make_uint4(0u, 0u, 0u, 0u);
-    };
-    auto lookup8 = [&](const uint4 &q, uint32_t (&dst)[8]) {
-      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-      for (int j = 0; j < 8; j++) dst[j] = __ldg(a.tab + chunk_code(w, j));
-    };
-    {
-      const uint4 q0 = load_codes(chunk), q1 = load_codes(chunk + 1);
-      q2 = load_codes(chunk + 2);
-      lookup8(q0, ebuf);
-      lookup8(q1, enext);
-    }
-
-    uint4 bregs[kBUnits];
-    load_b_units(a, tok0, ntok, W, 0, tid, bregs);
-    int window = 0, last_stage = 0;
-    for (int k0 = 0; k0 < W; k0 += kTileK, window++) {
-      const int k1 = k0 + kTileK;
-      const int st = window & 1;
-      uint8_t *A = tile_smem + st * kABytes, *B = tile_smem + 2 * kABytes + st * kBBytes;
-      const uint32_t mbar = st ? mbar1 : mbar0;
-      // 0. the stage is free once the MMAs that read it two windows ago have completed
-      const uint32_t used = st ? uses1 : uses0;
-      if (used > 0 && !mbar_wait(mbar, (used - 1u) & 1u)) atomicExch(&s_fail, 1);
-      tc_fence_after();
-      // 1. clear this thread's row of the A tile, store its share of the B tile, request the next one
-#pragma unroll
-      for (int c = 0; c < kTileChunks; c++)
-        *reinterpret_cast<uint4 *>(A + c * (kTileM * 16) + tid * 16) = make_uint4(0u, 0u, 0u, 0u);
+    if (!decoder) {
+      // ---- stagers --------------------------------------------------------------------------------
+      const __nv_bfloat16 *src[kBUnits];
+      bool live[kBUnits];
 #pragma unroll
       for (int i = 0; i < kBUnits; i++) {
-        const int u = tid + i * kTileM;
-        *reinterpret_cast<uint4 *>(B + (u >> 6) * (kTileN * 16) + (u & (kTileN - 1)) * 16) = bregs[i];
+        const int u = t + i * kTileM;
+        const int n = u & (kTileN - 1), c = u >> 6;
+        live[i] = n < ntok;
+        src[i] = a.x + (long long)(tok0 + (live[i] ? n : 0)) * a.x_stride + 8 * c;
       }
-      if (k1 < W) load_b_units(a, tok0, ntok, W, k1, tid, bregs);
-      // 2. decode the window [k0, k1) of the row; a code that straddles k1 is kept for the next window
-      if (valid_row) {
-        for (;;) {
-          if (!have) {
-            if (ci >= ce || pos >= k1) break;
-            const long long ia = ci + mis;
-            if ((ia >> 3) != chunk) {  // codes are consumed in order: this is chunk + 1
-              chunk = ia >> 3;
+      for (int w = 0; w < n_windows; w++) {
+        const int st = w & 1, k0 = w * kTileK;
+        uint8_t *A = tile_smem + st * kABytes, *B = tile_smem + 2 * kABytes + st * kBBytes;
+        uint4 v[kBUnits];
 #pragma unroll
-              for (int j = 0; j < 8; j++) ebuf[j] = enext[j];
-              lookup8(q2, enext);
-              q2 = load_codes(chunk + 2);
-            }
-            e = ebuf[ia & 7];
-            len = 2 * (int)entry_len(e);
-            have = true;
-          }
+        for (int i = 0; i < kBUnits; i++) {  // issue the loads first: they overlap the wait below
+          const int k = k0 + 8 * ((t + i * kTileM) >> 6);
+          const __nv_bfloat16 *p = src[i] + k0;
+          v[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (live[i] && k < W) {
+            if (k + 8 <= W && (reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+              v[i] = __ldg(reinterpret_cast<const uint4 *>(p));
+            } else {
+              uint16_t h[8];
 #pragma unroll
-          for (int k = 0; k < 3; k++) {
-            const uint32_t o = entry_nz_pos(e, k);
-            const int p = pos + (int)o;
-            if (o < 0x80u && p >= k0 && p < k1 && p < W) {
-              const int kk = p - k0;
-              *reinterpret_cast<uint16_t *>(A + (kk >> 3) * (kTileM * 16) + tid * 16 + (kk & 7) * 2) =
-                  (uint16_t)((e & (0x10u << k)) ? mx : mn);
+              for (int j = 0; j < 8; j++) h[j] = (k + j < W) ? __bfloat16_as_ushort(p[j]) : (uint16_t)0;
+              v[i].x = h[0] | ((uint32_t)h[1] << 16);
+              v[i].y = h[2] | ((uint32_t)h[3] << 16);
+              v[i].z = h[4] | ((uint32_t)h[5] << 16);
+              v[i].w = h[6] | ((uint32_t)h[7] << 16);
             }
           }
-          if (pos + len > k1) break;
-          pos += len;
-          ci++;
-          have = false;
         }
-      }
-      // 3. make the tiles visible to the tensor core; one thread issues four K=16 steps
-      fence_async_proxy();
-      __syncthreads();
-      if (s_fail) {
-        failed = true;
-        break;
-      }
-      if (tid == 0) {
+        const uint32_t used = st ? uses1 : uses0;
+        if (used > 0 && !s_fail && !mbar_wait(st ? mbar1 : mbar0, (used - 1u) & 1u)) s_fail = 1;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(A), b_addr = smem_u32(B);
 #pragma unroll
-        for (int s = 0; s < kTileK / 16; s++) {
-          const uint64_t da = make_smem_desc(a_addr + s * 2 * (kTileM * 16), kTileM * 16, 128);
-          const uint64_t db = make_smem_desc(b_addr + s * 2 * (kTileN * 16), kTileN * 16, 128);
-          mma_bf16(tmem, da, db, idesc, (k0 > 0 || s > 0) ? 1u : 0u);
+        for (int c = 0; c < kTileChunks; c++)
+          *reinterpret_cast<uint4 *>(A + c * (kTileM * 16) + t * 16) = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < kBUnits; i++) {
+          const int u = t + i * kTileM;
+          *reinterpret_cast<uint4 *>(B + (u >> 6) * (kTileN * 16) + (u & (kTileN - 1)) * 16) = v[i];
         }
-        mma_commit(mbar);
+        fence_async_proxy();
+        named_arrive(1 + st, kTileThreads);
+        if (st) uses1++;
+        else uses0++;
       }
-      if (st) uses1++;
-      else uses0++;
-      last_stage = st;
-    }
-    if (failed) break;
+    } else {
+      // ---- decoders -------------------------------------------------------------------------------
+      const int row = it.y + t;
+      const bool valid_row = row < d.height;
+      const uint16_t *codes = a.codes + d.code_base;
+      int ci = 0, ce = 0;
+      uint32_t mn = 0, mx = 0;
+      if (valid_row) {
+        const int32_t *ro = a.row_off + d.rowoff_base;
+        long long b = ro[row], e2 = ro[row + 1];
+        b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+        e2 = e2 < b ? b : (e2 > d.n_codes ? d.n_codes : e2);
+        ci = (int)b;
+        ce = (int)e2;
+        const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
+        mn = __bfloat16_as_ushort(mm.x);
+        mx = __bfloat16_as_ushort(mm.y);
+      }
+      // Codes are fetched eight at a time (one aligned 128-bit load) and their table entries are
+      // looked up together; both run ahead of their use: while the entries of chunk c are consumed,
+      // the entries of chunk c + 1 and the codes of chunk c + 2 are already in flight.
+      const int mis = (int)((reinterpret_cast<uintptr_t>(codes) & 15u) >> 1);
+      const uint16_t *codes_al = codes - mis;
+      const int end_al = ce + mis;
+      uint32_t ebuf[8], enext[8];
+      int chunk = (ci + mis) >> 3;  // chunk whose entries are in ebuf
+      auto load_codes = [&](int c) -> uint4 {
+        return (valid_row && c * 8 < end_al) ? __ldg(reinterpret_cast<const uint4 *>(codes_al + (long long)c * 8))
+                                             : make_uint4(0u, 0u, 0u, 0u);
+      };
+      auto lookup8 = [&](const uint4 &q, uint32_t (&dst)[8]) {
+        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) dst[j] = __ldg(a.tab + chunk_code(w4, j));
+      };
+      uint4 q2;
+      {
+        const uint4 q0 = load_codes(chunk), q1 = load_codes(chunk + 1);
+        q2 = load_codes(chunk + 2);
+        lookup8(q0, ebuf);
+        lookup8(q1, enext);
+      }
+      int pos = 0, len = 0;
+      uint32_t e = kEntryNull;
+      bool have = false;
 
-    // all MMAs of the item are complete when the last commit has arrived
-    if (!mbar_wait(last_stage ? mbar1 : mbar0, ((last_stage ? uses1 : uses0) - 1u) & 1u)) atomicExch(&s_fail, 1);
-    tc_fence_after();
-    __syncthreads();
-    if (s_fail) {
-      failed = true;
-      break;
+      for (int w = 0; w < n_windows; w++) {
+        const int st = w & 1, k0 = w * kTileK, k1 = k0 + kTileK;
+        uint8_t *A = tile_smem + st * kABytes;
+        named_sync(1 + st, kTileThreads);  // the stage is zeroed and holds the activations
+        if (valid_row) {
+          for (;;) {
+            if (!have) {
+              if (ci >= ce || pos >= k1) break;
+              const int ia = ci + mis;
+              if ((ia >> 3) != chunk) {  // codes are consumed in order: this is chunk + 1
+                chunk = ia >> 3;
+#pragma unroll
+                for (int j = 0; j < 8; j++) ebuf[j] = enext[j];
+                lookup8(q2, enext);
+                q2 = load_codes(chunk + 2);
+              }
+              e = ebuf[ia & 7];
+              len = 2 * (int)entry_len(e);
+              have = true;
+            }
+#pragma unroll
+            for (int k = 0; k < 3; k++) {
+              const uint32_t o = entry_nz_pos(e, k);
+              const int kk = pos + (int)o - k0;
+              if (o < 0x80u && (unsigned)kk < (unsigned)kTileK)
+                *reinterpret_cast<uint16_t *>(A + (kk >> 3) * (kTileM * 16) + t * 16 + (kk & 7) * 2) =
+                    (uint16_t)((e & (0x10u << k)) ? mx : mn);
+            }
+            if (pos + len > k1) break;  // straddles the window: applied again in the next one
+            pos += len;
+            ci++;
+            have = false;
+          }
+        }
+        fence_async_proxy();
+        named_sync(3, kTileM);
+        if (tid == 0) {
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(A), b_addr = smem_u32(tile_smem + 2 * kABytes + st * kBBytes);
+#pragma unroll
+          for (int s = 0; s < kTileK / 16; s++) {
+            const uint64_t da = make_smem_desc(a_addr + s * 2 * (kTileM * 16), kTileM * 16, 128);
+            const uint64_t db = make_smem_desc(b_addr + s * 2 * (kTileN * 16), kTileN * 16, 128);
+            mma_bf16(tmem, da, db, idesc, (w > 0 || s > 0) ? 1u : 0u);
+          }
+          mma_commit(st ? mbar1 : mbar0);
+        }
+        if (st) uses1++;
+        else uses0++;
+      }
+      // all MMAs of the item are complete when the last commit has arrived
+      const int last = (n_windows - 1) & 1;
+      const uint32_t used = last ? uses1 : uses0;
+      if (!s_fail && !mbar_wait(last ? mbar1 : mbar0, (used - 1u) & 1u)) s_fail = 1;
+      tc_fence_after();
     }
-    // epilogue: row `tid` of the accumulator -> y[token][row]
-    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
+    __syncthreads();
+    if (s_fail) break;  // uniform: read after the barrier
+
+    if (decoder) {  // epilogue: row t of the accumulator -> y[token][row]
+      const int row = it.y + t;
+      const bool valid_row = row < d.height;
+      const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
-    for (int j = 0; j < kTileN / 16; j++) {
-      uint32_t v[16];
-      tmem_ld16(taddr + j * 16, v);
+      for (int j = 0; j < kTileN / 16; j++) {
+        uint32_t v[16];
+        tmem_ld16(taddr + j * 16, v);
 #pragma unroll
-      for (int i = 0; i < 16; i++) {
-        const int n = j * 16 + i;
-        if (valid_row && n < ntok) {
-          float r = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
-          if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
-          a.y[(long long)(tok0 + n) * a.y_stride + row] = __float2bfloat16_rn(r);
+        for (int i = 0; i < 16; i++) {
+          const int n = j * 16 + i;
+          if (valid_row && n < ntok) {
+            float r = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+            if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
+            a.y[(long long)(tok0 + n) * a.y_stride + row] = __float2bfloat16_rn(r);
+          }
         }
       }
     }
@@ -327,11 +344,13 @@ __global__ void __launch_bounds__(kTileM, 2) k_tile_matmul(const TileArgs a) {
     tc_fence_after();
   }
 
-  if (failed) {
+  if (s_fail) {
     if (tid == 0 && a.status != nullptr) atomicAdd(a.status, 1);
     // one more bounded wait per stage for MMAs that may still be in flight
-    if (uses0 > 0) mbar_wait(mbar0, (uses0 - 1u) & 1u);
-    if (uses1 > 0) mbar_wait(mbar1, (uses1 - 1u) & 1u);
+    if (tid == 0) {
+      if (uses0 > 0) mbar_wait(mbar0, (uses0 - 1u) & 1u);
+      if (uses1 > 0) mbar_wait(mbar1, (uses1 - 1u) & 1u);
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -416,7 +435,7 @@ int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t 
     QMOE_CUDA(cudaFuncSetAttribute(k_tile_matmul, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     configured[device] = true;
   }
-  QMOE_LAUNCH(k_tile_matmul, grid, kTileM, kSmem, stream, a);
+  QMOE_LAUNCH(k_tile_matmul, grid, kTileThreads, kSmem, stream, a);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

@@ -1,0 +1,151 @@
+"""A Switch-shaped decoder stack around the compressed MoE layer, for end-to-end generation timing.
+
+The reference times generation through HuggingFace's Switch Transformers (sub1.py:365-385) with
+published compressed checkpoints; neither is available offline, so this module is a self-contained
+stand-in with the same structure where it matters for the hot path: every block is
+RMS-norm -> multi-head self-attention with a KV cache -> RMS-norm -> top-1 MoE FFN over compressed
+experts, with residual connections, seeded random dense weights (bf16, N(0, 0.02)) and seeded
+ternary experts.  Dense parts use torch (cuBLAS / SDPA); the MoE FFN is this package's grouped path.
+
+Expert parallelism for generation: the token stream is replicated (batch 1), every rank holds
+``n_experts / world`` experts of every layer, computes the FFN of the tokens routed to its own
+experts, and an all-reduce sums the disjoint contributions -- for one token per step that is one
+small all-reduce per layer instead of two all-to-alls.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import sub1, synth
+
+
+class ReplicatedTokenMoE:
+    """Top-1 MoE over the local experts of every rank, for tokens that all ranks hold.
+
+    Same arithmetic as :class:`qmoe_b200.sub1.FasterMLP` (sub1.py:306-321); a token whose expert
+    lives on another rank contributes zeros here and receives its result through the all-reduce."""
+
+    def __init__(self, router_weight: torch.Tensor, store, n_experts: int, rank: int = 0, world: int = 1,
+                 group=None, expert_capacity: int = 1024):
+        self.store, self.n_experts, self.rank, self.world, self.group = store, n_experts, rank, world, group
+        self.local = n_experts // world
+        self.capacity = expert_capacity
+        self.router = sub1.RouterClassifier(router_weight, store.device)
+
+    def __call__(self, hidden: torch.Tensor) -> torch.Tensor:
+        n, d = hidden.shape
+        choice, prob = sub1.route_top1(self.router(hidden).contiguous())
+        expert, _, _, _ = sub1.rank_buckets(choice, self.n_experts, n, self.capacity)
+        lo = self.rank * self.local
+        mine = (expert >= lo) & (expert < lo + self.local)
+        local_choice = torch.where(mine, expert - lo, torch.full_like(expert, -1))
+        bucket, rank, _, offsets = sub1.rank_buckets(local_choice, self.local, n, n)
+        xs = torch.empty_like(hidden)
+        slot = sub1.permute_rows(bucket, rank, offsets, hidden, xs)
+        ys = sub1.grouped_ffn(self.store, offsets, xs, n)
+        if self.world == 1:
+            kept_slot = torch.where(expert >= 0, slot, torch.full_like(slot, -1))
+            return sub1.combine(ys, hidden, kept_slot, prob)
+        part = torch.empty_like(hidden)
+        sub1.unpermute_rows(ys, slot, part)                      # zeros for tokens of other ranks
+        dist.all_reduce(part, group=self.group)
+        # tokens dropped by the capacity rule pass through (sub1.py:312,318)
+        ident = torch.arange(n, dtype=torch.int32, device=hidden.device)
+        return sub1.combine(part, hidden, torch.where(expert >= 0, ident, torch.full_like(ident, -1)), prob)
+
+
+def _rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class SwitchDecoderLM:
+    """``n_layers`` blocks of (self-attention, MoE FFN); greedy generation with a static KV cache."""
+
+    def __init__(self, d_model: int, d_ff: int, n_experts: int, n_layers: int, n_heads: int, vocab: int,
+                 max_len: int, device, seed: int = 0, rank: int = 0, world: int = 1, group=None):
+        self.d, self.h, self.hd, self.L, self.vocab, self.max_len = d_model, n_heads, d_model // n_heads, n_layers, vocab, max_len
+        self.dev = torch.device(device)
+        g = torch.Generator().manual_seed(seed * 9973 + 1)
+
+        def dense(*shape):
+            return (torch.randn(*shape, generator=g) * 0.02).bfloat16().to(self.dev)
+
+        d_attn = self.h * self.hd
+        self.embed = dense(vocab, d_model)
+        self.lm_head = dense(vocab, d_model)
+        self.final_norm = torch.ones(d_model, dtype=torch.bfloat16, device=self.dev)
+        self.blocks: List[dict] = []
+        local = n_experts // world
+        for layer in range(n_layers):
+            ids = [layer * n_experts + e for e in range(rank * local, (rank + 1) * local)]   # distinct seeds per layer
+            store = synth.build_store(d_model, d_ff, ids, seed, self.dev)
+            router = (torch.randn(n_experts, d_model, generator=g) / math.sqrt(d_model)).bfloat16().float()
+            self.blocks.append({
+                "ln1": torch.ones(d_model, dtype=torch.bfloat16, device=self.dev),
+                "ln2": torch.ones(d_model, dtype=torch.bfloat16, device=self.dev),
+                "wqkv": dense(3 * d_attn, d_model), "wo": dense(d_model, d_attn),
+                "moe": ReplicatedTokenMoE(router, store, n_experts, rank, world, group),
+            })
+        self.k_cache = torch.zeros(n_layers, self.h, max_len, self.hd, dtype=torch.bfloat16, device=self.dev)
+        self.v_cache = torch.zeros_like(self.k_cache)
+
+    @property
+    def compressed_bytes(self) -> int:
+        return sum(b["moe"].store.compressed_bytes for b in self.blocks)
+
+    def forward(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """``ids`` int64[n] at cache positions ``pos`` int64[n] (contiguous, ascending); returns the
+        logits fp32[n, vocab].  Attention sees cache positions <= the query's own position; the mask
+        is built from ``pos`` on the device, so the same code serves prefill, eager decoding and
+        CUDA-graph replay of a decode step."""
+        n = ids.shape[0]
+        x = self.embed[ids]
+        all_pos = torch.arange(self.max_len, device=self.dev)
+        mask = all_pos[None, :] <= pos[:, None]                                    # [n, max_len]
+        for i, b in enumerate(self.blocks):
+            hn = _rms_norm(x, b["ln1"])
+            qkv = (hn @ b["wqkv"].t()).view(n, 3, self.h, self.hd)
+            self.k_cache[i].index_copy_(1, pos, qkv[:, 1].transpose(0, 1))
+            self.v_cache[i].index_copy_(1, pos, qkv[:, 2].transpose(0, 1))
+            q = qkv[:, 0].transpose(0, 1)                                            # [h, n, hd]
+            att = F.scaled_dot_product_attention(q.unsqueeze(0), self.k_cache[i].unsqueeze(0),
+                                                 self.v_cache[i].unsqueeze(0), attn_mask=mask[None, None])
+            x = x + att[0].transpose(0, 1).reshape(n, -1) @ b["wo"].t()
+            x = x + b["moe"](_rms_norm(x, b["ln2"]).contiguous())
+        return (_rms_norm(x, self.final_norm) @ self.lm_head.t()).float()
+
+    @torch.no_grad()
+    def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True) -> torch.Tensor:
+        """Greedy generation: prefill the prompt, then ``n_new`` single-token steps."""
+        p = prompt.shape[0]
+        assert p + n_new <= self.max_len
+        logits = self.forward(prompt.to(self.dev), torch.arange(p, device=self.dev))
+        tok = logits[-1].argmax().reshape(1)
+        out = [tok]
+        step_ids = tok.clone()
+        step_pos = torch.full((1,), p, dtype=torch.int64, device=self.dev)
+        graph = None
+        if use_graph and n_new > 4:
+            from .graph import GraphedStep
+            try:
+                graph = GraphedStep(lambda t: self.forward(t, step_pos)[-1].argmax().reshape(1), step_ids)
+            except Exception:
+                graph = None
+        for _ in range(n_new - 1):
+            step_ids.copy_(tok)
+            if graph is not None:
+                graph.static_in.copy_(step_ids)
+                tok = graph.replay().clone()
+            else:
+                tok = self.forward(step_ids, step_pos)[-1].argmax().reshape(1)
+            out.append(tok)
+            step_pos += 1
+        if graph is not None:
+            graph.close()
+        return torch.cat(out)
