@@ -554,6 +554,7 @@ def run_generate(args):
                        "setup_s": round(setup_s, 1),
                        "execution": "eager" if args.no_graph else "cuda-graph replay of the decode step"},
             "data": "synthetic (seeded dense bf16 weights N(0,0.02), seeded ternary experts, random prompt ids)",
+            "timing_last_sample": getattr(model, "last_timing", None),
             "first_tokens": out[:8].tolist()}), flush=True)
     if world > 1:
         dist.barrier()

@@ -34,6 +34,11 @@ static inline int rows_per_chunk(int height, int rows_per_item) {
   rpc = (rpc + 31) / 32 * 32;
   return rpc;
 }
+__device__ __forceinline__ int rows_per_chunk_dev(int height, int rows_per_item) {
+  const int chunks = (height + rows_per_item - 1) / rows_per_item;
+  const int rpc = (height + chunks - 1) / chunks;
+  return (rpc + 31) / 32 * 32;
+}
 static inline int chunk_count(int height, int rows_per_item) {
   const int rpc = rows_per_chunk(height, rows_per_item);
   return (height + rpc - 1) / rpc;
@@ -527,73 +532,112 @@ int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cu
 }
 
 // ---- grouped expert FFN -------------------------------------------------------------------------
-// Work buffer layout: int header[16] | int4 items_wi[max_slots * chunks_wi] | int4 items_wo[...] |
-// tile items of wi | tile items of wo.
+// Work buffer layout: int header[16] | int4 items_wi[cap_wi] | int4 items_wo[cap_wo] | tile items of
+// wi | tile items of wo, with cap = max_slots * ceil(height / 1024) + kExtraItems.
 // header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter,
 // [4] / [5] = tile items of wi / wo, [8] = timeouts seen by the tile kernels.
+//
+// Item granularity is chosen here, on the device, from the number of (expert, token group) pairs:
+// a full layer (hundreds of pairs) uses blocks of up to 1024 rows, one row per thread of the
+// persistent CTAs; when only a few experts are active (one token per step while generating) the rows
+// are cut into smaller blocks so that about two items per SM exist and every SM takes part, instead
+// of nine CTAs walking thousand-row blocks.
+constexpr int kExtraItems = 1024;
+
+struct WorkPhase {
+  int4 *items;
+  int capacity;  // entries available in `items`
+  int height;    // rows of the phase's matrices (d_ff for wi, d_model for wo)
+  int which;     // 0 = wi (matrix 2e), 1 = wo (matrix 2e + 1)
+};
+
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
-                                                     int d_model, int d_ff, int rpc_wi, int chunks_wi,
-                                                     int rpc_wo, int chunks_wo, int max_slots, int tile_min,
-                                                     int *header, int4 *items_wi, int4 *items_wo) {
+                                                     int max_slots, int tile_min, int target_items,
+                                                     int *header, WorkPhase p0, WorkPhase p1) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
+  __shared__ int s_total;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) s_base = 0;
-  __syncthreads();
-  for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
-    const int e = e0 + tid;
-    int first = 0, count = 0;
+  auto group_count = [&](int e, int &first, int &count) {
+    first = 0;
+    count = 0;
     if (e < n_experts) {
       first = offsets[e];
       count = offsets[e + 1] - first;
       count = count < 0 ? 0 : count;
       if (tile_min > 0 && count >= tile_min) count = 0;  // handled by the tensor-core tile path
     }
-    const int groups = (count + kMaxGroup - 1) / kMaxGroup;
-    // exclusive scan of `groups` over the block
-    int incl = groups;
+    return (count + kMaxGroup - 1) / kMaxGroup;
+  };
+  // pass 1: total number of (expert, token group) pairs
+  if (tid == 0) s_total = 0;
+  __syncthreads();
+  {
+    int mine = 0, first, count;
+    for (int e = tid; e < n_experts; e += blockDim.x) mine += group_count(e, first, count);
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0 && mine) atomicAdd(&s_total, mine);
+  }
+  __syncthreads();
+  const int total = min(s_total, max_slots);
+
+  for (int phase = 0; phase < 2; phase++) {
+    const WorkPhase p = phase == 0 ? p0 : p1;
+    // rows per item: as many as a CTA has threads, fewer while that leaves SMs without work
+    int rpc = rows_per_chunk_dev(p.height, kGroupedThreads);
+    if (total > 0) {
+      const long long want = ((long long)total * p.height + target_items - 1) / target_items;
+      int fine = (int)((want + 31) / 32 * 32);
+      fine = fine < 32 ? 32 : fine;
+      if (fine < rpc && (long long)total * ((p.height + fine - 1) / fine) <= p.capacity) rpc = fine;
     }
-    if (lane == 31) s_warp[warp] = incl;
+    const int chunks = (p.height + rpc - 1) / rpc;
+    if (tid == 0) s_base = 0;
     __syncthreads();
-    if (warp == 0) {
-      int w = s_warp[lane];
+    for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
+      const int e = e0 + tid;
+      int first, count;
+      const int groups = group_count(e, first, count);
+      // exclusive scan of `groups` over the block
+      int incl = groups;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += v;
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
       }
-      s_warp[lane] = w;
+      if (lane == 31) s_warp[warp] = incl;
+      __syncthreads();
+      if (warp == 0) {
+        int w = s_warp[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, w, o);
+          if (lane >= o) w += v;
+        }
+        s_warp[lane] = w;
+      }
+      __syncthreads();
+      const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
+      for (int g = 0; g < groups; g++) {
+        const int gi = base + g;
+        if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
+        const int tok0 = first + g * kMaxGroup;
+        const int ntok = min(kMaxGroup, count - g * kMaxGroup);
+        for (int k = 0; k < chunks; k++) {
+          const int row0 = k * rpc;
+          p.items[(size_t)gi * chunks + k] = make_int4(2 * e + p.which, row0, tok0, min(rpc, p.height - row0) | (ntok << 16));
+        }
+      }
+      __syncthreads();
+      if (tid == 0) s_base += s_warp[31];
+      __syncthreads();
+    }
+    if (tid == 0) {
+      header[2 * phase] = min(s_base, max_slots) * chunks;
+      header[2 * phase + 1] = 0;
     }
     __syncthreads();
-    const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
-    for (int g = 0; g < groups; g++) {
-      const int gi = base + g;
-      if (gi >= max_slots) break;  // cannot happen while offsets[n_experts] <= max_slots
-      const int tok0 = first + g * kMaxGroup;
-      const int ntok = min(kMaxGroup, count - g * kMaxGroup);
-      for (int k = 0; k < chunks_wi; k++) {
-        const int row0 = k * rpc_wi;
-        items_wi[(size_t)gi * chunks_wi + k] = make_int4(2 * e, row0, tok0, min(rpc_wi, d_ff - row0) | (ntok << 16));
-      }
-      for (int k = 0; k < chunks_wo; k++) {
-        const int row0 = k * rpc_wo;
-        items_wo[(size_t)gi * chunks_wo + k] = make_int4(2 * e + 1, row0, tok0, min(rpc_wo, d_model - row0) | (ntok << 16));
-      }
-    }
-    __syncthreads();
-    if (tid == 0) s_base += s_warp[31];
-    __syncthreads();
-  }
-  if (tid == 0) {
-    const int total = min(s_base, max_slots);
-    header[0] = total * chunks_wi;
-    header[1] = 0;
-    header[2] = total * chunks_wo;
-    header[3] = 0;
   }
 }
 
@@ -629,9 +673,13 @@ int set_tile_min_tokens(int tokens) {
   return before;
 }
 
+static int64_t item_capacity(int max_slots, int height) {
+  return (int64_t)max_slots * chunk_count(height, kGroupedThreads) + kExtraItems;
+}
+
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
-  return 64 + (int64_t)max_slots * (chunk_count(d_ff, kGroupedThreads) + chunk_count(d_model, kGroupedThreads)) *
-                  (int64_t)sizeof(int4) + tile_work_bytes(max_slots, d_model, d_ff);
+  return 64 + (item_capacity(max_slots, d_ff) + item_capacity(max_slots, d_model)) * (int64_t)sizeof(int4) +
+         tile_work_bytes(max_slots, d_model, d_ff);
 }
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
@@ -640,15 +688,21 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                        int max_slots, int d_model, int d_ff, int device, cudaStream_t stream) {
   int rc = ensure_smem_limits(device);
   if (rc) return rc;
-  const int chunks_wi = chunk_count(d_ff, kGroupedThreads), chunks_wo = chunk_count(d_model, kGroupedThreads);
-  const int rpc_wi = rows_per_chunk(d_ff, kGroupedThreads), rpc_wo = rows_per_chunk(d_model, kGroupedThreads);
+  const int sms = sm_count(device);
   int *header = reinterpret_cast<int *>(work);
-  int4 *items_wi = reinterpret_cast<int4 *>(reinterpret_cast<char *>(work) + 64);
-  int4 *items_wo = items_wi + (size_t)max_slots * chunks_wi;
+  WorkPhase ph[2];
+  ph[0].items = reinterpret_cast<int4 *>(reinterpret_cast<char *>(work) + 64);
+  ph[0].capacity = (int)item_capacity(max_slots, d_ff);
+  ph[0].height = d_ff;
+  ph[0].which = 0;
+  ph[1].items = ph[0].items + ph[0].capacity;
+  ph[1].capacity = (int)item_capacity(max_slots, d_model);
+  ph[1].height = d_model;
+  ph[1].which = 1;
   const int tile_min = tab.conforming ? tile_min_tokens() : 0;
-  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, d_model, d_ff, rpc_wi, chunks_wi, rpc_wo, chunks_wo, max_slots, tile_min, header, items_wi, items_wo);
+  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, 2 * sms, header, ph[0], ph[1]);
   QMOE_CUDA(cudaGetLastError());
-  int4 *tile_wi = items_wo + (size_t)max_slots * chunks_wo;
+  int4 *tile_wi = ph[1].items + ph[1].capacity;
   int4 *tile_wo = tile_wi + (size_t)tile_cap_blocks(max_slots) * ((d_ff + 127) / 128);
   if (tile_min > 0) {
     rc = launch_build_tile_work(offsets, n_experts, tile_min, d_model, d_ff, max_slots, header, tile_wi, tile_wo, stream);
@@ -662,7 +716,6 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   a.row_off = row_off;
   a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
   a.descs = descs;
-  const int sms = sm_count(device);
   cudaEvent_t *events = nullptr;
   const bool timed = profile_begin(device, &events);
 
@@ -672,14 +725,10 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     a.y = reinterpret_cast<__nv_bfloat16 *>(phase == 0 ? hs : ys);
     a.x_stride = width;
     a.y_stride = phase == 0 ? d_ff : d_model;
-    a.items = phase == 0 ? items_wi : items_wo;
+    a.items = ph[phase].items;
     a.header = header + 2 * phase;
     a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
     const size_t smem = grouped_smem_bytes(width, kMaxGroup);
-    const long long max_items = (long long)max_slots * (phase == 0 ? chunks_wi : chunks_wo);
-    long long grid = sms;  // the 160 KB table allows one CTA per SM
-    grid = grid > max_items ? max_items : grid;
-    grid = grid < 1 ? 1 : grid;
     if (tile_min > 0) {
       const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
       rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
@@ -687,11 +736,12 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
       if (rc) return rc;
     }
+    const unsigned grid = (unsigned)sms;  // the 160 KB table allows one CTA per SM
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
     if (tab.conforming)
-      QMOE_LAUNCH(k_matmul_grouped<false>, (unsigned)grid, kGroupedThreads, smem, stream, a);
+      QMOE_LAUNCH(k_matmul_grouped<false>, grid, kGroupedThreads, smem, stream, a);
     else
-      QMOE_LAUNCH(k_matmul_grouped<true>, (unsigned)grid, kGroupedThreads, smem, stream, a);
+      QMOE_LAUNCH(k_matmul_grouped<true>, grid, kGroupedThreads, smem, stream, a);
     QMOE_CUDA(cudaGetLastError());
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }

@@ -123,10 +123,15 @@ class SwitchDecoderLM:
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True) -> torch.Tensor:
         """Greedy generation: prefill the prompt, then ``n_new`` single-token steps."""
+        import time
         p = prompt.shape[0]
         assert p + n_new <= self.max_len
+        torch.cuda.synchronize(self.dev)
+        t_start = time.perf_counter()
         logits = self.forward(prompt.to(self.dev), torch.arange(p, device=self.dev))
         tok = logits[-1].argmax().reshape(1)
+        torch.cuda.synchronize(self.dev)
+        t_prefill = time.perf_counter()
         out = [tok]
         step_ids = tok.clone()
         step_pos = torch.full((1,), p, dtype=torch.int64, device=self.dev)
@@ -135,8 +140,13 @@ class SwitchDecoderLM:
             from .graph import GraphedStep
             try:
                 graph = GraphedStep(lambda t: self.forward(t, step_pos)[-1].argmax().reshape(1), step_ids)
-            except Exception:
+            except Exception as exc:  # keep generating eagerly, but say so
+                import warnings
+                warnings.warn(f"CUDA-graph capture of the decode step failed, decoding eagerly: {exc!r}")
                 graph = None
+        self.last_generate_used_graph = graph is not None
+        torch.cuda.synchronize(self.dev)
+        t_capture = time.perf_counter()
         for _ in range(n_new - 1):
             step_ids.copy_(tok)
             if graph is not None:
@@ -146,6 +156,10 @@ class SwitchDecoderLM:
                 tok = self.forward(step_ids, step_pos)[-1].argmax().reshape(1)
             out.append(tok)
             step_pos += 1
+        torch.cuda.synchronize(self.dev)
+        t_end = time.perf_counter()
+        self.last_timing = {"prefill_s": t_prefill - t_start, "graph_capture_s": t_capture - t_prefill,
+                            "decode_s": t_end - t_capture, "decode_steps": n_new - 1}
         if graph is not None:
             graph.close()
         return torch.cat(out)

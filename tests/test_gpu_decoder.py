@@ -56,5 +56,6 @@ def test_decoder_blocks_match_dense_reference_and_graph_decoding():
     assert err <= 2e-2, err                                  # two blocks of bf16 arithmetic
     eager = model.generate(ids, 10, use_graph=False)
     graphed = model.generate(ids, 10, use_graph=True)
+    assert model.last_generate_used_graph
     assert torch.equal(eager, graphed)
     assert eager.shape == (10,) and int(eager.max()) < 512
