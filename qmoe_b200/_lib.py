@@ -74,6 +74,9 @@ SIGNATURES = {
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
     "qmoe_moe_set_tile_min_tokens": (_I, [_I]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_interleave_count": (_I, [_P, _P, _P, _I, _P, _I, _P]),
+    "qmoe_moe_interleave_emit": (_I, [_P, _P, _P, _I, _P, _P, _I, _P]),
     "qmoe_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_launch_count": (_L, []),
     "qmoe_profile_enable": (_I, [_I]),

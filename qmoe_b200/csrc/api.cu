@@ -81,8 +81,13 @@ int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
 int set_tile_min_tokens(int tokens);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
-                       const int32_t *offsets, const void *xs, void *hs, void *ys, void *work, int n_experts,
-                       int max_slots, int d_model, int d_ff, int device, cudaStream_t stream);
+                       const void *il_codes, const int64_t *blk_base, const int32_t *offsets, const void *xs,
+                       void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
+                       int device, cudaStream_t stream);
+int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+                            int32_t *blk_units, cudaStream_t stream);
+int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
+                           int n_matrices, const int64_t *blk_base, void *il, cudaStream_t stream);
 int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
                         cudaStream_t stream);
 int launch_pack_emit(const int32_t *w_tern, const int32_t *row_off, uint16_t *w_comp, int height, int width,
@@ -425,28 +430,95 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
   return moe_work_bytes(max_slots, d_model, d_ff);
 }
 
-int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
-                         const void *minmax_dev, const qmoe_matrix_desc *descs_dev, const int32_t *offsets_dev,
-                         const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
-                         int max_slots, int d_model, int d_ff, int device, void *stream) {
-  QMOE_REQUIRE(dec_dev && codes_dev && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev,
-               "null device pointer");
-  QMOE_REQUIRE(n_experts >= 1 && max_slots >= 0 && d_model >= 1 && d_ff >= 1, "bad shape");
+static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint16_t *codes_dev,
+                             const int32_t *row_off_dev, const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
+                             const void *il_dev, const int64_t *blk_base_dev, const int32_t *offsets_dev,
+                             const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
+                             int max_slots, int d_model, int d_ff, int device, void *stream) {
+  if (!(dec_dev && codes_dev && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev)) {
+    set_error("%s: null device pointer", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (!(n_experts >= 1 && max_slots >= 0 && d_model >= 1 && d_ff >= 1)) {
+    set_error("%s: bad shape", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
   if (d_model > QMOE_MAX_WIDTH || d_ff > QMOE_MAX_WIDTH) {
-    set_error("%s: d_model/d_ff exceed QMOE_MAX_WIDTH (%d)", __func__, QMOE_MAX_WIDTH);
+    set_error("%s: d_model/d_ff exceed QMOE_MAX_WIDTH (%d)", fn, QMOE_MAX_WIDTH);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  if (il_dev && (d_model % 32 != 0 || d_ff % 32 != 0)) {
+    set_error("%s: lane-interleaved streams need d_model and d_ff to be multiples of 32", fn);
     return QMOE_ERR_UNSUPPORTED;
   }
   if (max_slots == 0) return QMOE_OK;
-  QMOE_REQUIRE(xs_dev && hs_dev && ys_dev, "null activation pointer");
-  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(codes_dev) & 15u) == 0, "code store must be 16-byte aligned");
+  if (!(xs_dev && hs_dev && ys_dev)) {
+    set_error("%s: null activation pointer", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 || (reinterpret_cast<uintptr_t>(il_dev) & 15u) != 0) {
+    set_error("%s: code stores must be 16-byte aligned", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   SparseTable tab;
   int rc = get_sparse_table(dec_dev, device, as_stream(stream), &tab);
   if (rc) return rc;
-  return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, offsets_dev, xs_dev,
-                            hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff, device,
-                            as_stream(stream));
+  return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, il_dev, blk_base_dev,
+                            offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff,
+                            device, as_stream(stream));
+}
+
+int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                         const void *minmax_dev, const qmoe_matrix_desc *descs_dev, const int32_t *offsets_dev,
+                         const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
+                         int max_slots, int d_model, int d_ff, int device, void *stream) {
+  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, nullptr, nullptr,
+                           offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff,
+                           device, stream);
+}
+
+int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
+                                     const int32_t *row_off_dev, const void *minmax_dev,
+                                     const qmoe_matrix_desc *descs_dev, const void *il_codes_dev,
+                                     const int64_t *blk_base_dev, const int32_t *offsets_dev, const void *xs_dev,
+                                     void *hs_dev, void *ys_dev, void *work_dev, int n_experts, int max_slots,
+                                     int d_model, int d_ff, int device, void *stream) {
+  QMOE_REQUIRE(il_codes_dev && blk_base_dev, "null interleaved store");
+  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, il_codes_dev,
+                           blk_base_dev, offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots,
+                           d_model, d_ff, device, stream);
+}
+
+int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                              const qmoe_matrix_desc *descs_host, int n_matrices, int32_t *blk_units_dev,
+                              int device, void *stream) {
+  QMOE_REQUIRE(row_off_dev && descs_dev && descs_host && blk_units_dev, "null pointer");
+  QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
+  int64_t rows = 0;
+  for (int m = 0; m < n_matrices; m++) {
+    if (descs_host[m].height % 32 != 0 || descs_host[m].minmax_base != rows) {
+      set_error("%s: matrix %d: heights must be multiples of 32 and rows must be stored back to back", __func__, m);
+      return QMOE_ERR_UNSUPPORTED;
+    }
+    rows += descs_host[m].height;
+  }
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_interleave_count(row_off_dev, descs_dev, n_matrices, blk_units_dev, as_stream(stream));
+}
+
+int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_dev,
+                             const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
+                             void *il_codes_dev, int device, void *stream) {
+  QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && blk_base_dev && il_codes_dev, "null pointer");
+  QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
+  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) == 0, "interleaved store must be 16-byte aligned");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_interleave_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, il_codes_dev,
+                                as_stream(stream));
 }
 
 int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev, const void *prob_dev,

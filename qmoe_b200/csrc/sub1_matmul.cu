@@ -26,7 +26,7 @@ namespace qmoe {
 constexpr int kRowsPerItem = 256;     // single-matrix kernel: threads per CTA == rows per work item
 constexpr int kGroupedThreads = 1024; // grouped kernel: one persistent CTA per SM, rows per work item
 constexpr int kMaxGroup = 4;          // tokens decoded together
-constexpr int kPad = 32;              // zero entries after x: a code spans at most 28 positions
+constexpr int kPad = kWalkPad;        // zero entries after x (see walk_row)
 
 static inline int rows_per_chunk(int height, int rows_per_item) {
   const int chunks = (height + rows_per_item - 1) / rows_per_item;
@@ -153,6 +153,8 @@ struct MatmulArgs {
   const int32_t *row_off;
   const __nv_bfloat162 *minmax;
   const qmoe_matrix_desc *descs;  // grouped mode
+  const uint4 *il;                // grouped mode, lane-interleaved streams (or null)
+  const long long *blk_base;      // first uint4 of every 32-row block of `il`, plus the end
   qmoe_matrix_desc single;        // uniform mode
   const __nv_bfloat16 *x;
   __nv_bfloat16 *y;
@@ -167,7 +169,7 @@ __device__ __forceinline__ float bf16_round(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
-template <int T, bool GENERAL, class SinkT, class Lookup>
+template <int T, bool GENERAL, class SinkT, bool IL = false, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                              int nrows, int tok0, int ntok, typename SinkT::elem *xs,
                                              const Lookup &lookup) {
@@ -188,9 +190,6 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
 
   if (tid < nrows) {
     const int row = row0 + tid;
-    const uint16_t *codes_m = a.codes + d.code_base;
-    const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
-    const uint16_t *codes_al = codes_m - mis;
     const int32_t *ro = a.row_off + d.rowoff_base;
     long long b = ro[row], e = ro[row + 1];
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
@@ -200,7 +199,18 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
     sink.xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
 #pragma unroll
     for (int t = 0; t < T; t++) sink.s1[t] = sink.s2[t] = 0.f;
-    walk_row<GENERAL>(codes_al, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
+    if constexpr (IL) {
+      // Row blocks of 32 rows start at multiples of 32 in every matrix and in the store.
+      const long long gblk = (d.minmax_base + row) >> 5;
+      const long long first = a.blk_base[gblk];
+      const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;  // codes per row of this block
+      const long long n = e - b < room ? e - b : room;
+      walk_row<GENERAL>(LaneFetch{a.il + first + (row & 31)}, 0, (int)n, lookup, a.dec, wlim, sink);
+    } else {
+      const uint16_t *codes_m = a.codes + d.code_base;
+      const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
+      walk_row<GENERAL>(StreamFetch{codes_m - mis}, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
+    }
 
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     const float mn = __bfloat162float(mm.x), mx = __bfloat162float(mm.y);
@@ -352,7 +362,7 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_warp_rows(const Matm
 // Persistent CTAs (one per SM) pulling items of a device-built work list.  Shared memory holds the
 // hot part of the sparse table (loaded once per CTA) followed by the bf16 activations of the
 // current item.
-template <bool GENERAL>
+template <bool GENERAL, bool IL>
 __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
   __shared__ int s_item;
@@ -373,12 +383,12 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     const int nrows = it.w & 0xffff, ntok = it.w >> 16;
     // one or two tokens: fp32 activations (no conversion per gather); four: bf16, half the footprint
     if (ntok <= 1)
-      process_item<1, GENERAL, MatSink<1, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+      process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
     else if (ntok == 2)
-      process_item<2, GENERAL, MatSink<2, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+      process_item<2, GENERAL, MatSink<2, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
     else
-      process_item<4, GENERAL, MatSink<4, false>>(a, d, it.y, nrows, it.z, ntok,
-                                                  reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
+      process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
     __syncthreads();  // xs and s_item are rewritten by the next round
   }
 }
@@ -398,7 +408,7 @@ __global__ void k_decode(const uint32_t *__restrict__ tab, const int32_t *__rest
   e = e < b ? b : (e > n_codes ? n_codes : e);
   SymbolSink sink{sym + (size_t)row * width, width};
   const int wlim = (width + 1) & ~1;
-  const int pos = walk_row<GENERAL>(codes - mis, (int)b + mis, (int)e + mis, GlobalLookup{tab}, dec, wlim + 2, sink);
+  const int pos = walk_row<GENERAL>(StreamFetch{codes - mis}, (int)b + mis, (int)e + mis, GlobalLookup{tab}, dec, wlim + 2, sink);
   if (status != nullptr && (pos != wlim || !span_ok)) atomicAdd(status, 1);
 }
 
@@ -445,7 +455,9 @@ static int set_smem_limits() {
                                  (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_warp_rows<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
-  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   return QMOE_OK;
 }
@@ -528,6 +540,72 @@ int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cu
   QMOE_CUDA(cudaMemsetAsync(nonconforming, 0, sizeof(int), stream));
   QMOE_LAUNCH(k_build_table, QMOE_DICT_COUNT / 256, 256, 0, stream, dec, tab, nonconforming);
   QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+// ---- lane-interleaved code streams ----------------------------------------------------------------
+// One-time re-layout of a store's code streams for the grouped kernel.  Rows are taken in blocks of
+// 32 (one warp); inside a block, chunk k (codes 8k .. 8k+7) of row l is the uint4 at index
+// k * 32 + l, so the 32 lanes of a warp read 512 contiguous bytes per step instead of 32 separate
+// cache lines.  Every row of a block is padded with zero codes to the block's longest row, rounded
+// up to a whole chunk; the row lengths still come from row_off.  Heights must be multiples of 32.
+__global__ void k_interleave_count(const int32_t *__restrict__ row_off, const qmoe_matrix_desc *__restrict__ descs,
+                                   int32_t *__restrict__ blk_units) {
+  const qmoe_matrix_desc d = descs[blockIdx.x];
+  const int32_t *ro = row_off + d.rowoff_base;
+  for (int blk = threadIdx.x; blk < d.height / 32; blk += blockDim.x) {
+    int longest = 0;
+    for (int l = 0; l < 32; l++) {
+      const int n = ro[blk * 32 + l + 1] - ro[blk * 32 + l];
+      longest = n > longest ? n : longest;
+    }
+    blk_units[d.minmax_base / 32 + blk] = (longest + 7) / 8 * 32;  // uint4 entries of this block
+  }
+}
+
+__global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int32_t *__restrict__ row_off,
+                                  const qmoe_matrix_desc *__restrict__ descs,
+                                  const long long *__restrict__ blk_base, uint4 *__restrict__ il) {
+  const qmoe_matrix_desc d = descs[blockIdx.y];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int32_t *ro = row_off + d.rowoff_base;
+  const uint16_t *src = codes + d.code_base;
+  for (int blk = blockIdx.x * nwarps + warp; blk < d.height / 32; blk += gridDim.x * nwarps) {
+    const long long gblk = d.minmax_base / 32 + blk;
+    const long long first = blk_base[gblk];
+    const int chunks = (int)((blk_base[gblk + 1] - first) >> 5);
+    long long b = ro[blk * 32 + lane], e = ro[blk * 32 + lane + 1];
+    b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+    e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
+    for (int k = 0; k < chunks; k++) {
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const long long idx = b + 8 * k + j;
+        const uint32_t code = idx < e ? src[idx] : 0u;
+        w[j >> 1] |= code << (16 * (j & 1));
+      }
+      il[first + (long long)k * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+                            int32_t *blk_units, cudaStream_t stream) {
+  QMOE_LAUNCH(k_interleave_count, (unsigned)n_matrices, 256, 0, stream, row_off, descs, blk_units);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
+                           int n_matrices, const int64_t *blk_base, void *il, cudaStream_t stream) {
+  const int per_pass = 32768;  // grid.y limit is 65535
+  for (int m0 = 0; m0 < n_matrices; m0 += per_pass) {
+    const int n = n_matrices - m0 < per_pass ? n_matrices - m0 : per_pass;
+    QMOE_LAUNCH(k_interleave_emit, dim3(8, (unsigned)n), 256, 0, stream, codes, row_off, descs + m0,
+                reinterpret_cast<const long long *>(blk_base), reinterpret_cast<uint4 *>(il));
+    QMOE_CUDA(cudaGetLastError());
+  }
   return QMOE_OK;
 }
 
@@ -684,8 +762,9 @@ int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
-                       const int32_t *offsets, const void *xs, void *hs, void *ys, void *work, int n_experts,
-                       int max_slots, int d_model, int d_ff, int device, cudaStream_t stream) {
+                       const void *il_codes, const int64_t *blk_base, const int32_t *offsets, const void *xs,
+                       void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
+                       int device, cudaStream_t stream) {
   int rc = ensure_smem_limits(device);
   if (rc) return rc;
   const int sms = sm_count(device);
@@ -716,6 +795,9 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   a.row_off = row_off;
   a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
   a.descs = descs;
+  a.il = reinterpret_cast<const uint4 *>(il_codes);
+  a.blk_base = reinterpret_cast<const long long *>(blk_base);
+  const bool il = il_codes != nullptr;
   cudaEvent_t *events = nullptr;
   const bool timed = profile_begin(device, &events);
 
@@ -738,10 +820,14 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     }
     const unsigned grid = (unsigned)sms;  // the 160 KB table allows one CTA per SM
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
-    if (tab.conforming)
-      QMOE_LAUNCH(k_matmul_grouped<false>, grid, kGroupedThreads, smem, stream, a);
+    if (tab.conforming && il)
+      QMOE_LAUNCH((k_matmul_grouped<false, true>), grid, kGroupedThreads, smem, stream, a);
+    else if (tab.conforming)
+      QMOE_LAUNCH((k_matmul_grouped<false, false>), grid, kGroupedThreads, smem, stream, a);
+    else if (il)
+      QMOE_LAUNCH((k_matmul_grouped<true, true>), grid, kGroupedThreads, smem, stream, a);
     else
-      QMOE_LAUNCH(k_matmul_grouped<true>, grid, kGroupedThreads, smem, stream, a);
+      QMOE_LAUNCH((k_matmul_grouped<true, false>), grid, kGroupedThreads, smem, stream, a);
     QMOE_CUDA(cudaGetLastError());
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }

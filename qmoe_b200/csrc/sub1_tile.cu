@@ -246,9 +246,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
                                              : make_uint4(0u, 0u, 0u, 0u);
       };
       auto lookup8 = [&](const uint4 &q, uint32_t (&dst)[8]) {
-        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-        for (int j = 0; j < 8; j++) dst[j] = __ldg(a.tab + chunk_code(w4, j));
+        for (int j = 0; j < 8; j++) dst[j] = __ldg(a.tab + chunk_code(q, j));
       };
       uint4 q2;
       {

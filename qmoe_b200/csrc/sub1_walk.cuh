@@ -77,53 +77,93 @@ __device__ __noinline__ int dense_code(const int32_t *__restrict__ dec, uint32_t
   return 2 * len;
 }
 
-__device__ __forceinline__ uint32_t chunk_code(const uint32_t (&w)[4], int j) {
-  return (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+__device__ __forceinline__ uint32_t chunk_code(const uint4 &q, int j) {
+  const uint32_t w = j < 2 ? q.x : j < 4 ? q.y : j < 6 ? q.z : q.w;
+  return (j & 1) ? (w >> 16) : (w & 0xffffu);
 }
 
-// Walks codes [b_al, e_al) (indices relative to the 16-byte aligned pointer codes_al) and feeds
-// every entry to the sink.  Positions are kept scaled by the sink's element size
+// A code advances the position by at most 28 weights and the position is clamped once per four
+// codes, so x must be followed by this many zero entries.
+constexpr int kWalkPad = 4 * 28 + 32;
+
+// Where the eight codes of a chunk come from.  StreamFetch: the reference's stream (rows back to
+// back), read through a 16-byte aligned pointer.  LaneFetch: the lane-interleaved layout, in which
+// the 32 rows of a row block alternate chunk by chunk (chunk k of row l at uint4 index k * 32 + l),
+// so that the 32 loads of a warp cover 512 contiguous bytes.
+struct StreamFetch {
+  const uint16_t *__restrict__ codes_al;
+  __device__ __forceinline__ uint4 operator()(int c) const {
+    return __ldg(reinterpret_cast<const uint4 *>(codes_al + c));
+  }
+};
+struct LaneFetch {
+  const uint4 *__restrict__ p;  // chunk 0 of this lane's row
+  __device__ __forceinline__ uint4 operator()(int c) const { return __ldg(p + (c >> 3) * 32); }
+};
+
+// Walks codes [b_al, e_al) (indices as fetch() takes them; fetch(c) returns codes c .. c + 7 for c a
+// multiple of eight) and feeds every entry to the sink.  Positions are kept scaled by the sink's element size
 // (pos << Sink::kShift) so that they are shared-memory byte offsets; `pos_limit` (in weights)
-// clamps the running position so that a corrupt stream can never index past the zero padding that
-// follows x in shared memory.  Returns the final position in weights (== padded width for a
-// well-formed row).
-template <bool GENERAL, class Lookup, class Sink>
-__device__ __forceinline__ int walk_row(const uint16_t *__restrict__ codes_al, int b_al, int e_al,
-                                        const Lookup &lookup, const int32_t *__restrict__ dec,
-                                        int pos_limit, Sink &sink) {
+// clamps the running position after every four codes so that a corrupt stream can never index past the
+// kWalkPad zero entries that follow x in shared memory.  Returns the final position in weights
+// (== padded width for a well-formed row).
+//
+// Software pipeline in half chunks: while the four entries of one half are consumed, the table
+// lookups of the next half are in flight, and the code load runs a whole chunk ahead, so neither the
+// shared-memory lookups nor the (rarer, slower) global ones are waited for -- with the same number
+// of live registers as a loop that looks up eight entries and consumes them at once.
+template <bool GENERAL, class Fetch, class Lookup, class Sink>
+__device__ __forceinline__ int walk_row(const Fetch &fetch, int b_al, int e_al, const Lookup &lookup,
+                                        const int32_t *__restrict__ dec, int pos_limit, Sink &sink) {
   constexpr int S = Sink::kShift;
   uint32_t posb = 0;
   const uint32_t limit_b = (uint32_t)pos_limit << S;
   int c = b_al & ~7;
   if (c >= e_al) return 0;
-  uint4 q = __ldg(reinterpret_cast<const uint4 *>(codes_al + c));
-  for (; c < e_al; c += 8) {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    if (c + 8 < e_al) q = __ldg(reinterpret_cast<const uint4 *>(codes_al + c + 8));  // next chunk in flight
-    uint32_t e[8];
-    // Every 16-bit value is a valid table index, so the lookups are unconditional; slots outside
-    // the row (first and last chunk only) are then replaced by the null entry.
+  uint4 q_cur = fetch(c);
+  uint4 q_next = q_cur;
+  if (c + 8 < e_al) q_next = fetch(c + 8);
+  uint32_t ea[4], eb[4];
+  // Every 16-bit value is a valid table index, so the lookups are unconditional; slots outside
+  // the row (first and last chunk only) are then replaced by the null entry.
 #pragma unroll
-    for (int j = 0; j < 8; j++) e[j] = lookup(chunk_code(w, j));
-    if (c < b_al || c + 8 > e_al) {
+  for (int j = 0; j < 4; j++) ea[j] = lookup(chunk_code(q_cur, j));
+
+  auto consume = [&](uint32_t (&e)[4], const uint4 &q, int first) {
+    if (first < b_al || first + 4 > e_al) {
 #pragma unroll
-      for (int j = 0; j < 8; j++) {
-        const int idx = c + j;
+      for (int j = 0; j < 4; j++) {
+        const int idx = first + j;
         e[j] = (idx >= b_al && idx < e_al) ? e[j] : kEntryNull;
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
+    for (int j = 0; j < 4; j++) {
       if (GENERAL) {
         if ((e[j] & 0xffu) == 0x80u) {
           const int pos = (int)(posb >> S);
-          posb = min(((uint32_t)(pos + dense_code(dec, chunk_code(w, j), pos, sink))) << S, limit_b);
+          posb = ((uint32_t)(pos + dense_code(dec, chunk_code(q, (first & 4) + j), pos, sink))) << S;
           continue;
         }
       }
       sink.entry(e[j], posb);
-      posb = min(posb + (entry_len(e[j]) << (S + 1)), limit_b);
+      posb += entry_len(e[j]) << (S + 1);
     }
+    posb = min(posb, limit_b);
+  };
+
+  for (; c < e_al; c += 8) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) eb[j] = lookup(chunk_code(q_cur, 4 + j));
+    consume(ea, q_cur, c);
+    const uint4 q_now = q_cur;
+    q_cur = q_next;
+    if (c + 16 < e_al) q_next = fetch(c + 16);
+    if (c + 8 < e_al) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) ea[j] = lookup(chunk_code(q_cur, j));
+    }
+    consume(eb, q_now, c + 4);
   }
   return (int)(posb >> S);
 }

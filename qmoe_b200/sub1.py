@@ -138,17 +138,47 @@ class ExpertStore:
     ``descs``: device array of ``qmoe_matrix_desc``."""
 
     def __init__(self, codes: torch.Tensor, row_off: torch.Tensor, minmax: torch.Tensor,
-                 descs: Sequence[MatrixDesc], d_model: int, d_ff: int):
+                 descs: Sequence[MatrixDesc], d_model: int, d_ff: int, interleave: bool = True):
         assert codes.dtype == torch.int16 and row_off.dtype == torch.int32 and minmax.dtype == torch.bfloat16
         assert len(descs) % 2 == 0
         self.codes, self.row_off, self.minmax = codes, row_off, minmax
         self.d_model, self.d_ff = int(d_model), int(d_ff)
         self.n_experts = len(descs) // 2
         self.host_descs = list(descs)
-        arr = (MatrixDesc * len(descs))(*descs)
-        raw = np.frombuffer(bytes(arr), dtype=np.uint8).copy()
+        self._desc_array = (MatrixDesc * len(descs))(*descs)
+        raw = np.frombuffer(bytes(self._desc_array), dtype=np.uint8).copy()
         self.descs = torch.from_numpy(raw).to(codes.device)
         self.device = codes.device
+        self.il_codes: Optional[torch.Tensor] = None     # lane-interleaved copy of the streams
+        self.blk_base: Optional[torch.Tensor] = None     # int64, first 16-byte entry of every 32-row block
+        if interleave and codes.is_cuda and d_model % 32 == 0 and d_ff % 32 == 0:
+            self.interleave()
+
+    def interleave(self) -> None:
+        """Build the lane-interleaved copy of the code streams that the grouped kernel reads with
+        coalesced loads (layout in include/qmoe_sub1.h).  One-time cost when a store is created."""
+        import ctypes
+        L = _lib.load()
+        dev = self.device
+        rows = sum(d.height for d in self.host_descs)
+        units = torch.empty(rows // 32, dtype=torch.int32, device=dev)
+        _lib.check(L.qmoe_moe_interleave_count(self.row_off.data_ptr(), self.descs.data_ptr(),
+                                               ctypes.addressof(self._desc_array), len(self.host_descs),
+                                               units.data_ptr(), dev.index, _s(dev)))
+        base = torch.zeros(rows // 32 + 1, dtype=torch.int64, device=dev)
+        base[1:] = torch.cumsum(units, 0, dtype=torch.int64)
+        total = int(base[-1].item())
+        il = torch.empty((max(total, 1), 4), dtype=torch.int32, device=dev)
+        _lib.check(L.qmoe_moe_interleave_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
+                                              len(self.host_descs), base.data_ptr(), il.data_ptr(), dev.index,
+                                              _s(dev)))
+        self.il_codes, self.blk_base = il, base
+
+    @property
+    def resident_bytes(self) -> int:
+        """Device bytes held, including the interleaved copy."""
+        extra = 0 if self.il_codes is None else self.il_codes.numel() * 4 + self.blk_base.numel() * 8
+        return self.compressed_bytes + extra
 
     @property
     def compressed_bytes(self) -> int:
@@ -292,6 +322,13 @@ def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max
     if work is None or work.numel() < nbytes:
         work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     assert xs.is_contiguous() and xs.shape[1] == store.d_model
+    if store.il_codes is not None:
+        _lib.check(L.qmoe_moe_grouped_ffn_interleaved(
+            DEC(dev).data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(), store.minmax.data_ptr(),
+            store.descs.data_ptr(), store.il_codes.data_ptr(), store.blk_base.data_ptr(), offsets.data_ptr(),
+            xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(), store.n_experts, max_slots,
+            store.d_model, store.d_ff, dev.index, _s(dev)))
+        return ys
     _lib.check(L.qmoe_moe_grouped_ffn(DEC(dev).data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(),
                                       store.minmax.data_ptr(), store.descs.data_ptr(), offsets.data_ptr(),
                                       xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(),
