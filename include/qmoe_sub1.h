@@ -183,29 +183,48 @@ int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, cons
 
 /* Lane-interleaved copy of a store's code streams, the layout the grouped kernel reads fastest.
  * No counterpart in the reference, whose kernel (sub1_cuda_kernel.cu:129-202) reads w_comp row by
- * row; the copy holds the same codes and decodes to the same weights.  Rows are taken in blocks of
- * 32; chunk k (codes 8k..8k+7) of row l of a block is the 16-byte entry k * 32 + l of the block, and
- * every row of a block is zero-padded to the block's longest row rounded up to 8 codes.  Heights
- * must be multiples of 32 and the matrices' rows consecutive (minmax_base = rows before).
+ * row; the copy holds the same codes (optionally renumbered) and decodes to the same weights.
+ * Rows are taken in blocks of 32; chunk k (codes 8k..8k+7) of row l of a block is the 16-byte entry
+ * k * 32 + l of the block, and every row of a block is zero-padded to the block's longest row
+ * rounded up to 8 codes.  Heights must be multiples of 32 and the matrices' rows consecutive
+ * (minmax_base = rows before).
+ *
+ * Renumbering: the kernel keeps the first entries of the table in shared memory (as many as the
+ * activations leave room for, 45 000 - 53 000 of the 65 536), so the copy may store remap[code]
+ * instead of code, with remap a permutation that gives frequent codes small numbers
+ * (qmoe_sub1_code_histogram counts them); qmoe_sub1_remap_tables writes the sparse table and the
+ * reference table words in the new order (remap_dev NULL = identity).
  *   1. qmoe_moe_interleave_count: blk_units_dev int32[total_rows / 32] := 16-byte entries per block
  *      (descs_host: the same descriptors in host memory, for validation);
  *   2. the caller forms blk_base int64[total_rows / 32 + 1], the exclusive prefix sum, and allocates
  *      16 * blk_base[last] bytes;
  *   3. qmoe_moe_interleave_emit fills them;
  *   4. qmoe_moe_grouped_ffn_interleaved is qmoe_moe_grouped_ffn reading the copy (experts on the
- *      tensor-core tile path still read codes_dev). */
+ *      tensor-core tile path still read codes_dev with dec_dev). */
+typedef struct qmoe_interleaved_store {
+  const void *codes;       /* 16-byte entries, device */
+  const int64_t *blk_base; /* [total_rows / 32 + 1], device */
+  const uint32_t *table;   /* uint32[65536] from qmoe_sub1_remap_tables, device */
+  const int32_t *dec;      /* int32[131072] from qmoe_sub1_remap_tables, device */
+} qmoe_interleaved_store;
+
+int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev /* [65536], added to */,
+                             int device, void *stream);
+int qmoe_sub1_remap_tables(const int32_t *dec_dev, const uint32_t *remap_dev /* [65536] or NULL */,
+                           uint32_t *table_out_dev, int32_t *dec_out_dev, int device, void *stream);
 int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
                               const qmoe_matrix_desc *descs_host, int n_matrices, int32_t *blk_units_dev,
                               int device, void *stream);
 int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_dev,
                              const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
-                             void *il_codes_dev, int device, void *stream);
+                             const uint32_t *remap_dev /* [65536] or NULL */, void *il_codes_dev, int device,
+                             void *stream);
 int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
                                      const int32_t *row_off_dev, const void *minmax_dev,
-                                     const qmoe_matrix_desc *descs_dev, const void *il_codes_dev,
-                                     const int64_t *blk_base_dev, const int32_t *offsets_dev, const void *xs_dev,
-                                     void *hs_dev, void *ys_dev, void *work_dev, int n_experts, int max_slots,
-                                     int d_model, int d_ff, int device, void *stream);
+                                     const qmoe_matrix_desc *descs_dev, const qmoe_interleaved_store *store,
+                                     const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,
+                                     void *work_dev, int n_experts, int max_slots, int d_model, int d_ff,
+                                     int device, void *stream);
 
 /* out[token] = bf16(prob[token] * (slot >= 0 ? ys[slot] : hidden[token])): the scatter back to
  * token order, the pass-through of dropped tokens and the router-probability scaling of

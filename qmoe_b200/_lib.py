@@ -47,6 +47,13 @@ class MatrixDesc(ctypes.Structure):
     ]
 
 
+class InterleavedStore(ctypes.Structure):
+    """Mirror of ``qmoe_interleaved_store``."""
+
+    _fields_ = [("codes", ctypes.c_void_p), ("blk_base", ctypes.c_void_p), ("table", ctypes.c_void_p),
+                ("dec", ctypes.c_void_p)]
+
+
 _P = ctypes.c_void_p
 _I = ctypes.c_int
 _L = ctypes.c_int64
@@ -74,9 +81,11 @@ SIGNATURES = {
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
     "qmoe_moe_set_tile_min_tokens": (_I, [_I]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
-    "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_interleave_count": (_I, [_P, _P, _P, _I, _P, _I, _P]),
-    "qmoe_moe_interleave_emit": (_I, [_P, _P, _P, _I, _P, _P, _I, _P]),
+    "qmoe_moe_interleave_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P]),
+    "qmoe_sub1_code_histogram": (_I, [_P, _L, _P, _I, _P]),
+    "qmoe_sub1_remap_tables": (_I, [_P, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_launch_count": (_L, []),
     "qmoe_profile_enable": (_I, [_I]),

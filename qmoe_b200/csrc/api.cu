@@ -81,13 +81,17 @@ int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
 int set_tile_min_tokens(int tokens);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
-                       const void *il_codes, const int64_t *blk_base, const int32_t *offsets, const void *xs,
+                       const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
                        void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
                        int device, cudaStream_t stream);
+int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream);
+int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
+                        int *scratch2, cudaStream_t stream);
 int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
                             int32_t *blk_units, cudaStream_t stream);
 int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
-                           int n_matrices, const int64_t *blk_base, void *il, cudaStream_t stream);
+                           int n_matrices, const int64_t *blk_base, const uint32_t *remap, void *il,
+                           cudaStream_t stream);
 int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
                         cudaStream_t stream);
 int launch_pack_emit(const int32_t *w_tern, const int32_t *row_off, uint16_t *w_comp, int height, int width,
@@ -432,7 +436,7 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
 
 static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint16_t *codes_dev,
                              const int32_t *row_off_dev, const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
-                             const void *il_dev, const int64_t *blk_base_dev, const int32_t *offsets_dev,
+                             const qmoe_interleaved_store *ils, const int32_t *offsets_dev,
                              const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
                              int max_slots, int d_model, int d_ff, int device, void *stream) {
   if (!(dec_dev && codes_dev && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev)) {
@@ -447,7 +451,11 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     set_error("%s: d_model/d_ff exceed QMOE_MAX_WIDTH (%d)", fn, QMOE_MAX_WIDTH);
     return QMOE_ERR_UNSUPPORTED;
   }
-  if (il_dev && (d_model % 32 != 0 || d_ff % 32 != 0)) {
+  if (ils && !(ils->codes && ils->blk_base && ils->table && ils->dec)) {
+    set_error("%s: null pointer in the interleaved store", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (ils && (d_model % 32 != 0 || d_ff % 32 != 0)) {
     set_error("%s: lane-interleaved streams need d_model and d_ff to be multiples of 32", fn);
     return QMOE_ERR_UNSUPPORTED;
   }
@@ -456,7 +464,7 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     set_error("%s: null activation pointer", fn);
     return QMOE_ERR_INVALID_ARG;
   }
-  if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 || (reinterpret_cast<uintptr_t>(il_dev) & 15u) != 0) {
+  if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 || (ils && (reinterpret_cast<uintptr_t>(ils->codes) & 15u) != 0)) {
     set_error("%s: code stores must be 16-byte aligned", fn);
     return QMOE_ERR_INVALID_ARG;
   }
@@ -465,7 +473,7 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
   SparseTable tab;
   int rc = get_sparse_table(dec_dev, device, as_stream(stream), &tab);
   if (rc) return rc;
-  return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, il_dev, blk_base_dev,
+  return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, ils,
                             offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff,
                             device, as_stream(stream));
 }
@@ -474,21 +482,53 @@ int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, cons
                          const void *minmax_dev, const qmoe_matrix_desc *descs_dev, const int32_t *offsets_dev,
                          const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
                          int max_slots, int d_model, int d_ff, int device, void *stream) {
-  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, nullptr, nullptr,
+  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, nullptr,
                            offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff,
                            device, stream);
 }
 
 int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
                                      const int32_t *row_off_dev, const void *minmax_dev,
-                                     const qmoe_matrix_desc *descs_dev, const void *il_codes_dev,
-                                     const int64_t *blk_base_dev, const int32_t *offsets_dev, const void *xs_dev,
-                                     void *hs_dev, void *ys_dev, void *work_dev, int n_experts, int max_slots,
-                                     int d_model, int d_ff, int device, void *stream) {
-  QMOE_REQUIRE(il_codes_dev && blk_base_dev, "null interleaved store");
-  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, il_codes_dev,
-                           blk_base_dev, offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots,
-                           d_model, d_ff, device, stream);
+                                     const qmoe_matrix_desc *descs_dev, const qmoe_interleaved_store *store,
+                                     const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,
+                                     void *work_dev, int n_experts, int max_slots, int d_model, int d_ff,
+                                     int device, void *stream) {
+  QMOE_REQUIRE(store != nullptr, "null interleaved store");
+  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, store, offsets_dev,
+                           xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff, device, stream);
+}
+
+int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev, int device,
+                             void *stream) {
+  QMOE_REQUIRE(codes_dev && hist_dev, "null device pointer");
+  QMOE_REQUIRE(n_codes >= 0, "bad count");
+  if (n_codes == 0) return QMOE_OK;
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_code_histogram(codes_dev, n_codes, hist_dev, as_stream(stream));
+}
+
+int qmoe_sub1_remap_tables(const int32_t *dec_dev, const uint32_t *remap_dev, uint32_t *table_out_dev,
+                           int32_t *dec_out_dev, int device, void *stream) {
+  QMOE_REQUIRE(dec_dev && table_out_dev && dec_out_dev, "null device pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  int *scratch = nullptr;
+  QMOE_CUDA(cudaMalloc(&scratch, 2 * sizeof(int)));
+  int rc = launch_remap_tables(dec_dev, remap_dev, table_out_dev, dec_out_dev, scratch, as_stream(stream));
+  int host[2] = {0, 0};
+  if (rc == QMOE_OK) {
+    cudaError_t e = cudaMemcpyAsync(host, scratch, sizeof(host), cudaMemcpyDeviceToHost, as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) rc = cuda_fail(e, "remap tables");
+  }
+  cudaFree(scratch);
+  if (rc) return rc;
+  if (host[0] != 0) {
+    set_error("%s: remap is not a permutation of 0..65535", __func__);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  return QMOE_OK;
 }
 
 int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
@@ -511,14 +551,14 @@ int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc
 
 int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_dev,
                              const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
-                             void *il_codes_dev, int device, void *stream) {
+                             const uint32_t *remap_dev, void *il_codes_dev, int device, void *stream) {
   QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && blk_base_dev && il_codes_dev, "null pointer");
   QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
   QMOE_REQUIRE((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) == 0, "interleaved store must be 16-byte aligned");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_interleave_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, il_codes_dev,
-                                as_stream(stream));
+  return launch_interleave_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, remap_dev,
+                                il_codes_dev, as_stream(stream));
 }
 
 int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev, const void *prob_dev,

@@ -155,6 +155,9 @@ struct MatmulArgs {
   const qmoe_matrix_desc *descs;  // grouped mode
   const uint4 *il;                // grouped mode, lane-interleaved streams (or null)
   const long long *blk_base;      // first uint4 of every 32-row block of `il`, plus the end
+  const uint32_t *il_tab;         // sparse table in the order of the interleaved store's code values
+  const int32_t *il_dec;          // reference table words in that order
+  int n_hot;                      // entries of il_tab kept in shared memory
   qmoe_matrix_desc single;        // uniform mode
   const __nv_bfloat16 *x;
   __nv_bfloat16 *y;
@@ -205,7 +208,7 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
       const long long first = a.blk_base[gblk];
       const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;  // codes per row of this block
       const long long n = e - b < room ? e - b : room;
-      walk_row<GENERAL>(LaneFetch{a.il + first + (row & 31)}, 0, (int)n, lookup, a.dec, wlim, sink);
+      walk_row<GENERAL>(LaneFetch{a.il + first + (row & 31)}, 0, (int)n, lookup, a.il_dec, wlim, sink);
     } else {
       const uint16_t *codes_m = a.codes + d.code_base;
       const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
@@ -367,12 +370,20 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
   extern __shared__ __align__(16) uint32_t smem_u32[];
   __shared__ int s_item;
   uint32_t *hot = smem_u32;
-  void *xs = smem_u32 + kHotSlots;
+  const uint32_t n_hot = IL ? (uint32_t)a.n_hot : kHotSlots;
+  void *xs = smem_u32 + n_hot;
   const int n_items = a.header[0];
   if (n_items <= 0) return;
-  for (uint32_t i = threadIdx.x; i < kHotSlots; i += blockDim.x)
-    hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
-  const HotLookup lookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
+  using Lookup = typename std::conditional<IL, HotLookupLow, HotLookup>::type;
+  Lookup lookup;
+  if constexpr (IL) {
+    for (uint32_t i = threadIdx.x; i < n_hot; i += blockDim.x) hot[i] = __ldg(a.il_tab + i);
+    lookup = HotLookupLow{(uint32_t)__cvta_generic_to_shared(hot), a.il_tab, n_hot};
+  } else {
+    for (uint32_t i = threadIdx.x; i < kHotSlots; i += blockDim.x)
+      hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
+    lookup = HotLookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
+  }
   for (;;) {
     if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
     __syncthreads();  // also orders the table fill before the first lookups
@@ -381,11 +392,13 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     const int4 it = a.items[i];
     const qmoe_matrix_desc d = a.descs[it.x];
     const int nrows = it.w & 0xffff, ntok = it.w >> 16;
-    // one or two tokens: fp32 activations (no conversion per gather); four: bf16, half the footprint
+    // one token: fp32 activations (no conversion per gather); two and four: bf16, so that a gather
+    // is one 4- or 8-byte shared load (two 4-byte words per lane cost twice the bank cycles)
     if (ntok <= 1)
       process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
     else if (ntok == 2)
-      process_item<2, GENERAL, MatSink<2, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+      process_item<2, GENERAL, MatSink<2, false>, IL>(a, d, it.y, nrows, it.z, ntok,
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
     else
       process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
                                                       reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
@@ -444,9 +457,19 @@ static size_t smem_bytes(int width, int group) {
   const int wlim = (width + 1) & ~1;
   return (size_t)(wlim + kPad) * group * sizeof(float);
 }
-static size_t grouped_smem_bytes(int width, int group) {
+static size_t grouped_x_bytes(int width, int group) {
   const int wlim = (width + 1) & ~1;
-  return sizeof(uint32_t) * kHotSlots + (size_t)(wlim + kPad) * group * sizeof(__nv_bfloat16);
+  return (size_t)(wlim + kPad) * group * sizeof(__nv_bfloat16);
+}
+static size_t grouped_smem_bytes(int width, int group) {
+  return sizeof(uint32_t) * kHotSlots + grouped_x_bytes(width, group);
+}
+// Interleaved stores: whatever the activations leave of the 227 KB goes to the table.
+constexpr size_t kSmemPerCta = 232448 - 1024;  // opt-in limit minus static shared memory and slack
+static int hot_entries_for(int width) {
+  const size_t left = kSmemPerCta - grouped_x_bytes(width, kMaxGroup);
+  size_t n = left / sizeof(uint32_t) / 1024 * 1024;
+  return (int)(n > QMOE_DICT_COUNT ? QMOE_DICT_COUNT : n);
 }
 
 template <bool GENERAL>
@@ -458,7 +481,7 @@ static int set_smem_limits() {
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+                                 (int)kSmemPerCta));
   return QMOE_OK;
 }
 
@@ -543,6 +566,56 @@ int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cu
   return QMOE_OK;
 }
 
+// ---- renumbering of code values --------------------------------------------------------------------
+__global__ void k_code_histogram(const uint16_t *__restrict__ codes, long long n,
+                                 unsigned long long *__restrict__ hist) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    atomicAdd(hist + codes[i], 1ull);
+}
+
+// dec_out[2 * remap[c] + i] = dec[2 * c + i]: the reference table in the order of the new code values.
+__global__ void k_permute_dec(const int32_t *__restrict__ dec, const uint32_t *__restrict__ remap,
+                              int32_t *__restrict__ dec_out, int *bad) {
+  const int code = blockIdx.x * blockDim.x + threadIdx.x;
+  if (code >= QMOE_DICT_COUNT) return;
+  const uint32_t to = remap != nullptr ? remap[code] : (uint32_t)code;
+  if (to >= (uint32_t)QMOE_DICT_COUNT) {
+    atomicAdd(bad, 1);
+    return;
+  }
+  dec_out[2 * to] = dec[2 * code];
+  dec_out[2 * to + 1] = dec[2 * code + 1];
+}
+
+int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream) {
+  QMOE_LAUNCH(k_code_histogram, 148 * 8, 256, 0, stream, codes, (long long)n,
+              reinterpret_cast<unsigned long long *>(hist));
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+// Entries of dec_out that no code was mapped to (remap is not a permutation) keep length 0.
+__global__ void k_count_unset(const int32_t *__restrict__ dec_out, const int32_t *__restrict__ dec, int *bad) {
+  const int code = blockIdx.x * blockDim.x + threadIdx.x;
+  if (code >= QMOE_DICT_COUNT) return;
+  if (dec_out[2 * code] == 0 && dec_out[2 * code + 1] == 0) atomicAdd(bad, 1);
+  if (dec[2 * code] == 0 && dec[2 * code + 1] == 0) atomicSub(bad, 1);  // all-zero words of the source itself
+}
+
+// scratch2[0] := number of out-of-range or colliding targets, scratch2[1] := non-conforming entries.
+int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
+                        int *scratch2, cudaStream_t stream) {
+  QMOE_CUDA(cudaMemsetAsync(scratch2, 0, 2 * sizeof(int), stream));
+  QMOE_CUDA(cudaMemsetAsync(dec_out, 0, sizeof(int32_t) * 2 * QMOE_DICT_COUNT, stream));
+  QMOE_LAUNCH(k_permute_dec, QMOE_DICT_COUNT / 256, 256, 0, stream, dec, remap, dec_out, scratch2);
+  QMOE_CUDA(cudaGetLastError());
+  QMOE_LAUNCH(k_count_unset, QMOE_DICT_COUNT / 256, 256, 0, stream, dec_out, dec, scratch2);
+  QMOE_CUDA(cudaGetLastError());
+  QMOE_LAUNCH(k_build_table, QMOE_DICT_COUNT / 256, 256, 0, stream, dec_out, tab_out, scratch2 + 1);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
 // ---- lane-interleaved code streams ----------------------------------------------------------------
 // One-time re-layout of a store's code streams for the grouped kernel.  Rows are taken in blocks of
 // 32 (one warp); inside a block, chunk k (codes 8k .. 8k+7) of row l is the uint4 at index
@@ -565,7 +638,8 @@ __global__ void k_interleave_count(const int32_t *__restrict__ row_off, const qm
 
 __global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int32_t *__restrict__ row_off,
                                   const qmoe_matrix_desc *__restrict__ descs,
-                                  const long long *__restrict__ blk_base, uint4 *__restrict__ il) {
+                                  const long long *__restrict__ blk_base, const uint32_t *__restrict__ remap,
+                                  uint4 *__restrict__ il) {
   const qmoe_matrix_desc d = descs[blockIdx.y];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int32_t *ro = row_off + d.rowoff_base;
@@ -582,7 +656,8 @@ __global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int3
 #pragma unroll
       for (int j = 0; j < 8; j++) {
         const long long idx = b + 8 * k + j;
-        const uint32_t code = idx < e ? src[idx] : 0u;
+        uint32_t code = idx < e ? src[idx] : 0u;
+        if (remap != nullptr) code = __ldg(remap + code) & 0xffffu;
         w[j >> 1] |= code << (16 * (j & 1));
       }
       il[first + (long long)k * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -598,12 +673,13 @@ int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *desc
 }
 
 int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
-                           int n_matrices, const int64_t *blk_base, void *il, cudaStream_t stream) {
+                           int n_matrices, const int64_t *blk_base, const uint32_t *remap, void *il,
+                           cudaStream_t stream) {
   const int per_pass = 32768;  // grid.y limit is 65535
   for (int m0 = 0; m0 < n_matrices; m0 += per_pass) {
     const int n = n_matrices - m0 < per_pass ? n_matrices - m0 : per_pass;
     QMOE_LAUNCH(k_interleave_emit, dim3(8, (unsigned)n), 256, 0, stream, codes, row_off, descs + m0,
-                reinterpret_cast<const long long *>(blk_base), reinterpret_cast<uint4 *>(il));
+                reinterpret_cast<const long long *>(blk_base), remap, reinterpret_cast<uint4 *>(il));
     QMOE_CUDA(cudaGetLastError());
   }
   return QMOE_OK;
@@ -762,7 +838,7 @@ int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
-                       const void *il_codes, const int64_t *blk_base, const int32_t *offsets, const void *xs,
+                       const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
                        void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
                        int device, cudaStream_t stream) {
   int rc = ensure_smem_limits(device);
@@ -795,9 +871,13 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   a.row_off = row_off;
   a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
   a.descs = descs;
-  a.il = reinterpret_cast<const uint4 *>(il_codes);
-  a.blk_base = reinterpret_cast<const long long *>(blk_base);
-  const bool il = il_codes != nullptr;
+  const bool il = ils != nullptr;
+  if (il) {
+    a.il = reinterpret_cast<const uint4 *>(ils->codes);
+    a.blk_base = reinterpret_cast<const long long *>(ils->blk_base);
+    a.il_tab = ils->table;
+    a.il_dec = ils->dec;
+  }
   cudaEvent_t *events = nullptr;
   const bool timed = profile_begin(device, &events);
 
@@ -810,7 +890,9 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     a.items = ph[phase].items;
     a.header = header + 2 * phase;
     a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
-    const size_t smem = grouped_smem_bytes(width, kMaxGroup);
+    a.n_hot = hot_entries_for(width);
+    const size_t smem = il ? sizeof(uint32_t) * a.n_hot + grouped_x_bytes(width, kMaxGroup)
+                           : grouped_smem_bytes(width, kMaxGroup);
     if (tile_min > 0) {
       const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
       rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,

@@ -56,6 +56,27 @@ struct HotLookup {
     return e;
   }
 };
+// The same for a store whose code values were renumbered by decreasing frequency: the first n_hot
+// entries live in shared memory, the rest in global memory.
+struct HotLookupLow {
+  uint32_t hot_addr;
+  const uint32_t *__restrict__ tab;
+  uint32_t n_hot;
+  __device__ __forceinline__ uint32_t operator()(uint32_t code) const {
+    uint32_t e;
+    const uint32_t saddr = hot_addr + code * 4u;
+    const uint32_t *gaddr = tab + code;
+    asm("{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.lt.u32 p, %1, %4;\n\t"
+        "@p ld.shared.b32 %0, [%2];\n\t"
+        "@!p ld.global.nc.b32 %0, [%3];\n\t"
+        "}"
+        : "=r"(e)
+        : "r"(code), "r"(saddr), "l"(gaddr), "r"(n_hot));
+    return e;
+  }
+};
 static_assert(kHotLow == 24576 && kHotHigh == 49152 && (kHotHigh - kHotLow) * 4 == 98304,
               "HotLookup's inline PTX hard-codes the hot ranges");
 

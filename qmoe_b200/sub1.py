@@ -154,12 +154,29 @@ class ExpertStore:
         if interleave and codes.is_cuda and d_model % 32 == 0 and d_ff % 32 == 0:
             self.interleave()
 
-    def interleave(self) -> None:
+    def interleave(self, renumber: bool = True) -> None:
         """Build the lane-interleaved copy of the code streams that the grouped kernel reads with
-        coalesced loads (layout in include/qmoe_sub1.h).  One-time cost when a store is created."""
-        import ctypes
+        coalesced loads (layout in include/qmoe_sub1.h), with code values renumbered by decreasing
+        frequency so that the part of the table kept in shared memory serves as many lookups as
+        possible.  One-time cost when a store is created."""
         L = _lib.load()
         dev = self.device
+        dec = DEC(dev)
+        remap_ptr = None
+        if renumber:
+            hist = torch.zeros(_lib.DICT_COUNT, dtype=torch.int64, device=dev)
+            last = self.host_descs[min(63, len(self.host_descs) - 1)]      # 64 matrices are sample enough
+            n = min(last.code_base + last.n_codes, self.codes.numel())
+            _lib.check(L.qmoe_sub1_code_histogram(self.codes.data_ptr(), n, hist.data_ptr(), dev.index, _s(dev)))
+            order = torch.argsort(hist, descending=True, stable=True)
+            remap = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
+            remap[order] = torch.arange(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
+            self.remap = remap
+            remap_ptr = remap.data_ptr()
+        self.il_table = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
+        self.il_dec = torch.empty(2 * _lib.DICT_COUNT, dtype=torch.int32, device=dev)
+        _lib.check(L.qmoe_sub1_remap_tables(dec.data_ptr(), remap_ptr, self.il_table.data_ptr(),
+                                            self.il_dec.data_ptr(), dev.index, _s(dev)))
         rows = sum(d.height for d in self.host_descs)
         units = torch.empty(rows // 32, dtype=torch.int32, device=dev)
         _lib.check(L.qmoe_moe_interleave_count(self.row_off.data_ptr(), self.descs.data_ptr(),
@@ -170,9 +187,11 @@ class ExpertStore:
         total = int(base[-1].item())
         il = torch.empty((max(total, 1), 4), dtype=torch.int32, device=dev)
         _lib.check(L.qmoe_moe_interleave_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
-                                              len(self.host_descs), base.data_ptr(), il.data_ptr(), dev.index,
-                                              _s(dev)))
+                                              len(self.host_descs), base.data_ptr(), remap_ptr, il.data_ptr(),
+                                              dev.index, _s(dev)))
         self.il_codes, self.blk_base = il, base
+        self.il_struct = _lib.InterleavedStore(il.data_ptr(), base.data_ptr(), self.il_table.data_ptr(),
+                                               self.il_dec.data_ptr())
 
     @property
     def resident_bytes(self) -> int:
@@ -325,7 +344,7 @@ def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max
     if store.il_codes is not None:
         _lib.check(L.qmoe_moe_grouped_ffn_interleaved(
             DEC(dev).data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(), store.minmax.data_ptr(),
-            store.descs.data_ptr(), store.il_codes.data_ptr(), store.blk_base.data_ptr(), offsets.data_ptr(),
+            store.descs.data_ptr(), ctypes.addressof(store.il_struct), offsets.data_ptr(),
             xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(), store.n_experts, max_slots,
             store.d_model, store.d_ff, dev.index, _s(dev)))
         return ys
