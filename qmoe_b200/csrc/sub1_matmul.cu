@@ -67,8 +67,19 @@ __device__ __forceinline__ void lds_pred_b128(uint32_t (&v)[4], uint32_t addr, u
 
 constexpr int ilog2(int v) { return v <= 1 ? 0 : 1 + ilog2(v / 2); }
 
-// Accumulates, for T tokens, s1 = sum of x over digit-1 positions and s2 = sum over digit-2
-// positions of a row.  x lives in shared memory as [position][T], fp32 (F32) or bf16.
+// acc2 += c * v2 on a pair of floats with one packed instruction (fma.rn.f32x2).
+__device__ __forceinline__ void fma_pair(float &a0, float &a1, float c, float v0, float v1) {
+  asm("{\n\t.reg .b64 ra, rc, rv;\n\t"
+      "mov.b64 ra, {%0, %1};\n\tmov.b64 rc, {%2, %2};\n\tmov.b64 rv, {%3, %4};\n\t"
+      "fma.rn.f32x2 ra, rc, rv, ra;\n\t"
+      "mov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(a0), "+f"(a1)
+      : "f"(c), "f"(v0), "f"(v1));
+}
+
+// Accumulates, for T tokens, acc[t] = sum over the non-zeros of a row of w * x[t][c] in fp32, with
+// w = min_r for digit 1 and max_r for digit 2 (the reference's fp32 multiply-add per weight,
+// sub1_cuda_kernel.cu:188-192).  x lives in shared memory as [position][T], fp32 (F32) or bf16.
 template <int T, bool F32>
 struct MatSink {
   using elem = typename std::conditional<F32, float, __nv_bfloat16>::type;
@@ -78,8 +89,16 @@ struct MatSink {
     else return v;
   }
   uint32_t xs_addr;  // shared-space byte address of x
-  float s1[T], s2[T];
+  float mn, mx;      // the row's two weight values
+  float acc[T];
 
+  __device__ __forceinline__ void reset(float row_min, float row_max, uint32_t addr) {
+    xs_addr = addr;
+    mn = row_min;
+    mx = row_max;
+#pragma unroll
+    for (int t = 0; t < T; t++) acc[t] = 0.f;
+  }
   __device__ __forceinline__ void load(float (&vf)[T], uint32_t addr, uint32_t pos_byte) {
     if constexpr (F32) {
       uint32_t v[4] = {0u, 0u, 0u, 0u};
@@ -101,30 +120,28 @@ struct MatSink {
       }
     }
   }
+  __device__ __forceinline__ void add(float c, const float (&vf)[T]) {
+    if constexpr (T == 1) {
+      acc[0] = fmaf(c, vf[0], acc[0]);
+    } else {
+#pragma unroll
+      for (int t = 0; t < T; t += 2) fma_pair(acc[t], acc[t + 1], c, vf[t], vf[t + 1]);
+    }
+  }
   __device__ __forceinline__ void entry(uint32_t e, uint32_t posb) {
     const uint32_t base = xs_addr + posb;
 #pragma unroll
     for (int k = 0; k < 3; k++) {
       const uint32_t o = entry_nz_pos(e, k);
       float vf[T];
-      load(vf, base + (o << kShift), o);
-      if (e & (0x10u << k)) {
-#pragma unroll
-        for (int t = 0; t < T; t++) s2[t] += vf[t];
-      } else {
-#pragma unroll
-        for (int t = 0; t < T; t++) s1[t] += vf[t];
-      }
+      load(vf, base + (o << kShift), o);  // zeros where the non-zero is absent
+      add((e & (0x10u << k)) ? mx : mn, vf);
     }
   }
   __device__ __forceinline__ void dense(int p, uint32_t digit) {
     float vf[T];
     load(vf, xs_addr + ((uint32_t)p << kShift), 0u);
-#pragma unroll
-    for (int t = 0; t < T; t++) {
-      if (digit == 1u) s1[t] += vf[t];
-      else s2[t] += vf[t];
-    }
+    add(digit == 1u ? mn : mx, vf);
   }
 };
 
@@ -198,10 +215,9 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
     e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
 
+    const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     SinkT sink;
-    sink.xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
-#pragma unroll
-    for (int t = 0; t < T; t++) sink.s1[t] = sink.s2[t] = 0.f;
+    sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
     if constexpr (IL) {
       // Row blocks of 32 rows start at multiples of 32 in every matrix and in the store.
       const long long gblk = (d.minmax_base + row) >> 5;
@@ -215,13 +231,11 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
       walk_row<GENERAL>(StreamFetch{codes_m - mis}, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
     }
 
-    const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
-    const float mn = __bfloat162float(mm.x), mx = __bfloat162float(mm.y);
 #pragma unroll
     for (int t = 0; t < T; t++) {
       if (t < ntok) {
         // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
-        float r = bf16_round(fmaf(mn, sink.s1[t], mx * sink.s2[t]));
+        float r = bf16_round(sink.acc[t]);
         __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
         if (a.flags & QMOE_FLAG_ACCUMULATE) r = bf16_round(__bfloat162float(*yp) + r);
         if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
@@ -279,10 +293,9 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
     long long b = a.row_off[row], e = a.row_off[row + 1];
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
     e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
+    const __nv_bfloat162 mm = a.minmax[row];
     SinkT sink;
-    sink.xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
-#pragma unroll
-    for (int t = 0; t < T; t++) sink.s1[t] = sink.s2[t] = 0.f;
+    sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
     uint32_t row_pos = 0;
     // Two groups of 32 codes per iteration (both dictionary lookups in flight together), and the
     // codes of the next iteration are requested before this one is processed.
@@ -327,18 +340,13 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
 #pragma unroll
     for (int t = 0; t < T; t++) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        sink.s1[t] += __shfl_xor_sync(0xffffffffu, sink.s1[t], o);
-        sink.s2[t] += __shfl_xor_sync(0xffffffffu, sink.s2[t], o);
-      }
+      for (int o = 16; o > 0; o >>= 1) sink.acc[t] += __shfl_xor_sync(0xffffffffu, sink.acc[t], o);
     }
     if (lane == 0) {
-      const __nv_bfloat162 mm = a.minmax[row];
-      const float mn = __bfloat162float(mm.x), mx = __bfloat162float(mm.y);
 #pragma unroll
       for (int t = 0; t < T; t++) {
         if (t < ntok) {
-          float v = bf16_round(fmaf(mn, sink.s1[t], mx * sink.s2[t]));
+          float v = bf16_round(sink.acc[t]);
           __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
           if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
           if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
