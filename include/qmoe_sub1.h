@@ -199,8 +199,9 @@ int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, cons
  *   2. the caller forms blk_base int64[total_rows / 32 + 1], the exclusive prefix sum, and allocates
  *      16 * blk_base[last] bytes;
  *   3. qmoe_moe_interleave_emit fills them;
- *   4. qmoe_moe_grouped_ffn_interleaved is qmoe_moe_grouped_ffn reading the copy (experts on the
- *      tensor-core tile path still read codes_dev with dec_dev). */
+ *   4. qmoe_moe_grouped_ffn_interleaved is qmoe_moe_grouped_ffn reading the copy.  Experts on the
+ *      tensor-core tile path still read codes_dev with dec_dev; codes_dev may be NULL (a store that
+ *      freed its row-by-row streams), which turns that path off. */
 typedef struct qmoe_interleaved_store {
   const void *codes;       /* 16-byte entries, device */
   const int64_t *blk_base; /* [total_rows / 32 + 1], device */

@@ -439,7 +439,7 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
                              const qmoe_interleaved_store *ils, const int32_t *offsets_dev,
                              const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
                              int max_slots, int d_model, int d_ff, int device, void *stream) {
-  if (!(dec_dev && codes_dev && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev)) {
+  if (!(dec_dev && (codes_dev || ils) && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev)) {
     set_error("%s: null device pointer", fn);
     return QMOE_ERR_INVALID_ARG;
   }

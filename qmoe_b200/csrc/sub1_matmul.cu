@@ -862,7 +862,9 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   ph[1].capacity = (int)item_capacity(max_slots, d_model);
   ph[1].height = d_model;
   ph[1].which = 1;
-  const int tile_min = tab.conforming ? tile_min_tokens() : 0;
+  // The tile path decodes the row-by-row streams; a store that kept only its interleaved copy
+  // (codes == nullptr) sends every expert through the per-row kernel.
+  const int tile_min = tab.conforming && codes != nullptr ? tile_min_tokens() : 0;
   QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, 2 * sms, header, ph[0], ph[1]);
   QMOE_CUDA(cudaGetLastError());
   int4 *tile_wi = ph[1].items + ph[1].capacity;

@@ -68,7 +68,8 @@ class SwitchDecoderLM:
     """``n_layers`` blocks of (self-attention, MoE FFN); greedy generation with a static KV cache."""
 
     def __init__(self, d_model: int, d_ff: int, n_experts: int, n_layers: int, n_heads: int, vocab: int,
-                 max_len: int, device, seed: int = 0, rank: int = 0, world: int = 1, group=None):
+                 max_len: int, device, seed: int = 0, rank: int = 0, world: int = 1, group=None,
+                 drop_reference_layout: bool = True):
         self.d, self.h, self.hd, self.L, self.vocab, self.max_len = d_model, n_heads, d_model // n_heads, n_layers, vocab, max_len
         self.dev = torch.device(device)
         g = torch.Generator().manual_seed(seed * 9973 + 1)
@@ -85,6 +86,8 @@ class SwitchDecoderLM:
         for layer in range(n_layers):
             ids = [layer * n_experts + e for e in range(rank * local, (rank + 1) * local)]   # distinct seeds per layer
             store = synth.build_store(d_model, d_ff, ids, seed, self.dev)
+            if drop_reference_layout and store.il_codes is not None:
+                store.drop_reference_layout()       # 15 layers of both layouts would not fit one GPU
             router = (torch.randn(n_experts, d_model, generator=g) / math.sqrt(d_model)).bfloat16().float()
             self.blocks.append({
                 "ln1": torch.ones(d_model, dtype=torch.bfloat16, device=self.dev),
@@ -92,6 +95,8 @@ class SwitchDecoderLM:
                 "wqkv": dense(3 * d_attn, d_model), "wo": dense(d_model, d_attn),
                 "moe": ReplicatedTokenMoE(router, store, n_experts, rank, world, group),
             })
+        if drop_reference_layout:
+            torch.cuda.empty_cache()                # hand the freed streams back before graphs are captured
         self.k_cache = torch.zeros(n_layers, self.h, max_len, self.hd, dtype=torch.bfloat16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
 

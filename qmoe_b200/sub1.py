@@ -196,12 +196,26 @@ class ExpertStore:
     @property
     def resident_bytes(self) -> int:
         """Device bytes held, including the interleaved copy."""
-        extra = 0 if self.il_codes is None else self.il_codes.numel() * 4 + self.blk_base.numel() * 8
-        return self.compressed_bytes + extra
+        total = self.row_off.numel() * 4 + self.minmax.numel() * 2
+        if self.codes is not None:
+            total += self.codes.numel() * 2
+        if self.il_codes is not None:
+            total += self.il_codes.numel() * 4 + self.blk_base.numel() * 8 + 3 * 4 * _lib.DICT_COUNT
+        return total
+
+    def drop_reference_layout(self) -> None:
+        """Free the row-by-row streams and keep only the interleaved copy (about half the device
+        memory).  Afterwards :meth:`matrix` is unavailable and experts with many tokens stay on the
+        per-row kernel (the tensor-core tile path reads the row-by-row streams)."""
+        if self.il_codes is None:
+            raise RuntimeError("store has no interleaved copy to fall back on")
+        self._code_elems = self.codes.numel()
+        self.codes = None
 
     @property
     def compressed_bytes(self) -> int:
-        return self.codes.numel() * 2 + self.row_off.numel() * 4 + self.minmax.numel() * 2
+        n = self.codes.numel() if self.codes is not None else self._code_elems
+        return n * 2 + self.row_off.numel() * 4 + self.minmax.numel() * 2
 
     def matrix_bytes(self, m: int) -> int:
         """Algorithmic bytes of one matrix: codes + row offsets + (min, max) pairs."""
@@ -211,6 +225,8 @@ class ExpertStore:
     def matrix(self, m: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         """(w_comp, row_off, ter_minmax) views of matrix ``m`` in the reference's per-matrix layout."""
         d = self.host_descs[m]
+        if self.codes is None:
+            raise RuntimeError("the row-by-row streams of this store were dropped")
         return (self.codes[d.code_base:d.code_base + d.n_codes],
                 self.row_off[d.rowoff_base:d.rowoff_base + d.height + 1],
                 self.minmax[2 * d.minmax_base:2 * (d.minmax_base + d.height)])
@@ -343,7 +359,8 @@ def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max
     assert xs.is_contiguous() and xs.shape[1] == store.d_model
     if store.il_codes is not None:
         _lib.check(L.qmoe_moe_grouped_ffn_interleaved(
-            DEC(dev).data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(), store.minmax.data_ptr(),
+            DEC(dev).data_ptr(), None if store.codes is None else store.codes.data_ptr(),
+            store.row_off.data_ptr(), store.minmax.data_ptr(),
             store.descs.data_ptr(), ctypes.addressof(store.il_struct), offsets.data_ptr(),
             xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(), store.n_experts, max_slots,
             store.d_model, store.d_ff, dev.index, _s(dev)))

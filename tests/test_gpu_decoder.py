@@ -47,7 +47,7 @@ def _reference_forward(model, ids):
 def test_decoder_blocks_match_dense_reference_and_graph_decoding():
     dev = torch.device("cuda", 0)
     model = SwitchDecoderLM(d_model=128, d_ff=256, n_experts=8, n_layers=2, n_heads=4, vocab=512,
-                            max_len=32, device=dev, seed=3)
+                            max_len=32, device=dev, seed=3, drop_reference_layout=False)
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 512, (12,), generator=g).to(dev)
     logits = model.forward(ids, torch.arange(12, device=dev))
@@ -59,3 +59,8 @@ def test_decoder_blocks_match_dense_reference_and_graph_decoding():
     assert model.last_generate_used_graph
     assert torch.equal(eager, graphed)
     assert eager.shape == (10,) and int(eager.max()) < 512
+    # the same model holding only the interleaved copies of its experts (how the benchmark runs it)
+    for b in model.blocks:
+        b["moe"].store.drop_reference_layout()
+    assert torch.equal(model.forward(ids, torch.arange(12, device=dev)), logits)
+    assert torch.equal(model.generate(ids, 10, use_graph=True), eager)

@@ -121,3 +121,68 @@ def test_tensor_core_tile_path_for_heavily_loaded_experts(dev, small_layer):
         if c:
             assert rel_err(ys[pos:pos + c], experts[e].oracle_ffn(xs[pos:pos + c])) <= TOL, (e, c)
         pos += c
+
+
+def _plain_copy(store, **kw):
+    """The same store without / with a differently built interleaved copy."""
+    from qmoe_b200.sub1 import ExpertStore
+    return ExpertStore(store.codes, store.row_off, store.minmax, store.host_descs, store.d_model, store.d_ff, **kw)
+
+
+def test_interleaved_copy_holds_the_same_codes(dev, small_layer):
+    """Undo the lane interleaving and the renumbering on the host: every row's codes come back."""
+    _, store = small_layer
+    assert store.il_codes is not None
+    il = store.il_codes.cpu().numpy().view(np.uint16).reshape(-1, 8)          # [16-byte entry, 8 codes]
+    base = store.blk_base.cpu().numpy()
+    inverse = np.empty(65536, np.int64)
+    inverse[store.remap.cpu().numpy()] = np.arange(65536)
+    codes = store.codes.cpu().numpy().view(np.uint16)
+    row_off = store.row_off.cpu().numpy()
+    for d in store.host_descs:
+        for row in range(d.height):
+            b, e = row_off[d.rowoff_base + row], row_off[d.rowoff_base + row + 1]
+            gblk, lane = (d.minmax_base + row) // 32, row % 32
+            chunks = (base[gblk + 1] - base[gblk]) // 32
+            mine = il[base[gblk] + lane:base[gblk] + 32 * chunks:32].reshape(-1)
+            assert len(mine) >= e - b
+            assert (inverse[mine[:e - b]] == codes[d.code_base + b:d.code_base + e]).all()
+            assert (mine[e - b:] == store.remap.cpu().numpy()[0] % 65536).all()   # padding = code 0, renumbered
+
+
+@pytest.mark.parametrize("variant", ["row_by_row", "interleaved_plain_numbers", "interleaved_only"])
+def test_interleaved_and_row_by_row_stores_give_identical_results(dev, small_layer, variant):
+    """Same codes, same order of accumulation: the layouts must agree bit for bit."""
+    experts, store = small_layer
+    counts = [3, 9, 1, 0, 4, 2, 2, 5]
+    n = sum(counts)
+    xs = synth.tokens(n, store.d_model, seed=5).to(dev)
+    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+    want = sub1.grouped_ffn(store, offsets, xs, n)
+    if variant == "row_by_row":
+        other = _plain_copy(store, interleave=False)
+        assert other.il_codes is None
+    elif variant == "interleaved_plain_numbers":
+        other = _plain_copy(store, interleave=False)
+        other.interleave(renumber=False)
+    else:
+        other = _plain_copy(store)
+        other.drop_reference_layout()
+        assert other.codes is None and other.compressed_bytes == store.compressed_bytes
+        with pytest.raises(RuntimeError):
+            other.matrix(0)
+    got = sub1.grouped_ffn(other, offsets, xs, n)
+    assert torch.equal(got[:n], want[:n])
+    assert rel_err(got[:counts[0]], experts[0].oracle_ffn(xs[:counts[0]].cpu())) <= TOL
+
+
+def test_remap_tables_reject_a_non_permutation(dev):
+    from qmoe_b200 import _lib
+    remap = torch.arange(65536, dtype=torch.int32, device=dev)
+    remap[7] = 8                                                  # two codes onto one number
+    tab = torch.empty(65536, dtype=torch.int32, device=dev)
+    dec_out = torch.empty(131072, dtype=torch.int32, device=dev)
+    rc = _lib.load().qmoe_sub1_remap_tables(sub1.DEC(dev).data_ptr(), remap.data_ptr(), tab.data_ptr(),
+                                            dec_out.data_ptr(), dev.index, None)
+    assert rc == _lib.ERR_INVALID_ARG
+    assert b"permutation" in _lib.load().qmoe_last_error()
