@@ -189,6 +189,35 @@ __device__ __forceinline__ float bf16_round(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
+template <int T, class SinkT>
+__device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink, int row, int tok0, int ntok) {
+#pragma unroll
+  for (int t = 0; t < T; t++) {
+    if (t < ntok) {
+      // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
+      float v = bf16_round(sink.acc[t]);
+      __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
+      if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
+      if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
+      *yp = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+template <int T, class SinkT>
+__device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wlim, int tok0, int ntok,
+                                             typename SinkT::elem *xs) {
+  // xs[c][t] = x[tok0 + t][c], zero beyond the width / token count.
+  for (int c = threadIdx.x; c < wlim + kPad; c += blockDim.x) {
+#pragma unroll
+    for (int t = 0; t < T; t++) {
+      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
+      if (c < W && t < ntok) v = a.x[(long long)(tok0 + t) * a.x_stride + c];
+      xs[c * T + t] = SinkT::stage(v);
+    }
+  }
+}
+
 template <int T, bool GENERAL, class SinkT, bool IL = false, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                              int nrows, int tok0, int ntok, typename SinkT::elem *xs,
@@ -197,15 +226,7 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
 
-  // Stage the token group: xs[c][t] = x[tok0 + t][c], zero beyond the width / token count.
-  for (int c = tid; c < wlim + kPad; c += blockDim.x) {
-#pragma unroll
-    for (int t = 0; t < T; t++) {
-      __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-      if (c < W && t < ntok) v = a.x[(long long)(tok0 + t) * a.x_stride + c];
-      xs[c * T + t] = SinkT::stage(v);
-    }
-  }
+  stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs);
   __syncthreads();
 
   if (tid < nrows) {
@@ -231,17 +252,7 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
       walk_row<GENERAL>(StreamFetch{codes_m - mis}, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
     }
 
-#pragma unroll
-    for (int t = 0; t < T; t++) {
-      if (t < ntok) {
-        // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
-        float r = bf16_round(sink.acc[t]);
-        __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
-        if (a.flags & QMOE_FLAG_ACCUMULATE) r = bf16_round(__bfloat162float(*yp) + r);
-        if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
-        *yp = __float2bfloat16_rn(r);
-      }
-    }
+    store_row<T>(a, sink, row, tok0, ntok);
   }
 }
 
@@ -269,25 +280,69 @@ __global__ void __launch_bounds__(kRowsPerItem) k_matmul_uniform(const MatmulArg
 // serial depth of a row drops from its number of codes to that number / 32.
 constexpr int kWarpRowThreads = 256;
 
+// One row by a whole warp: code_at(i) returns code i of the row (0 <= i < n), `tab` / `dec` are the
+// tables for those code values.  Leaves the row's sums, reduced over the lanes, in sink.acc.
+template <bool GENERAL, class SinkT, class CodeAt>
+__device__ __forceinline__ void warp_row_sum(const CodeAt &code_at, int n, const uint32_t *__restrict__ tab,
+                                             const int32_t *__restrict__ dec, uint32_t limit, SinkT &sink,
+                                             int lane) {
+  constexpr int S = SinkT::kShift;
+  uint32_t row_pos = 0;
+  // Two groups of 32 codes per iteration (both dictionary lookups in flight together), and the
+  // codes of the next iteration are requested before this one is processed.
+  uint32_t code0 = 0, code1 = 0;
+  if (lane < n) code0 = code_at(lane);
+  if (32 + lane < n) code1 = code_at(32 + lane);
+  for (int base = 0; base < n; base += 64) {
+    const bool v0 = base + lane < n, v1 = base + 32 + lane < n;
+    const uint32_t c0 = code0, c1 = code1;
+    uint32_t e0 = kEntryNull, e1 = kEntryNull;
+    if (v0) e0 = __ldg(tab + c0);
+    if (v1) e1 = __ldg(tab + c1);
+    if (base + 64 + lane < n) code0 = code_at(base + 64 + lane);
+    if (base + 96 + lane < n) code1 = code_at(base + 96 + lane);
+    uint32_t len0 = 2u * entry_len(e0), len1 = 2u * entry_len(e1);
+    bool d0 = false, d1 = false;
+    if (GENERAL) {
+      d0 = (e0 & 0xffu) == 0x80u;
+      d1 = (e1 & 0xffu) == 0x80u;
+      if (d0) len0 = 2u * min((uint32_t)__ldg(dec + 2 * c0) & 15u, 14u);
+      if (d1) len1 = 2u * min((uint32_t)__ldg(dec + 2 * c1) & 15u, 14u);
+    }
+    uint32_t i0 = len0, i1 = len1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t u0 = __shfl_up_sync(0xffffffffu, i0, o);
+      const uint32_t u1 = __shfl_up_sync(0xffffffffu, i1, o);
+      if (lane >= o) {
+        i0 += u0;
+        i1 += u1;
+      }
+    }
+    const uint32_t total0 = __shfl_sync(0xffffffffu, i0, 31), total1 = __shfl_sync(0xffffffffu, i1, 31);
+    const uint32_t p0 = min(row_pos + i0 - len0, limit);
+    const uint32_t p1 = min(row_pos + total0 + i1 - len1, limit);
+    if (GENERAL && d0) dense_code(dec, c0, (int)p0, sink);
+    else sink.entry(e0, p0 << S);
+    if (GENERAL && d1) dense_code(dec, c1, (int)p1, sink);
+    else sink.entry(e1, p1 << S);
+    row_pos = min(row_pos + total0 + total1, limit);
+  }
+#pragma unroll
+  for (int t = 0; t < (int)(sizeof(sink.acc) / sizeof(float)); t++) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sink.acc[t] += __shfl_xor_sync(0xffffffffu, sink.acc[t], o);
+  }
+}
+
 template <int T, bool GENERAL>
 __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nrows, int tok0, int ntok, float *xs) {
   using SinkT = MatSink<T, true>;
   const qmoe_matrix_desc &d = a.single;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  const int W = d.width;
-  const int wlim = (W + 1) & ~1;
-  for (int c = tid; c < wlim + kPad; c += blockDim.x) {
-#pragma unroll
-    for (int t = 0; t < T; t++) {
-      float v = 0.f;
-      if (c < W && t < ntok) v = __bfloat162float(a.x[(long long)(tok0 + t) * a.x_stride + c]);
-      xs[c * T + t] = v;
-    }
-  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int wlim = (d.width + 1) & ~1;
+  stage_tokens<T, SinkT>(a, d.width, wlim, tok0, ntok, xs);
   __syncthreads();
-
-  constexpr int S = SinkT::kShift;
-  const uint32_t limit = (uint32_t)wlim;
   for (int r = warp; r < nrows; r += nwarps) {
     const int row = row0 + r;
     long long b = a.row_off[row], e = a.row_off[row + 1];
@@ -296,64 +351,39 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
     const __nv_bfloat162 mm = a.minmax[row];
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
-    uint32_t row_pos = 0;
-    // Two groups of 32 codes per iteration (both dictionary lookups in flight together), and the
-    // codes of the next iteration are requested before this one is processed.
-    uint32_t code0 = 0, code1 = 0;
-    if (b + lane < e) code0 = a.codes[b + lane];
-    if (b + 32 + lane < e) code1 = a.codes[b + 32 + lane];
-    for (long long base = b; base < e; base += 64) {
-      const bool v0 = base + lane < e, v1 = base + 32 + lane < e;
-      const uint32_t c0 = code0, c1 = code1;
-      uint32_t e0 = kEntryNull, e1 = kEntryNull;
-      if (v0) e0 = __ldg(a.tab + c0);
-      if (v1) e1 = __ldg(a.tab + c1);
-      if (base + 64 + lane < e) code0 = a.codes[base + 64 + lane];
-      if (base + 96 + lane < e) code1 = a.codes[base + 96 + lane];
-      uint32_t len0 = 2u * entry_len(e0), len1 = 2u * entry_len(e1);
-      bool d0 = false, d1 = false;
-      if (GENERAL) {
-        d0 = (e0 & 0xffu) == 0x80u;
-        d1 = (e1 & 0xffu) == 0x80u;
-        if (d0) len0 = 2u * min((uint32_t)__ldg(a.dec + 2 * c0) & 15u, 14u);
-        if (d1) len1 = 2u * min((uint32_t)__ldg(a.dec + 2 * c1) & 15u, 14u);
-      }
-      uint32_t i0 = len0, i1 = len1;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t u0 = __shfl_up_sync(0xffffffffu, i0, o);
-        const uint32_t u1 = __shfl_up_sync(0xffffffffu, i1, o);
-        if (lane >= o) {
-          i0 += u0;
-          i1 += u1;
-        }
-      }
-      const uint32_t total0 = __shfl_sync(0xffffffffu, i0, 31), total1 = __shfl_sync(0xffffffffu, i1, 31);
-      const uint32_t p0 = min(row_pos + i0 - len0, limit);
-      const uint32_t p1 = min(row_pos + total0 + i1 - len1, limit);
-      if (GENERAL && d0) dense_code(a.dec, c0, (int)p0, sink);
-      else sink.entry(e0, p0 << S);
-      if (GENERAL && d1) dense_code(a.dec, c1, (int)p1, sink);
-      else sink.entry(e1, p1 << S);
-      row_pos = min(row_pos + total0 + total1, limit);
-    }
-#pragma unroll
-    for (int t = 0; t < T; t++) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) sink.acc[t] += __shfl_xor_sync(0xffffffffu, sink.acc[t], o);
-    }
-    if (lane == 0) {
-#pragma unroll
-      for (int t = 0; t < T; t++) {
-        if (t < ntok) {
-          float v = bf16_round(sink.acc[t]);
-          __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
-          if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
-          if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
-          *yp = __float2bfloat16_rn(v);
-        }
-      }
-    }
+    const uint16_t *src = a.codes + b;
+    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)src[i]; }, (int)(e - b), a.tab, a.dec, (uint32_t)wlim, sink,
+                          lane);
+    if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
+  }
+}
+
+// The same for a work item of an interleaved store: code i of row l of a block is element i % 8
+// of the 16-byte entry (i / 8) * 32 + l.
+template <int T, bool GENERAL, class SinkT>
+__device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
+                                               int tok0, int ntok, typename SinkT::elem *xs) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int wlim = (d.width + 1) & ~1;
+  stage_tokens<T, SinkT>(a, d.width, wlim, tok0, ntok, xs);
+  __syncthreads();
+  const int32_t *ro = a.row_off + d.rowoff_base;
+  for (int r = warp; r < nrows; r += nwarps) {
+    const int row = row0 + r;
+    long long b = ro[row], e = ro[row + 1];
+    b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+    e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
+    const long long gblk = (d.minmax_base + row) >> 5;
+    const long long first = a.blk_base[gblk];
+    const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;
+    const int n = (int)(e - b < room ? e - b : room);
+    const uint16_t *src = reinterpret_cast<const uint16_t *>(a.il + first + (row & 31));
+    const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
+    SinkT sink;
+    sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
+    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); }, n, a.il_tab,
+                          a.il_dec, (uint32_t)wlim, sink, lane);
+    if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
   }
 }
 
@@ -410,6 +440,35 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     else
       process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
                                                       reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
+    __syncthreads();  // xs and s_item are rewritten by the next round
+  }
+}
+
+// Work items of an interleaved store whose rows are shared out one per WARP: the rows that are left
+// when a matrix's height is not a multiple of the 1024 rows a CTA of k_matmul_grouped takes, and
+// whole layers when so few experts are active (one token per step while generating) that rows per
+// thread could not fill the GPU.  Several CTAs per SM; the table is read through L1/L2.
+template <bool GENERAL>
+__global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const MatmulArgs a) {
+  extern __shared__ __align__(16) uint32_t smem_u32[];
+  __shared__ int s_item;
+  const int n_items = a.header[0];
+  for (;;) {
+    if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
+    __syncthreads();
+    const int i = s_item;
+    if (i >= n_items) break;
+    const int4 it = a.items[i];
+    const qmoe_matrix_desc d = a.descs[it.x];
+    const int nrows = it.w & 0xffff, ntok = it.w >> 16;
+    if (ntok <= 1)
+      warp_rows_item<1, GENERAL, MatSink<1, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(smem_u32));
+    else if (ntok == 2)
+      warp_rows_item<2, GENERAL, MatSink<2, false>>(a, d, it.y, nrows, it.z, ntok,
+                                                    reinterpret_cast<__nv_bfloat16 *>(smem_u32));
+    else
+      warp_rows_item<4, GENERAL, MatSink<4, false>>(a, d, it.y, nrows, it.z, ntok,
+                                                    reinterpret_cast<__nv_bfloat16 *>(smem_u32));
     __syncthreads();  // xs and s_item are rewritten by the next round
   }
 }
@@ -490,6 +549,8 @@ static int set_smem_limits() {
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemPerCta));
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped_warp<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   return QMOE_OK;
 }
 
@@ -694,28 +755,36 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 }
 
 // ---- grouped expert FFN -------------------------------------------------------------------------
-// Work buffer layout: int header[16] | int4 items_wi[cap_wi] | int4 items_wo[cap_wo] | tile items of
-// wi | tile items of wo, with cap = max_slots * ceil(height / 1024) + kExtraItems.
+// Work buffer layout: int header[16] | int4 items_wi[cap] | int4 items_wo[cap] | tile items of wi |
+// tile items of wo | warp items of wi | warp items of wo.
 // header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter,
-// [4] / [5] = tile items of wi / wo, [8] = timeouts seen by the tile kernels.
+// [4] / [5] = tile items of wi / wo, [8] = timeouts seen by the tile kernels, [10] .. [13] = counts
+// and fetch counters of the warp items of wi and wo.
 //
-// Item granularity is chosen here, on the device, from the number of (expert, token group) pairs:
-// a full layer (hundreds of pairs) uses blocks of up to 1024 rows, one row per thread of the
-// persistent CTAs; when only a few experts are active (one token per step while generating) the rows
-// are cut into smaller blocks so that about two items per SM exist and every SM takes part, instead
-// of nine CTAs walking thousand-row blocks.
+// Who takes which rows is decided here, on the device, from the number of (expert, token group)
+// pairs.  A full layer (hundreds of pairs) is cut into items of up to 1024 rows for
+// k_matmul_grouped, one row per thread of its persistent CTAs.  With an interleaved store, rows that
+// do not fill such an item (heights like 2080 = 2 x 1024 + 32) go to k_matmul_grouped_warp in items
+// of 32 rows, and so does everything when so few pairs exist (one token per step while generating)
+// that thousand-row items would leave most SMs idle.  Without an interleaved store the height is cut
+// into equal items, and into finer ones when few pairs exist.
 constexpr int kExtraItems = 1024;
+constexpr int kWarpItemRows = 32;
+constexpr int kWarpRemainderMax = 256;      // most rows of a matrix that are left to the warp kernel
+constexpr int kSmallRows = 2 * 148 * 1024;  // fewer rows in total: the warp kernel takes all of them
 
 struct WorkPhase {
   int4 *items;
   int capacity;  // entries available in `items`
+  int4 *warp_items;
+  int warp_capacity;
   int height;    // rows of the phase's matrices (d_ff for wi, d_model for wo)
   int which;     // 0 = wi (matrix 2e), 1 = wo (matrix 2e + 1)
 };
 
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
                                                      int max_slots, int tile_min, int target_items,
-                                                     int *header, WorkPhase p0, WorkPhase p1) {
+                                                     int use_warp, int *header, WorkPhase p0, WorkPhase p1) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_total;
@@ -746,15 +815,25 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
 
   for (int phase = 0; phase < 2; phase++) {
     const WorkPhase p = phase == 0 ? p0 : p1;
-    // rows per item: as many as a CTA has threads, fewer while that leaves SMs without work
-    int rpc = rows_per_chunk_dev(p.height, kGroupedThreads);
-    if (total > 0) {
-      const long long want = ((long long)total * p.height + target_items - 1) / target_items;
+    const int H = p.height;
+    // rows [0, main_rows) in items of rpc rows for the per-thread kernel, the rest in warp items
+    int rpc = rows_per_chunk_dev(H, kGroupedThreads), main_rows = H;
+    if (use_warp) {
+      const int rest = H % kGroupedThreads;
+      if ((long long)total * H <= kSmallRows) {
+        main_rows = 0;
+      } else if (H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) {
+        main_rows = H - rest;
+        rpc = kGroupedThreads;
+      }
+    } else if (total > 0) {
+      const long long want = ((long long)total * H + target_items - 1) / target_items;
       int fine = (int)((want + 31) / 32 * 32);
       fine = fine < 32 ? 32 : fine;
-      if (fine < rpc && (long long)total * ((p.height + fine - 1) / fine) <= p.capacity) rpc = fine;
+      if (fine < rpc && (long long)total * ((H + fine - 1) / fine) <= p.capacity) rpc = fine;
     }
-    const int chunks = (p.height + rpc - 1) / rpc;
+    const int chunks = (main_rows + rpc - 1) / rpc;
+    const int wchunks = (H - main_rows + kWarpItemRows - 1) / kWarpItemRows;
     if (tid == 0) s_base = 0;
     __syncthreads();
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
@@ -783,12 +862,20 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
       for (int g = 0; g < groups; g++) {
         const int gi = base + g;
-        if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
+        // cannot happen for valid offsets
+        if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity ||
+            (long long)(gi + 1) * wchunks > p.warp_capacity)
+          break;
         const int tok0 = first + g * kMaxGroup;
         const int ntok = min(kMaxGroup, count - g * kMaxGroup);
         for (int k = 0; k < chunks; k++) {
           const int row0 = k * rpc;
-          p.items[(size_t)gi * chunks + k] = make_int4(2 * e + p.which, row0, tok0, min(rpc, p.height - row0) | (ntok << 16));
+          p.items[(size_t)gi * chunks + k] = make_int4(2 * e + p.which, row0, tok0, min(rpc, main_rows - row0) | (ntok << 16));
+        }
+        for (int k = 0; k < wchunks; k++) {
+          const int row0 = main_rows + k * kWarpItemRows;
+          p.warp_items[(size_t)gi * wchunks + k] =
+              make_int4(2 * e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (ntok << 16));
         }
       }
       __syncthreads();
@@ -796,8 +883,11 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       __syncthreads();
     }
     if (tid == 0) {
-      header[2 * phase] = min(s_base, max_slots) * chunks;
+      const int groups_done = min(s_base, max_slots);
+      header[2 * phase] = groups_done * chunks;
       header[2 * phase + 1] = 0;
+      header[10 + 2 * phase] = groups_done * wchunks;
+      header[11 + 2 * phase] = 0;
     }
     __syncthreads();
   }
@@ -839,8 +929,13 @@ static int64_t item_capacity(int max_slots, int height) {
   return (int64_t)max_slots * chunk_count(height, kGroupedThreads) + kExtraItems;
 }
 
+static int64_t warp_item_capacity(int max_slots) {
+  return (int64_t)max_slots * (kWarpRemainderMax / kWarpItemRows) + kSmallRows / kWarpItemRows + kExtraItems;
+}
+
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
-  return 64 + (item_capacity(max_slots, d_ff) + item_capacity(max_slots, d_model)) * (int64_t)sizeof(int4) +
+  return 64 + (item_capacity(max_slots, d_ff) + item_capacity(max_slots, d_model) +
+               2 * warp_item_capacity(max_slots)) * (int64_t)sizeof(int4) +
          tile_work_bytes(max_slots, d_model, d_ff);
 }
 
@@ -862,13 +957,18 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   ph[1].capacity = (int)item_capacity(max_slots, d_model);
   ph[1].height = d_model;
   ph[1].which = 1;
+  int4 *tile_wi = ph[1].items + ph[1].capacity;
+  int4 *tile_wo = tile_wi + (size_t)tile_cap_blocks(max_slots) * ((d_ff + 127) / 128);
+  ph[0].warp_items = tile_wo + (size_t)tile_cap_blocks(max_slots) * ((d_model + 127) / 128);
+  ph[0].warp_capacity = ph[1].warp_capacity = (int)warp_item_capacity(max_slots);
+  ph[1].warp_items = ph[0].warp_items + ph[0].warp_capacity;
+  const bool il = ils != nullptr;
   // The tile path decodes the row-by-row streams; a store that kept only its interleaved copy
   // (codes == nullptr) sends every expert through the per-row kernel.
   const int tile_min = tab.conforming && codes != nullptr ? tile_min_tokens() : 0;
-  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, 2 * sms, header, ph[0], ph[1]);
+  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, 2 * sms, il ? 1 : 0,
+              header, ph[0], ph[1]);
   QMOE_CUDA(cudaGetLastError());
-  int4 *tile_wi = ph[1].items + ph[1].capacity;
-  int4 *tile_wo = tile_wi + (size_t)tile_cap_blocks(max_slots) * ((d_ff + 127) / 128);
   if (tile_min > 0) {
     rc = launch_build_tile_work(offsets, n_experts, tile_min, d_model, d_ff, max_slots, header, tile_wi, tile_wo, stream);
     if (rc) return rc;
@@ -881,7 +981,6 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   a.row_off = row_off;
   a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
   a.descs = descs;
-  const bool il = ils != nullptr;
   if (il) {
     a.il = reinterpret_cast<const uint4 *>(ils->codes);
     a.blk_base = reinterpret_cast<const long long *>(ils->blk_base);
@@ -921,6 +1020,17 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     else
       QMOE_LAUNCH((k_matmul_grouped<true, false>), grid, kGroupedThreads, smem, stream, a);
     QMOE_CUDA(cudaGetLastError());
+    if (il) {
+      MatmulArgs w = a;
+      w.items = ph[phase].warp_items;
+      w.header = header + 10 + 2 * phase;
+      const size_t wsmem = grouped_x_bytes(width, kMaxGroup);
+      if (tab.conforming)
+        QMOE_LAUNCH(k_matmul_grouped_warp<false>, (unsigned)(4 * sms), kWarpRowThreads, wsmem, stream, w);
+      else
+        QMOE_LAUNCH(k_matmul_grouped_warp<true>, (unsigned)(4 * sms), kWarpRowThreads, wsmem, stream, w);
+      QMOE_CUDA(cudaGetLastError());
+    }
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }
   return QMOE_OK;
