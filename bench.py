@@ -556,6 +556,7 @@ def run_generate(args):
             "data": "synthetic (seeded dense bf16 weights N(0,0.02), seeded ternary experts, random prompt ids)",
             "timing_last_sample": getattr(model, "last_timing", None),
             "first_tokens": out[:8].tolist()}), flush=True)
+    model.close()                      # the graph holds the NCCL communicator
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize()

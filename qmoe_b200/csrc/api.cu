@@ -464,7 +464,8 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     set_error("%s: null activation pointer", fn);
     return QMOE_ERR_INVALID_ARG;
   }
-  if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 || (ils && (reinterpret_cast<uintptr_t>(ils->codes) & 15u) != 0)) {
+  if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 ||
+      (ils && ((reinterpret_cast<uintptr_t>(ils->codes) | reinterpret_cast<uintptr_t>(ils->table)) & 15u) != 0)) {
     set_error("%s: code stores must be 16-byte aligned", fn);
     return QMOE_ERR_INVALID_ARG;
   }

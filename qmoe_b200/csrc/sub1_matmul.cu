@@ -415,7 +415,9 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
   using Lookup = typename std::conditional<IL, HotLookupLow, HotLookup>::type;
   Lookup lookup;
   if constexpr (IL) {
-    for (uint32_t i = threadIdx.x; i < n_hot; i += blockDim.x) hot[i] = __ldg(a.il_tab + i);
+    // n_hot is a multiple of 1024 and both tables are 16-byte aligned
+    for (uint32_t i = threadIdx.x; i < n_hot / 4; i += blockDim.x)
+      reinterpret_cast<uint4 *>(hot)[i] = __ldg(reinterpret_cast<const uint4 *>(a.il_tab) + i);
     lookup = HotLookupLow{(uint32_t)__cvta_generic_to_shared(hot), a.il_tab, n_hot};
   } else {
     for (uint32_t i = threadIdx.x; i < kHotSlots; i += blockDim.x)
@@ -766,12 +768,13 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 // k_matmul_grouped, one row per thread of its persistent CTAs.  With an interleaved store, rows that
 // do not fill such an item (heights like 2080 = 2 x 1024 + 32) go to k_matmul_grouped_warp in items
 // of 32 rows, and so does everything when so few pairs exist (one token per step while generating)
-// that thousand-row items would leave most SMs idle.  Without an interleaved store the height is cut
-// into equal items, and into finer ones when few pairs exist.
+// that rows per thread could not fill the SMs.  In between, the items are made finer than 1024 rows
+// until there are about two per SM.  Without an interleaved store there is no warp kernel.
 constexpr int kExtraItems = 1024;
 constexpr int kWarpItemRows = 32;
 constexpr int kWarpRemainderMax = 256;      // most rows of a matrix that are left to the warp kernel
-constexpr int kSmallRows = 2 * 148 * 1024;  // fewer rows in total: the warp kernel takes all of them
+constexpr int kSmallRows = 148 * 8 * 32;    // fewer rows in total (less than eight warps of rows per SM):
+                                            // the warp kernel takes all of them
 
 struct WorkPhase {
   int4 *items;
@@ -818,19 +821,19 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
     const int H = p.height;
     // rows [0, main_rows) in items of rpc rows for the per-thread kernel, the rest in warp items
     int rpc = rows_per_chunk_dev(H, kGroupedThreads), main_rows = H;
-    if (use_warp) {
-      const int rest = H % kGroupedThreads;
-      if ((long long)total * H <= kSmallRows) {
-        main_rows = 0;
-      } else if (H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) {
-        main_rows = H - rest;
-        rpc = kGroupedThreads;
-      }
+    if (use_warp && (long long)total * H <= kSmallRows) {
+      main_rows = 0;
     } else if (total > 0) {
+      const int rest = H % kGroupedThreads;
       const long long want = ((long long)total * H + target_items - 1) / target_items;
       int fine = (int)((want + 31) / 32 * 32);
       fine = fine < 32 ? 32 : fine;
-      if (fine < rpc && (long long)total * ((H + fine - 1) / fine) <= p.capacity) rpc = fine;
+      if (fine < rpc && (long long)total * ((H + fine - 1) / fine) <= p.capacity) {
+        rpc = fine;  // few pairs: finer items, so that every SM gets some
+      } else if (use_warp && H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) {
+        main_rows = H - rest;
+        rpc = kGroupedThreads;
+      }
     }
     const int chunks = (main_rows + rpc - 1) / rpc;
     const int wchunks = (H - main_rows + kWarpItemRows - 1) / kWarpItemRows;

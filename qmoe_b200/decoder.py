@@ -97,6 +97,8 @@ class SwitchDecoderLM:
             })
         if drop_reference_layout:
             torch.cuda.empty_cache()                # hand the freed streams back before graphs are captured
+        self._graph = None
+        self._step_ids = self._step_pos = None
         self.k_cache = torch.zeros(n_layers, self.h, max_len, self.hd, dtype=torch.bfloat16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
 
@@ -138,17 +140,25 @@ class SwitchDecoderLM:
         torch.cuda.synchronize(self.dev)
         t_prefill = time.perf_counter()
         out = [tok]
-        step_ids = tok.clone()
-        step_pos = torch.full((1,), p, dtype=torch.int64, device=self.dev)
+        if self._step_pos is None:
+            self._step_ids = tok.clone()
+            self._step_pos = torch.zeros(1, dtype=torch.int64, device=self.dev)
+        step_ids, step_pos = self._step_ids, self._step_pos
+        step_ids.copy_(tok)
+        step_pos.fill_(p)
         graph = None
         if use_graph and n_new > 4:
-            from .graph import GraphedStep
-            try:
-                graph = GraphedStep(lambda t: self.forward(t, step_pos)[-1].argmax().reshape(1), step_ids)
-            except Exception as exc:  # keep generating eagerly, but say so
-                import warnings
-                warnings.warn(f"CUDA-graph capture of the decode step failed, decoding eagerly: {exc!r}")
-                graph = None
+            # The decode step reads its position from a device tensor, so one captured graph serves
+            # every later call; it is captured on first use and kept until close().
+            if self._graph is None:
+                from .graph import GraphedStep
+                try:
+                    self._graph = GraphedStep(lambda t: self.forward(t, step_pos)[-1].argmax().reshape(1), step_ids)
+                    step_pos.fill_(p)                 # capture and its warm-up runs did not advance it
+                except Exception as exc:  # keep generating eagerly, but say so
+                    import warnings
+                    warnings.warn(f"CUDA-graph capture of the decode step failed, decoding eagerly: {exc!r}")
+            graph = self._graph
         self.last_generate_used_graph = graph is not None
         torch.cuda.synchronize(self.dev)
         t_capture = time.perf_counter()
@@ -165,6 +175,10 @@ class SwitchDecoderLM:
         t_end = time.perf_counter()
         self.last_timing = {"prefill_s": t_prefill - t_start, "graph_capture_s": t_capture - t_prefill,
                             "decode_s": t_end - t_capture, "decode_steps": n_new - 1}
-        if graph is not None:
-            graph.close()
         return torch.cat(out)
+
+    def close(self) -> None:
+        """Destroy the captured decode graph (before tearing down a process group it captured)."""
+        if self._graph is not None:
+            self._graph.close()
+            self._graph = None
