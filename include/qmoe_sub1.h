@@ -171,7 +171,7 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
 /* Inside qmoe_moe_grouped_ffn, experts with at least `tokens` tokens are multiplied on the tensor
  * cores (tcgen05): their rows are decoded once into bf16 tiles in shared memory and multiplied with
  * blocks of 64 tokens, instead of being re-decoded for every group of four tokens.  0 disables that
- * path; values below 8 are raised to 8.  Default 128 (or the environment variable
+ * path; values below 8 are raised to 8.  Default 448 (or the environment variable
  * QMOE_TILE_MIN_TOKENS), the measured break-even.  Returns the previous value.  No counterpart in
  * the reference, which runs one matvec per token (sub1.py:139-142). */
 int qmoe_moe_set_tile_min_tokens(int tokens);

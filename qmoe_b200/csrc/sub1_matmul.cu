@@ -218,10 +218,17 @@ __device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wli
   }
 }
 
+template <int T, bool GENERAL, class SinkT, class Lookup>
+__device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
+                                                 int nrows, int tok0, int ntok, typename SinkT::elem *xs,
+                                                 const Lookup &lookup);
+
+// Rows [row0, row0 + nrows) one per thread; with an interleaved store, `tail_rows` further rows
+// (what a height like 2080 leaves after blocks of 1024) one per warp, against the same staged x.
 template <int T, bool GENERAL, class SinkT, bool IL = false, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                              int nrows, int tok0, int ntok, typename SinkT::elem *xs,
-                                             const Lookup &lookup) {
+                                             const Lookup &lookup, int tail_rows = 0) {
   const int tid = threadIdx.x;
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
@@ -254,6 +261,9 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
 
     store_row<T>(a, sink, row, tok0, ntok);
   }
+  if constexpr (IL) {
+    if (tail_rows > 0) warp_rows_staged<T, GENERAL, SinkT>(a, d, row0 + nrows, tail_rows, tok0, ntok, xs, lookup);
+  }
 }
 
 // One CTA per (row block, token group) of a single matrix; the sparse table is read through L1/L2.
@@ -282,8 +292,8 @@ constexpr int kWarpRowThreads = 256;
 
 // One row by a whole warp: code_at(i) returns code i of the row (0 <= i < n), `tab` / `dec` are the
 // tables for those code values.  Leaves the row's sums, reduced over the lanes, in sink.acc.
-template <bool GENERAL, class SinkT, class CodeAt>
-__device__ __forceinline__ void warp_row_sum(const CodeAt &code_at, int n, const uint32_t *__restrict__ tab,
+template <bool GENERAL, class SinkT, class CodeAt, class Lookup>
+__device__ __forceinline__ void warp_row_sum(const CodeAt &code_at, int n, const Lookup &lookup,
                                              const int32_t *__restrict__ dec, uint32_t limit, SinkT &sink,
                                              int lane) {
   constexpr int S = SinkT::kShift;
@@ -297,8 +307,8 @@ __device__ __forceinline__ void warp_row_sum(const CodeAt &code_at, int n, const
     const bool v0 = base + lane < n, v1 = base + 32 + lane < n;
     const uint32_t c0 = code0, c1 = code1;
     uint32_t e0 = kEntryNull, e1 = kEntryNull;
-    if (v0) e0 = __ldg(tab + c0);
-    if (v1) e1 = __ldg(tab + c1);
+    if (v0) e0 = lookup(c0);
+    if (v1) e1 = lookup(c1);
     if (base + 64 + lane < n) code0 = code_at(base + 64 + lane);
     if (base + 96 + lane < n) code1 = code_at(base + 96 + lane);
     uint32_t len0 = 2u * entry_len(e0), len1 = 2u * entry_len(e1);
@@ -352,21 +362,20 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
     const uint16_t *src = a.codes + b;
-    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)src[i]; }, (int)(e - b), a.tab, a.dec, (uint32_t)wlim, sink,
-                          lane);
+    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)src[i]; }, (int)(e - b), GlobalLookup{a.tab}, a.dec,
+                          (uint32_t)wlim, sink, lane);
     if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
   }
 }
 
 // The same for a work item of an interleaved store: code i of row l of a block is element i % 8
 // of the 16-byte entry (i / 8) * 32 + l.
-template <int T, bool GENERAL, class SinkT>
-__device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
-                                               int tok0, int ntok, typename SinkT::elem *xs) {
+template <int T, bool GENERAL, class SinkT, class Lookup>
+__device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
+                                                 int nrows, int tok0, int ntok, typename SinkT::elem *xs,
+                                                 const Lookup &lookup) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int wlim = (d.width + 1) & ~1;
-  stage_tokens<T, SinkT>(a, d.width, wlim, tok0, ntok, xs);
-  __syncthreads();
   const int32_t *ro = a.row_off + d.rowoff_base;
   for (int r = warp; r < nrows; r += nwarps) {
     const int row = row0 + r;
@@ -381,10 +390,18 @@ __device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_m
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
-    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); }, n, a.il_tab,
+    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); }, n, lookup,
                           a.il_dec, (uint32_t)wlim, sink, lane);
     if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
   }
+}
+
+template <int T, bool GENERAL, class SinkT>
+__device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
+                                               int tok0, int ntok, typename SinkT::elem *xs) {
+  stage_tokens<T, SinkT>(a, d.width, (d.width + 1) & ~1, tok0, ntok, xs);
+  __syncthreads();
+  warp_rows_staged<T, GENERAL, SinkT>(a, d, row0, nrows, tok0, ntok, xs, GlobalLookup{a.il_tab});
 }
 
 // grid.x = row blocks of a.rpc rows, grid.y = token groups of kMaxGroup tokens.
@@ -431,17 +448,19 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     if (i >= n_items) break;
     const int4 it = a.items[i];
     const qmoe_matrix_desc d = a.descs[it.x];
-    const int nrows = it.w & 0xffff, ntok = it.w >> 16;
+    const int nrows = it.w & 0x7fff, ntok = it.w >> 16;
+    const int tail = (it.w & 0x8000) ? d.height - (it.y + nrows) : 0;
     // one token: fp32 activations (no conversion per gather); two and four: bf16, so that a gather
     // is one 4- or 8-byte shared load (two 4-byte words per lane cost twice the bank cycles)
     if (ntok <= 1)
-      process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+      process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup,
+                                                     tail);
     else if (ntok == 2)
       process_item<2, GENERAL, MatSink<2, false>, IL>(a, d, it.y, nrows, it.z, ntok,
-                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail);
     else
       process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
-                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail);
     __syncthreads();  // xs and s_item are rewritten by the next round
   }
 }
@@ -766,9 +785,10 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 // Who takes which rows is decided here, on the device, from the number of (expert, token group)
 // pairs.  A full layer (hundreds of pairs) is cut into items of up to 1024 rows for
 // k_matmul_grouped, one row per thread of its persistent CTAs.  With an interleaved store, rows that
-// do not fill such an item (heights like 2080 = 2 x 1024 + 32) go to k_matmul_grouped_warp in items
-// of 32 rows, and so does everything when so few pairs exist (one token per step while generating)
-// that rows per thread could not fill the SMs.  In between, the items are made finer than 1024 rows
+// do not fill such an item (heights like 2080 = 2 x 1024 + 32) are done one per warp by the CTA that
+// takes the matrix's last item, and when so few pairs exist (one token per step while generating)
+// that rows per thread could not fill the SMs, everything goes to k_matmul_grouped_warp in items of
+// 32 rows.  In between, the items are made finer than 1024 rows
 // until there are about two per SM.  Without an interleaved store there is no warp kernel.
 constexpr int kExtraItems = 1024;
 constexpr int kWarpItemRows = 32;
@@ -836,7 +856,10 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       }
     }
     const int chunks = (main_rows + rpc - 1) / rpc;
-    const int wchunks = (H - main_rows + kWarpItemRows - 1) / kWarpItemRows;
+    // what is left after the per-thread items: with none of those, items for the warp kernel;
+    // otherwise the CTA that takes the last per-thread item does them, one row per warp (bit 15)
+    const int wchunks = main_rows == 0 ? (H + kWarpItemRows - 1) / kWarpItemRows : 0;
+    const int tail_flag = main_rows > 0 && main_rows < H ? 0x8000 : 0;
     if (tid == 0) s_base = 0;
     __syncthreads();
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
@@ -873,10 +896,12 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
         const int ntok = min(kMaxGroup, count - g * kMaxGroup);
         for (int k = 0; k < chunks; k++) {
           const int row0 = k * rpc;
-          p.items[(size_t)gi * chunks + k] = make_int4(2 * e + p.which, row0, tok0, min(rpc, main_rows - row0) | (ntok << 16));
+          p.items[(size_t)gi * chunks + k] = make_int4(2 * e + p.which, row0, tok0,
+                                                       min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) |
+                                                           (ntok << 16));
         }
         for (int k = 0; k < wchunks; k++) {
-          const int row0 = main_rows + k * kWarpItemRows;
+          const int row0 = k * kWarpItemRows;
           p.warp_items[(size_t)gi * wchunks + k] =
               make_int4(2 * e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (ntok << 16));
         }
@@ -907,17 +932,18 @@ int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t 
                       cudaStream_t stream);
 
 // Experts with at least this many tokens take the tile path (0 disables it).  The default is the
-// measured break-even on a switch-large-128 layer with a skewed router: at 32-37 tokens per hot expert
-// the per-row kernel (eight or nine passes of four tokens) is still faster, 0.31 ms against 0.43 ms per
-// layer; at about 140 tokens the two are level (0.82 ms); at about 560 tokens the tile path wins,
-// 2.49 ms against 2.92 ms.  The environment variable exists for such measurements.
+// measured break-even on a switch-large-128 layer with a skewed router (eight hot experts share half
+// of the tokens): at about 140 tokens per hot expert the per-row kernel (36 passes of four tokens) is
+// still faster, 0.70 ms against 1.06 ms per layer; at about 560 tokens the tile path wins, 2.16 ms
+// against 2.45 ms; at about 2200 tokens, 5.03 ms against 6.99 ms.  The environment variable exists
+// for such measurements.
 static std::atomic<int> g_tile_min{-1};  // -1: not yet initialised from the environment
 static int clamp_tile_min(int t) { return t <= 0 ? 0 : (t < 8 ? 8 : t); }
 static int tile_min_tokens() {
   int v = g_tile_min.load(std::memory_order_relaxed);
   if (v < 0) {
     const char *s = getenv("QMOE_TILE_MIN_TOKENS");
-    v = clamp_tile_min(s ? atoi(s) : 128);
+    v = clamp_tile_min(s ? atoi(s) : 448);
     g_tile_min.store(v, std::memory_order_relaxed);
   }
   return v;
@@ -933,7 +959,8 @@ static int64_t item_capacity(int max_slots, int height) {
 }
 
 static int64_t warp_item_capacity(int max_slots) {
-  return (int64_t)max_slots * (kWarpRemainderMax / kWarpItemRows) + kSmallRows / kWarpItemRows + kExtraItems;
+  (void)max_slots;  // only steps with at most kSmallRows rows use warp items
+  return kSmallRows / kWarpItemRows + kExtraItems;
 }
 
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
