@@ -124,6 +124,7 @@ class ClockSampler:
             out["sm_mhz"] = sm[len(sm) // 2]
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
+        out["window"] = "1.5 s of untimed repeats of the step, then the device-timed and the end-to-end region"
         return out
 
 
@@ -338,9 +339,23 @@ def run_ours(args):
         run()
     barrier()
 
+    # nvidia-smi needs most of a second before its first sample and a step can be under a
+    # millisecond, so the sampler starts here and the step is repeated, untimed, until it has had
+    # 1.5 s under load; the timed regions follow directly.  Every rank runs the same repeats (the
+    # step contains collectives), rank 0 decides when to stop.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    t_load = time.perf_counter()
+    go = torch.ones(1, device=dev)
+    while float(go.item()) > 0:
+        for _ in range(20):
+            run()
+        torch.cuda.synchronize()
+        go.fill_(1.0 if time.perf_counter() - t_load < 1.5 else 0.0)
+        if world > 1:
+            dist.broadcast(go, 0)
+    barrier()
     ms_total = timed(run, args.steps)
 
     def e2e_step():
