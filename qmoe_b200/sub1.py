@@ -138,7 +138,8 @@ class ExpertStore:
     ``descs``: device array of ``qmoe_matrix_desc``."""
 
     def __init__(self, codes: torch.Tensor, row_off: torch.Tensor, minmax: torch.Tensor,
-                 descs: Sequence[MatrixDesc], d_model: int, d_ff: int, interleave: bool = True):
+                 descs: Sequence[MatrixDesc], d_model: int, d_ff: int, interleave: bool = True,
+                 dec: Optional[torch.Tensor] = None):
         assert codes.dtype == torch.int16 and row_off.dtype == torch.int32 and minmax.dtype == torch.bfloat16
         assert len(descs) % 2 == 0
         self.codes, self.row_off, self.minmax = codes, row_off, minmax
@@ -149,6 +150,7 @@ class ExpertStore:
         raw = np.frombuffer(bytes(self._desc_array), dtype=np.uint8).copy()
         self.descs = torch.from_numpy(raw).to(codes.device)
         self.device = codes.device
+        self.dec = dec                                   # decoder table of these streams (None: the standard one)
         self.il_codes: Optional[torch.Tensor] = None     # lane-interleaved copy of the streams
         self.blk_base: Optional[torch.Tensor] = None     # int64, first 16-byte entry of every 32-row block
         if interleave and codes.is_cuda and d_model % 32 == 0 and d_ff % 32 == 0:
@@ -161,7 +163,7 @@ class ExpertStore:
         possible.  One-time cost when a store is created."""
         L = _lib.load()
         dev = self.device
-        dec = DEC(dev)
+        dec = self.dec if self.dec is not None else DEC(dev)
         remap_ptr = None
         if renumber:
             hist = torch.zeros(_lib.DICT_COUNT, dtype=torch.int64, device=dev)
@@ -357,15 +359,16 @@ def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max
     if work is None or work.numel() < nbytes:
         work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     assert xs.is_contiguous() and xs.shape[1] == store.d_model
+    dec = store.dec if store.dec is not None else DEC(dev)
     if store.il_codes is not None:
         _lib.check(L.qmoe_moe_grouped_ffn_interleaved(
-            DEC(dev).data_ptr(), None if store.codes is None else store.codes.data_ptr(),
+            dec.data_ptr(), None if store.codes is None else store.codes.data_ptr(),
             store.row_off.data_ptr(), store.minmax.data_ptr(),
             store.descs.data_ptr(), ctypes.addressof(store.il_struct), offsets.data_ptr(),
             xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(), store.n_experts, max_slots,
             store.d_model, store.d_ff, dev.index, _s(dev)))
         return ys
-    _lib.check(L.qmoe_moe_grouped_ffn(DEC(dev).data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(),
+    _lib.check(L.qmoe_moe_grouped_ffn(dec.data_ptr(), store.codes.data_ptr(), store.row_off.data_ptr(),
                                       store.minmax.data_ptr(), store.descs.data_ptr(), offsets.data_ptr(),
                                       xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(),
                                       store.n_experts, max_slots, store.d_model, store.d_ff, dev.index, _s(dev)))

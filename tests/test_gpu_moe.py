@@ -186,3 +186,62 @@ def test_remap_tables_reject_a_non_permutation(dev):
                                             dec_out.data_ptr(), dev.index, None)
     assert rc == _lib.ERR_INVALID_ARG
     assert b"permutation" in _lib.load().qmoe_last_error()
+
+
+@pytest.mark.parametrize("interleave", [True, False])
+def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
+    """A decoder table with an entry of four non-zeros (not expressible in the sparse form): the
+    grouped kernels must fall back to digit-by-digit decoding of that entry, in the row-by-row and in
+    the interleaved, renumbered layout, for groups of one, two and three tokens."""
+    from oracle import oracle as O
+    from qmoe_b200 import _lib
+    from qmoe_b200.sub1 import ExpertStore
+    dec_np = O.build_dictionary()[0].copy()
+    digits, nweights = O.numpy_entry_digits(dec_np)
+    bad = int(np.where((nweights >= 8) & (nweights <= 28) & ((digits != 0).sum(1) == 3))[0][0])
+    free = int(np.where(digits[bad][:nweights[bad]] == 0)[0][0])
+    word, bit = free // 14, 4 + 2 * (free % 14)
+    dec_np[2 * bad + word] = np.int32(np.uint32(dec_np[2 * bad + word]) | np.uint32(2 << bit))
+    all_zero = np.where((digits != 0).sum(1) == 0)[0]
+    zero_run = {int(nweights[c]): int(c) for c in all_zero[::-1]}     # runs of 2..28 zeros
+    some = [int(c) for c in np.where((nweights == 12) & ((digits != 0).sum(1) == 2))[0][:4]]
+
+    def row(width, r):
+        codes, left = [], width
+        for c in ([bad] if r % 2 == 0 else []) + [some[r % len(some)]]:
+            codes.append(c)
+            left -= int(nweights[c])
+        while left > 0:
+            n = min(left, 28)
+            codes.append(zero_run[n])
+            left -= n
+        assert left == 0
+        return codes[::-1] if r % 3 == 0 else codes
+
+    # wi: 1024 rows one per thread plus 32 one per warp in k_matmul_grouped; wo (64 rows, few in
+    # total): k_matmul_grouped_warp
+    d_model, d_ff, n_exp = 64, 1056, 40
+    parts, dense = [], []
+    for h, w in ((d_ff, d_model), (d_model, d_ff)):
+        rows = [row(w, r) for r in range(h)]
+        codes = np.array([c for rc in rows for c in rc], dtype=np.uint16)
+        row_off = np.concatenate([[0], np.cumsum([len(rc) for rc in rows])]).astype(np.int32)
+        mm = synth.row_scales(h, 3, h)
+        sym = O.numpy_decode_matrix(dec_np, codes, row_off, h, w)
+        deq = np.concatenate([np.zeros((h, 1), np.float32), mm.float().numpy().reshape(-1, 2)], 1)
+        dense.append(torch.from_numpy(np.take_along_axis(deq, sym.astype(np.int64), 1)))
+        parts.append((torch.from_numpy(codes.view(np.int16)).to(dev), torch.from_numpy(row_off).to(dev), mm.to(dev), h, w))
+    dec2 = torch.from_numpy(dec_np).to(dev)
+    base = ExpertStore.from_matrices(parts * n_exp, d_model, d_ff)    # experts with the same two matrices
+    store = ExpertStore(base.codes, base.row_off, base.minmax, base.host_descs, d_model, d_ff,
+                        interleave=interleave, dec=dec2)
+    assert (store.il_codes is not None) == interleave
+    counts = [1 + e % 3 for e in range(n_exp)]
+    n = sum(counts)
+    xs = synth.tokens(n, d_model, seed=9)
+    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+    ys = sub1.grouped_ffn(store, offsets, xs.to(dev), n).cpu()
+    hidden = torch.relu((xs.float() @ dense[0].t()).bfloat16())
+    want = (hidden.float() @ dense[1].t()).bfloat16()
+    assert rel_err(ys, want) <= TOL
+    _lib.check(_lib.load().qmoe_sub1_release(0))
