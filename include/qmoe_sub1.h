@@ -234,6 +234,24 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
                      const void *prob_dev, void *out_dev, int n_tokens, int d_model, int device,
                      void *stream);
 
+/* Fused helpers of the batch-1 decode step of the generation harness (qmoe_b200/decoder.py).  No
+ * counterpart in the reference, which leaves these parts to HuggingFace's Switch Transformers
+ * modules behind model.generate (sub1.py:373-379).
+ *   qmoe_moe_combine_add: out = bf16(residual + qmoe_moe_combine(...)), one launch.
+ *   qmoe_rms_norm: out[r] = bf16(bf16(x[r] * rsqrt(mean(x[r]^2) + eps)) * weight), bf16 [rows, d].
+ *   qmoe_decode_attention: one new token of causal self-attention.  qkv_dev bf16 [3][heads][head_dim]
+ *     of the token; caches bf16 [heads][max_len][head_dim]; *pos_dev (device int64) is the token's
+ *     position: its key and value are written there, then
+ *     out[head] = softmax(q . K[0..pos] / sqrt(head_dim)) V[0..pos] (fp32 arithmetic, bf16 result).
+ *     head_dim <= 256, max_len <= 8192. */
+int qmoe_moe_combine_add(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev,
+                         const void *prob_dev, const void *residual_dev, void *out_dev, int n_tokens,
+                         int d_model, int device, void *stream);
+int qmoe_rms_norm(const void *x_dev, const void *weight_dev, void *out_dev, int rows, int d, float eps,
+                  int device, void *stream);
+int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
+                          void *out_dev, int heads, int head_dim, int max_len, int device, void *stream);
+
 /* Number of kernels this library has launched in the calling process (all devices, all entry points). */
 int64_t qmoe_launch_count(void);
 

@@ -84,6 +84,11 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
                        void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
                        int device, cudaStream_t stream);
+int launch_combine_add(const void *ys, const void *hidden, const int32_t *slot, const void *prob,
+                       const void *residual, void *out, int n_tokens, int d_model, cudaStream_t stream);
+int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, float eps, cudaStream_t stream);
+int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
+                            int heads, int hd, int max_len, cudaStream_t stream);
 int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream);
 int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
                         int *scratch2, cudaStream_t stream);
@@ -570,6 +575,42 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   return launch_combine(ys_dev, hidden_dev, slot_dev, prob_dev, out_dev, n_tokens, d_model, as_stream(stream));
+}
+
+int qmoe_moe_combine_add(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev, const void *prob_dev,
+                         const void *residual_dev, void *out_dev, int n_tokens, int d_model, int device,
+                         void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && d_model >= 1, "bad shape");
+  if (n_tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(hidden_dev && slot_dev && prob_dev && residual_dev && out_dev, "null device pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_combine_add(ys_dev, hidden_dev, slot_dev, prob_dev, residual_dev, out_dev, n_tokens, d_model,
+                            as_stream(stream));
+}
+
+int qmoe_rms_norm(const void *x_dev, const void *weight_dev, void *out_dev, int rows, int d, float eps,
+                  int device, void *stream) {
+  QMOE_REQUIRE(rows >= 0 && d >= 1, "bad shape");
+  if (rows == 0) return QMOE_OK;
+  QMOE_REQUIRE(x_dev && weight_dev && out_dev, "null device pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_rms_norm(x_dev, weight_dev, out_dev, rows, d, eps, as_stream(stream));
+}
+
+int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
+                          void *out_dev, int heads, int head_dim, int max_len, int device, void *stream) {
+  QMOE_REQUIRE(qkv_dev && k_cache_dev && v_cache_dev && pos_dev && out_dev, "null device pointer");
+  QMOE_REQUIRE(heads >= 1 && head_dim >= 1 && max_len >= 1, "bad shape");
+  if (head_dim > 256 || max_len > 8192) {
+    set_error("%s: head_dim <= 256 and max_len <= 8192 are supported", __func__);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_decode_attention(qkv_dev, k_cache_dev, v_cache_dev, pos_dev, out_dev, heads, head_dim, max_len,
+                                 as_stream(stream));
 }
 
 int64_t qmoe_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }

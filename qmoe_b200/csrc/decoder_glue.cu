@@ -1,0 +1,197 @@
+// Small fused kernels for the batch-1 decode step of the generation harness (decoder.py).  The
+// reference leaves these parts to HuggingFace's Switch Transformers modules (called through
+// model.generate at sub1.py:373-379); at one token per step they are pure launch overhead, so each
+// group of element-wise torch kernels becomes one launch here.
+#include "common.cuh"
+
+namespace qmoe {
+
+constexpr int kMaxHeadDim = 256;
+constexpr int kAttentionThreads = 1024;  // 32 warps share the cached positions of a head
+
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();  // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int w = 0; w < nwarps; w++) t += scratch[w];
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float *scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = scratch[0];
+  for (int w = 1; w < nwarps; w++) t = fmaxf(t, scratch[w]);
+  return t;
+}
+
+// out[r] = bf16(bf16(x[r] * rsqrt(mean(x[r]^2) + eps)) * w), one CTA per row: the T5 layer norm
+// (no mean subtraction, no bias) with the roundings of its bf16 torch formulation.
+__global__ void k_rms_norm(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ w,
+                           __nv_bfloat16 *__restrict__ out, int d, float eps) {
+  __shared__ float scratch[32];
+  const __nv_bfloat16 *row = x + (size_t)blockIdx.x * d;
+  float ss = 0.f;
+  if ((d & 1) == 0 && (reinterpret_cast<uintptr_t>(row) & 3u) == 0) {
+    const __nv_bfloat162 *row2 = reinterpret_cast<const __nv_bfloat162 *>(row);
+    for (int i = threadIdx.x; i < d / 2; i += blockDim.x) {
+      const float2 v = __bfloat1622float2(row2[i]);
+      ss += v.x * v.x + v.y * v.y;
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const float v = __bfloat162float(row[i]);
+      ss += v * v;
+    }
+  }
+  const float r = rsqrtf(block_sum(ss, scratch) / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float y = __bfloat162float(__float2bfloat16_rn(__bfloat162float(row[i]) * r));
+    out[(size_t)blockIdx.x * d + i] = __float2bfloat16_rn(y * __bfloat162float(w[i]));
+  }
+}
+
+// One new token of causal self-attention, one CTA per head.  qkv: [3][heads][hd] of the token;
+// caches: [heads][max_len][hd].  Writes the token's key and value at position *pos, then
+// out[head] = softmax(q . K[0..pos] / sqrt(hd)) V[0..pos], fp32 arithmetic, bf16 result.
+template <int J>  // ceil(head_dim / 32): values of a cache row per lane
+__global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __nv_bfloat16 *__restrict__ qkv, __nv_bfloat16 *__restrict__ k_cache,
+                                   __nv_bfloat16 *__restrict__ v_cache, const long long *__restrict__ pos_ptr,
+                                   __nv_bfloat16 *__restrict__ out, int heads, int hd, int max_len) {
+  extern __shared__ float smem[];
+  float *q = smem;            // hd
+  float *score = smem + hd;   // max_len
+  __shared__ float scratch[32];
+  const int head = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  long long pos = *pos_ptr;
+  pos = pos < 0 ? 0 : (pos >= max_len ? max_len - 1 : pos);
+  __nv_bfloat16 *kc = k_cache + (size_t)head * max_len * hd;
+  __nv_bfloat16 *vc = v_cache + (size_t)head * max_len * hd;
+  for (int i = tid; i < hd; i += blockDim.x) {
+    q[i] = __bfloat162float(qkv[(size_t)head * hd + i]);
+    kc[pos * hd + i] = qkv[(size_t)(heads + head) * hd + i];
+    vc[pos * hd + i] = qkv[(size_t)(2 * heads + head) * hd + i];
+  }
+  __syncthreads();
+  const float scale = rsqrtf((float)hd);
+  // Positions are taken eight at a time per warp with every load of the eight issued before the
+  // first use: the loop is bound by the latency of the cache reads, not by their number.
+  constexpr int U = 8;
+  for (int t0 = warp * U; t0 <= pos; t0 += nwarps * U) {
+    float kv[U][J];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+        const int i = lane + 32 * j;
+        kv[u][j] = (t0 + u <= pos && i < hd) ? __bfloat162float(kc[(size_t)(t0 + u) * hd + i]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+        const int i = lane + 32 * j;
+        if (i < hd) s += q[i] * kv[u][j];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (lane == 0 && t0 + u <= pos) score[t0 + u] = s * scale;
+    }
+  }
+  __syncthreads();
+  float m = -3.0e38f;
+  for (int t = tid; t <= pos; t += blockDim.x) m = fmaxf(m, score[t]);
+  m = block_max(m, scratch);
+  float sum = 0.f;
+  for (int t = tid; t <= pos; t += blockDim.x) {
+    const float p = __expf(score[t] - m);
+    score[t] = p;
+    sum += p;
+  }
+  sum = block_sum(sum, scratch);  // its barriers also publish score[]
+  const float inv = 1.f / sum;
+  // out[i] = sum_t p[t] V[t][i]: every warp takes the positions t = warp, warp + nwarps, ... with
+  // its lanes over i, then the warps' partial sums are added through shared memory (partial[]
+  // follows score[]).
+  float *partial = score + max_len;  // [nwarps][hd]
+  float acc[J];
+#pragma unroll
+  for (int j = 0; j < J; j++) acc[j] = 0.f;
+  for (int t0 = warp * U; t0 <= pos; t0 += nwarps * U) {
+    float vv[U][J];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+        const int i = lane + 32 * j;
+        vv[u][j] = (t0 + u <= pos && i < hd) ? __bfloat162float(vc[(size_t)(t0 + u) * hd + i]) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const float p = t0 + u <= pos ? score[t0 + u] : 0.f;
+#pragma unroll
+      for (int j = 0; j < J; j++) acc[j] += p * vv[u][j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxHeadDim / 32; j++) {
+    const int i = lane + 32 * j;
+    if (i < hd) partial[warp * hd + i] = acc[j];
+  }
+  __syncthreads();
+  for (int i = tid; i < hd; i += blockDim.x) {
+    float total = 0.f;
+    for (int w = 0; w < nwarps; w++) total += partial[w * hd + i];
+    out[(size_t)head * hd + i] = __float2bfloat16_rn(total * inv);
+  }
+}
+
+int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, float eps, cudaStream_t stream) {
+  if (rows == 0) return QMOE_OK;
+  QMOE_LAUNCH(k_rms_norm, (unsigned)rows, 512, 0, stream, reinterpret_cast<const __nv_bfloat16 *>(x),
+              reinterpret_cast<const __nv_bfloat16 *>(w), reinterpret_cast<__nv_bfloat16 *>(out), d, eps);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
+                            int heads, int hd, int max_len, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * ((size_t)hd + (size_t)max_len + (size_t)(kAttentionThreads / 32) * hd);
+  static bool limit_set[64][kMaxHeadDim / 32 + 1] = {};  // per device and instantiation
+  int device = 0;
+  QMOE_CUDA(cudaGetDevice(&device));
+  const int chunk_count = (hd + 31) / 32;
+  auto run = [&](auto kernel) -> int {
+    if (device < 64 && !limit_set[device][chunk_count]) {
+      QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+      limit_set[device][chunk_count] = true;
+    } else if (device >= 64) {
+      QMOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    }
+    QMOE_LAUNCH(kernel, (unsigned)heads, kAttentionThreads, smem, stream, reinterpret_cast<const __nv_bfloat16 *>(qkv),
+                reinterpret_cast<__nv_bfloat16 *>(k_cache), reinterpret_cast<__nv_bfloat16 *>(v_cache),
+                reinterpret_cast<const long long *>(pos), reinterpret_cast<__nv_bfloat16 *>(out), heads, hd, max_len);
+    QMOE_CUDA(cudaGetLastError());
+    return QMOE_OK;
+  };
+  switch (chunk_count) {
+    case 1: return run(k_decode_attention<1>);
+    case 2: return run(k_decode_attention<2>);
+    case 3: return run(k_decode_attention<3>);
+    case 4: return run(k_decode_attention<4>);
+    default: return run(k_decode_attention<kMaxHeadDim / 32>);
+  }
+}
+
+}  // namespace qmoe

@@ -49,6 +49,47 @@ __global__ void k_route_choose(const float *__restrict__ logits, int32_t *__rest
   }
 }
 
+// The same with one CTA of 256 threads per token, for the few tokens of a decode step (a single
+// warp walking 2048 logits three times is pure latency).
+__global__ void __launch_bounds__(256) k_route_choose_block(const float *__restrict__ logits,
+                                                            int32_t *__restrict__ choice,
+                                                            __nv_bfloat16 *__restrict__ prob, int n_experts) {
+  __shared__ float s_f[8];
+  __shared__ int s_i[8];
+  const int token = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float *l = logits + (size_t)token * n_experts;
+  float m = -INFINITY;
+  for (int i = tid; i < n_experts; i += 256) m = fmaxf(m, l[i]);
+  m = warp_max(m);
+  if (lane == 0) s_f[warp] = m;
+  __syncthreads();
+  m = s_f[0];
+  for (int w = 1; w < 8; w++) m = fmaxf(m, s_f[w]);
+  __syncthreads();
+  float s = 0.f;
+  for (int i = tid; i < n_experts; i += 256) s += expf(l[i] - m);
+  s = warp_sum(s);
+  if (lane == 0) s_f[warp] = s;
+  __syncthreads();
+  s = 0.f;
+  for (int w = 0; w < 8; w++) s += s_f[w];
+  const __nv_bfloat16 pmax = __float2bfloat16_rn(1.f / s);
+  const unsigned short pmax_bits = __bfloat16_as_ushort(pmax);
+  int first = n_experts;
+  for (int i = tid; i < n_experts; i += 256) {
+    const __nv_bfloat16 p = __float2bfloat16_rn(expf(l[i] - m) / s);
+    if (__bfloat16_as_ushort(p) >= pmax_bits && i < first) first = i;
+  }
+  first = warp_min(first);
+  if (lane == 0) s_i[warp] = first;
+  __syncthreads();
+  if (tid == 0) {
+    for (int w = 1; w < 8; w++) first = min(first, s_i[w]);
+    choice[token] = first < n_experts ? first : 0;
+    prob[token] = pmax;
+  }
+}
+
 // Capacity rule: kept iff fewer than `capacity` earlier tokens of the same sequence chose the same
 // expert (cumsum(one_hot, dim=-2) <= expert_capacity in the router).
 __global__ void k_capacity(const int32_t *__restrict__ choice, int32_t *__restrict__ bucket, int n_tokens,
@@ -182,10 +223,32 @@ __global__ void k_combine(const __nv_bfloat16 *__restrict__ ys, const __nv_bfloa
     dst[i] = __float2bfloat16_rn(p * __bfloat162float(src[i]));
 }
 
+// out[t] = bf16(residual[t] + bf16(prob[t] * (slot >= 0 ? ys[slot] : hidden[t]))): k_combine followed
+// by the block's residual addition in bf16.
+__global__ void k_combine_add(const __nv_bfloat16 *__restrict__ ys, const __nv_bfloat16 *__restrict__ hidden,
+                              const int32_t *__restrict__ slot, const __nv_bfloat16 *__restrict__ prob,
+                              const __nv_bfloat16 *__restrict__ residual, __nv_bfloat16 *__restrict__ out,
+                              int d_model) {
+  const int t = blockIdx.x;
+  const int s = slot[t];
+  const float p = __bfloat162float(prob[t]);
+  const __nv_bfloat16 *src = s >= 0 ? ys + (size_t)s * d_model : hidden + (size_t)t * d_model;
+  for (int i = threadIdx.x; i < d_model; i += blockDim.x) {
+    const float moe = __bfloat162float(__float2bfloat16_rn(p * __bfloat162float(src[i])));
+    out[(size_t)t * d_model + i] = __float2bfloat16_rn(__bfloat162float(residual[(size_t)t * d_model + i]) + moe);
+  }
+}
+
 // ---- launchers ----------------------------------------------------------------------------------
 int launch_route(const float *logits, int32_t *choice, void *prob, int n_tokens, int n_experts,
                  cudaStream_t stream) {
   if (n_tokens == 0) return QMOE_OK;
+  if (n_tokens <= 16 && n_experts >= 512) {
+    QMOE_LAUNCH(k_route_choose_block, (unsigned)n_tokens, 256, 0, stream, logits, choice,
+                reinterpret_cast<__nv_bfloat16 *>(prob), n_experts);
+    QMOE_CUDA(cudaGetLastError());
+    return QMOE_OK;
+  }
   const int threads = 128;
   const long long total = (long long)n_tokens * 32;
   QMOE_LAUNCH(k_route_choose, (unsigned)((total + threads - 1) / threads), threads, 0, stream, logits, choice, reinterpret_cast<__nv_bfloat16 *>(prob), n_tokens, n_experts);
@@ -232,6 +295,15 @@ int launch_unpermute(const void *ys, const int32_t *slot, void *out, int n_token
 int launch_combine(const void *ys, const void *hidden, const int32_t *slot, const void *prob, void *out,
                    int n_tokens, int d_model, cudaStream_t stream) {
   QMOE_LAUNCH(k_combine, n_tokens, 128, 0, stream, reinterpret_cast<const __nv_bfloat16 *>(ys), reinterpret_cast<const __nv_bfloat16 *>(hidden), slot, reinterpret_cast<const __nv_bfloat16 *>(prob), reinterpret_cast<__nv_bfloat16 *>(out), d_model);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_combine_add(const void *ys, const void *hidden, const int32_t *slot, const void *prob,
+                       const void *residual, void *out, int n_tokens, int d_model, cudaStream_t stream) {
+  QMOE_LAUNCH(k_combine_add, n_tokens, 256, 0, stream, reinterpret_cast<const __nv_bfloat16 *>(ys),
+              reinterpret_cast<const __nv_bfloat16 *>(hidden), slot, reinterpret_cast<const __nv_bfloat16 *>(prob),
+              reinterpret_cast<const __nv_bfloat16 *>(residual), reinterpret_cast<__nv_bfloat16 *>(out), d_model);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

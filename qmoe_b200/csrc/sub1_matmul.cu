@@ -791,7 +791,7 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 // 32 rows.  In between, the items are made finer than 1024 rows
 // until there are about two per SM.  Without an interleaved store there is no warp kernel.
 constexpr int kExtraItems = 1024;
-constexpr int kWarpItemRows = 32;
+constexpr int kWarpItemRows = 8;             // one row per warp of a k_matmul_grouped_warp CTA
 constexpr int kWarpRemainderMax = 256;      // most rows of a matrix that are left to the warp kernel
 constexpr int kSmallRows = 148 * 8 * 32;    // fewer rows in total (less than eight warps of rows per SM):
                                             // the warp kernel takes all of them
@@ -886,24 +886,34 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       }
       __syncthreads();
       const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
-      for (int g = 0; g < groups; g++) {
-        const int gi = base + g;
-        // cannot happen for valid offsets
-        if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity ||
-            (long long)(gi + 1) * wchunks > p.warp_capacity)
-          break;
-        const int tok0 = first + g * kMaxGroup;
-        const int ntok = min(kMaxGroup, count - g * kMaxGroup);
-        for (int k = 0; k < chunks; k++) {
-          const int row0 = k * rpc;
-          p.items[(size_t)gi * chunks + k] = make_int4(2 * e + p.which, row0, tok0,
-                                                       min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) |
-                                                           (ntok << 16));
-        }
-        for (int k = 0; k < wchunks; k++) {
-          const int row0 = k * kWarpItemRows;
-          p.warp_items[(size_t)gi * wchunks + k] =
-              make_int4(2 * e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (ntok << 16));
+      // The items of a lane's expert are written by its whole warp (hundreds of 8-row warp items
+      // per group would otherwise be one thread's serial loop).
+      unsigned busy = __ballot_sync(0xffffffffu, groups > 0);
+      while (busy) {
+        const int src = __ffs(busy) - 1;
+        busy &= busy - 1;
+        const int o_e = __shfl_sync(0xffffffffu, e, src), o_first = __shfl_sync(0xffffffffu, first, src);
+        const int o_count = __shfl_sync(0xffffffffu, count, src), o_groups = __shfl_sync(0xffffffffu, groups, src);
+        const int o_base = __shfl_sync(0xffffffffu, base, src);
+        for (int g = 0; g < o_groups; g++) {
+          const int gi = o_base + g;
+          // cannot happen for valid offsets
+          if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity ||
+              (long long)(gi + 1) * wchunks > p.warp_capacity)
+            break;
+          const int tok0 = o_first + g * kMaxGroup;
+          const int ntok = min(kMaxGroup, o_count - g * kMaxGroup);
+          for (int k = lane; k < chunks; k += 32) {
+            const int row0 = k * rpc;
+            p.items[(size_t)gi * chunks + k] =
+                make_int4(2 * o_e + p.which, row0, tok0,
+                          min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) | (ntok << 16));
+          }
+          for (int k = lane; k < wchunks; k += 32) {
+            const int row0 = k * kWarpItemRows;
+            p.warp_items[(size_t)gi * wchunks + k] =
+                make_int4(2 * o_e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (ntok << 16));
+          }
         }
       }
       __syncthreads();
@@ -995,7 +1005,11 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   const bool il = ils != nullptr;
   // The tile path decodes the row-by-row streams; a store that kept only its interleaved copy
   // (codes == nullptr) sends every expert through the per-row kernel.
-  const int tile_min = tab.conforming && codes != nullptr ? tile_min_tokens() : 0;
+  // max_slots bounds the tokens of the step, so launches that cannot get work are left out: the
+  // tile path when no expert can reach its threshold, the per-thread kernel when the step is small
+  // enough for the warp kernel whatever the routing (see k_build_work).
+  int tile_min = tab.conforming && codes != nullptr ? tile_min_tokens() : 0;
+  if (tile_min > max_slots) tile_min = 0;
   QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, 2 * sms, il ? 1 : 0,
               header, ph[0], ph[1]);
   QMOE_CUDA(cudaGetLastError());
@@ -1039,9 +1053,12 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
       if (rc) return rc;
     }
-    const unsigned grid = (unsigned)sms;  // the 160 KB table allows one CTA per SM
+    const unsigned grid = (unsigned)sms;  // the table in shared memory allows one CTA per SM
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
-    if (tab.conforming && il)
+    const int height = phase == 0 ? d_ff : d_model;
+    if (il && (long long)max_slots * height <= kSmallRows) {
+      // every step this small goes to the warp kernel
+    } else if (tab.conforming && il)
       QMOE_LAUNCH((k_matmul_grouped<false, true>), grid, kGroupedThreads, smem, stream, a);
     else if (tab.conforming)
       QMOE_LAUNCH((k_matmul_grouped<false, false>), grid, kGroupedThreads, smem, stream, a);

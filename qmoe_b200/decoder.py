@@ -37,9 +37,19 @@ class ReplicatedTokenMoE:
         self.capacity = expert_capacity
         self.router = sub1.RouterClassifier(router_weight, store.device)
 
-    def __call__(self, hidden: torch.Tensor) -> torch.Tensor:
+    def __call__(self, hidden: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """MoE output for ``hidden``; with ``residual`` (single-rank only) ``residual + output``."""
         n, d = hidden.shape
         choice, prob = sub1.route_top1(self.router(hidden).contiguous())
+        if self.world == 1:
+            # all experts are local: the single-GPU layer (route, rank, permute, FFN, combine)
+            bucket, rank, _, offsets = sub1.rank_buckets(choice, self.n_experts, n, self.capacity)
+            xs = torch.empty_like(hidden)
+            slot = sub1.permute_rows(bucket, rank, offsets, hidden, xs)
+            ys = sub1.grouped_ffn(self.store, offsets, xs, n)
+            if residual is not None:
+                return sub1.combine_add(ys, hidden, slot, prob, residual)
+            return sub1.combine(ys, hidden, slot, prob)
         expert, _, _, _ = sub1.rank_buckets(choice, self.n_experts, n, self.capacity)
         lo = self.rank * self.local
         mine = (expert >= lo) & (expert < lo + self.local)
@@ -48,15 +58,13 @@ class ReplicatedTokenMoE:
         xs = torch.empty_like(hidden)
         slot = sub1.permute_rows(bucket, rank, offsets, hidden, xs)
         ys = sub1.grouped_ffn(self.store, offsets, xs, n)
-        if self.world == 1:
-            kept_slot = torch.where(expert >= 0, slot, torch.full_like(slot, -1))
-            return sub1.combine(ys, hidden, kept_slot, prob)
         part = torch.empty_like(hidden)
         sub1.unpermute_rows(ys, slot, part)                      # zeros for tokens of other ranks
         dist.all_reduce(part, group=self.group)
         # tokens dropped by the capacity rule pass through (sub1.py:312,318)
         ident = torch.arange(n, dtype=torch.int32, device=hidden.device)
-        return sub1.combine(part, hidden, torch.where(expert >= 0, ident, torch.full_like(ident, -1)), prob)
+        out = sub1.combine(part, hidden, torch.where(expert >= 0, ident, torch.full_like(ident, -1)), prob)
+        return out if residual is None else residual + out
 
 
 def _rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -99,6 +107,7 @@ class SwitchDecoderLM:
             torch.cuda.empty_cache()                # hand the freed streams back before graphs are captured
         self._graph = None
         self._step_ids = self._step_pos = None
+        self.fused_decode = True                    # single-token steps take _forward_one
         self.k_cache = torch.zeros(n_layers, self.h, max_len, self.hd, dtype=torch.bfloat16, device=self.dev)
         self.v_cache = torch.zeros_like(self.k_cache)
 
@@ -112,6 +121,8 @@ class SwitchDecoderLM:
         is built from ``pos`` on the device, so the same code serves prefill, eager decoding and
         CUDA-graph replay of a decode step."""
         n = ids.shape[0]
+        if n == 1 and self.fused_decode:
+            return self._forward_one(ids, pos)
         x = self.embed[ids]
         all_pos = torch.arange(self.max_len, device=self.dev)
         mask = all_pos[None, :] <= pos[:, None]                                    # [n, max_len]
@@ -126,6 +137,18 @@ class SwitchDecoderLM:
             x = x + att[0].transpose(0, 1).reshape(n, -1) @ b["wo"].t()
             x = x + b["moe"](_rms_norm(x, b["ln2"]).contiguous())
         return (_rms_norm(x, self.final_norm) @ self.lm_head.t()).float()
+
+    def _forward_one(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """The same block arithmetic for a single token with one launch per group of element-wise
+        operations: fused RMS norm, one attention kernel that also stores the token's key and value,
+        and the MoE combine with the residual addition folded in."""
+        x = self.embed[ids]
+        for i, b in enumerate(self.blocks):
+            qkv = sub1.rms_norm(x, b["ln1"]) @ b["wqkv"].t()
+            att = sub1.decode_attention(qkv, self.k_cache[i], self.v_cache[i], pos)
+            x = torch.addmm(x, att, b["wo"].t())
+            x = b["moe"](sub1.rms_norm(x, b["ln2"]), residual=x)
+        return (sub1.rms_norm(x, self.final_norm) @ self.lm_head.t()).float()
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True) -> torch.Tensor:

@@ -386,6 +386,40 @@ def combine(ys: torch.Tensor, hidden: torch.Tensor, slot: torch.Tensor, prob: to
     return out
 
 
+def combine_add(ys: torch.Tensor, hidden: torch.Tensor, slot: torch.Tensor, prob: torch.Tensor,
+                residual: torch.Tensor) -> torch.Tensor:
+    """``residual + combine(ys, hidden, slot, prob)`` in one launch (bf16 addition)."""
+    n, d = hidden.shape
+    dev = hidden.device
+    out = torch.empty_like(hidden)
+    assert hidden.is_contiguous() and residual.is_contiguous() and (ys.numel() == 0 or ys.is_contiguous())
+    _lib.check(_lib.load().qmoe_moe_combine_add(ys.data_ptr(), hidden.data_ptr(), slot.data_ptr(), prob.data_ptr(),
+                                                residual.data_ptr(), out.data_ptr(), n, d, dev.index, _s(dev)))
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """T5-style RMS norm of bf16 rows in one launch."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and weight.dtype == torch.bfloat16
+    out = torch.empty_like(x)
+    d = x.shape[-1]
+    _lib.check(_lib.load().qmoe_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.numel() // d, d,
+                                         float(eps), x.device.index, _s(x.device)))
+    return out
+
+
+def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    """Causal self-attention of one new token (``qkv`` bf16 [3, heads, head_dim]) against caches
+    bf16 [heads, max_len, head_dim]; the token's key / value are stored at ``pos`` (device int64[1])."""
+    heads, max_len, hd = k_cache.shape
+    assert qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and pos.dtype == torch.int64
+    out = torch.empty((1, heads * hd), dtype=torch.bfloat16, device=qkv.device)
+    _lib.check(_lib.load().qmoe_decode_attention(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                 pos.data_ptr(), out.data_ptr(), heads, hd, max_len,
+                                                 qkv.device.index, _s(qkv.device)))
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 # FasterMLP (sub1.py:299-321): the single-GPU top-1 MoE layer
 # ---------------------------------------------------------------------------------------------

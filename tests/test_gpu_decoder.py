@@ -54,6 +54,15 @@ def test_decoder_blocks_match_dense_reference_and_graph_decoding():
     ref = _reference_forward(model, ids)
     err = float((logits - ref).abs().max() / ref.abs().max())
     assert err <= 2e-2, err                                  # two blocks of bf16 arithmetic
+    # single-token step through the fused kernels (RMS norm, attention with cache update, combine +
+    # residual) against the batched path: token 11 after a prefill of tokens 0..10
+    model.forward(ids[:11], torch.arange(11, device=dev))
+    one = model.forward(ids[11:12], torch.full((1,), 11, dtype=torch.int64, device=dev))
+    assert float((one[0] - logits[11]).abs().max() / logits[11].abs().max()) <= 2e-2
+    model.fused_decode = False
+    unfused = model.forward(ids[11:12], torch.full((1,), 11, dtype=torch.int64, device=dev))
+    model.fused_decode = True
+    assert float((one - unfused).abs().max() / unfused.abs().max()) <= 2e-2
     eager = model.generate(ids, 10, use_graph=False)
     graphed = model.generate(ids, 10, use_graph=True)
     assert model.last_generate_used_graph
@@ -64,3 +73,35 @@ def test_decoder_blocks_match_dense_reference_and_graph_decoding():
         b["moe"].store.drop_reference_layout()
     assert torch.equal(model.forward(ids, torch.arange(12, device=dev)), logits)
     assert torch.equal(model.generate(ids, 10, use_graph=True), eager)
+
+
+def test_fused_rms_norm_matches_torch_formulation():
+    from qmoe_b200 import sub1
+    from qmoe_b200.decoder import _rms_norm
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(5)
+    for rows, d in ((1, 2080), (3, 130), (2, 7)):
+        x = (torch.randn(rows, d, generator=g) * 3).bfloat16().to(dev)
+        w = (1 + 0.1 * torch.randn(d, generator=g)).bfloat16().to(dev)
+        got, want = sub1.rms_norm(x, w), _rms_norm(x, w)
+        assert float((got.float() - want.float()).abs().max()) <= 2 ** -6 * float(want.float().abs().max())
+
+
+def test_decode_attention_matches_masked_sdpa():
+    import torch.nn.functional as F
+    from qmoe_b200 import sub1
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(6)
+    heads, hd, max_len = 4, 65, 48
+    k_cache = torch.randn(heads, max_len, hd, generator=g).bfloat16().to(dev)
+    v_cache = torch.randn(heads, max_len, hd, generator=g).bfloat16().to(dev)
+    for p in (0, 1, 17, max_len - 1):
+        qkv = torch.randn(3, heads, hd, generator=g).bfloat16().to(dev)
+        k_ref, v_ref = k_cache.clone(), v_cache.clone()
+        k_ref[:, p], v_ref[:, p] = qkv[1], qkv[2]
+        pos = torch.full((1,), p, dtype=torch.int64, device=dev)
+        got = sub1.decode_attention(qkv.contiguous(), k_cache, v_cache, pos).reshape(heads, hd)
+        assert torch.equal(k_cache, k_ref) and torch.equal(v_cache, v_ref)          # cache updated in place
+        want = F.scaled_dot_product_attention(qkv[0].float().unsqueeze(1), k_ref[:, :p + 1].float(),
+                                              v_ref[:, :p + 1].float())[:, 0]
+        assert float((got.float() - want).abs().max()) <= 2e-2 * max(float(want.abs().max()), 1e-3)
