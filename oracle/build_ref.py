@@ -1,6 +1,6 @@
 """Builds the REFERENCE's own CUDA extension, unmodified, as a GPU-side oracle / baseline.
 
-    python oracle/build_ref.py            # needs the reference checkout (default /root/reference)
+    [QMOE_REFERENCE=/path/to/reference] python oracle/build_ref.py     # needs the reference checkout
 
 The two source files are compiled where they lie (``sub1_cuda.cpp`` and ``sub1_cuda_kernel.cu`` of
 IST-DASLab/qmoe); nothing is copied and nothing is written outside ``oracle/_ref/``.  The recipe is

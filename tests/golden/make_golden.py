@@ -1,6 +1,6 @@
 """Generates tests/golden/sub1_golden.npz by running the REFERENCE's own Python.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where the reference checkout is available:
 
     [QMOE_REFERENCE=/path/to/reference] python tests/golden/make_golden.py
 
