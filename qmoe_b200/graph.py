@@ -47,3 +47,55 @@ class GraphedStep:
         self.static_in.copy_(x, non_blocking=True)
         self.graph.replay()
         return self.static_out
+
+
+class PipelinedStep:
+    """Host-to-host pipeline around a :class:`GraphedStep`: the host-to-device copy of the next
+    input and the device-to-host copy of the previous result run on their own streams while the
+    graph of the current step executes, with two device buffers on either side.
+
+    ``submit(host_in, host_out)`` enqueues one step and returns at once; ``host_out`` (pinned) is
+    complete after ``drain()`` followed by a synchronisation of the current stream, or after the
+    event ``submit`` returns.  Results are those of ``gstep(host_in)`` in submission order."""
+
+    def __init__(self, gstep: GraphedStep):
+        self.g = gstep
+        dev = gstep.static_in.device
+        self.dev = dev
+        self.s_in = torch.cuda.Stream(device=dev)
+        self.s_out = torch.cuda.Stream(device=dev)
+        self.bufs_in = [torch.empty_like(gstep.static_in) for _ in range(2)]
+        self.bufs_out = [torch.empty_like(gstep.static_out) for _ in range(2)]
+        self.ev_in_ready = [torch.cuda.Event() for _ in range(2)]
+        self.ev_done = [torch.cuda.Event() for _ in range(2)]
+        self.ev_out_free = [torch.cuda.Event() for _ in range(2)]
+        self.count = 0
+
+    def submit(self, host_in: torch.Tensor, host_out: torch.Tensor) -> torch.cuda.Event:
+        b = self.count % 2
+        again = self.count >= 2                       # buffer b was used two steps ago
+        cur = torch.cuda.current_stream(self.dev)
+        with torch.cuda.stream(self.s_in):
+            if again:
+                self.s_in.wait_event(self.ev_done[b])     # that step's compute has read bufs_in[b]
+            self.bufs_in[b].copy_(host_in, non_blocking=True)
+            self.ev_in_ready[b].record(self.s_in)
+        cur.wait_event(self.ev_in_ready[b])
+        if again:
+            cur.wait_event(self.ev_out_free[b])           # its result has left bufs_out[b]
+        self.g.static_in.copy_(self.bufs_in[b], non_blocking=True)
+        self.g.graph.replay()
+        self.bufs_out[b].copy_(self.g.static_out, non_blocking=True)
+        self.ev_done[b].record(cur)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_done[b])
+            host_out.copy_(self.bufs_out[b], non_blocking=True)
+            self.ev_out_free[b].record(self.s_out)
+        self.count += 1
+        return self.ev_out_free[b]
+
+    def drain(self) -> None:
+        """Make the current stream wait for every result copy submitted so far."""
+        cur = torch.cuda.current_stream(self.dev)
+        for b in range(min(self.count, 2)):
+            cur.wait_event(self.ev_out_free[b])
