@@ -63,6 +63,33 @@ def test_argument_validation_without_gpu():
         _lib.check(lib.qmoe_sub1_pack_prepare(None, None, None, 1, 2, 0, None))
 
 
+def test_interleaved_store_arguments_are_validated_without_gpu():
+    lib = _lib.load()
+    fake = ctypes.c_void_p(256)
+    # heights must be multiples of 32 and rows consecutive: checked on the host copy of the descriptors
+    descs = (_lib.MatrixDesc * 2)(_lib.MatrixDesc(0, 10, 0, 0, 64, 32), _lib.MatrixDesc(16, 10, 65, 64, 33, 64))
+    rc = lib.qmoe_moe_interleave_count(fake, fake, ctypes.addressof(descs), 2, fake, 0, None)
+    assert rc == _lib.ERR_UNSUPPORTED and b"multiples of 32" in lib.qmoe_last_error()
+    descs = (_lib.MatrixDesc * 2)(_lib.MatrixDesc(0, 10, 0, 0, 64, 32), _lib.MatrixDesc(16, 10, 65, 96, 32, 64))
+    assert lib.qmoe_moe_interleave_count(fake, fake, ctypes.addressof(descs), 2, fake, 0, None) == _lib.ERR_UNSUPPORTED
+    assert lib.qmoe_moe_interleave_count(None, fake, ctypes.addressof(descs), 2, fake, 0, None) == _lib.ERR_INVALID_ARG
+    assert lib.qmoe_moe_interleave_emit(fake, fake, fake, 2, fake, None, ctypes.c_void_p(8), 0, None) \
+        == _lib.ERR_INVALID_ARG                                   # copy not 16-byte aligned
+    # grouped FFN over an interleaved store: null store, null member, widths that are not multiples of 32
+    args = (fake, None, fake, fake, fake)
+    tail = (fake, fake, fake, fake, fake, 4, 8)
+    assert lib.qmoe_moe_grouped_ffn_interleaved(*args, None, *tail, 64, 96, 0, None) == _lib.ERR_INVALID_ARG
+    store = _lib.InterleavedStore(256, 256, 256, None)
+    assert lib.qmoe_moe_grouped_ffn_interleaved(*args, ctypes.addressof(store), *tail, 64, 96, 0, None) \
+        == _lib.ERR_INVALID_ARG
+    store = _lib.InterleavedStore(256, 256, 256, 256)
+    assert lib.qmoe_moe_grouped_ffn_interleaved(*args, ctypes.addressof(store), *tail, 64, 100, 0, None) \
+        == _lib.ERR_UNSUPPORTED
+    assert lib.qmoe_decode_attention(fake, fake, fake, fake, fake, 4, 512, 64, 0, None) == _lib.ERR_UNSUPPORTED
+    assert lib.qmoe_rms_norm(None, fake, fake, 1, 8, 1e-6, 0, None) == _lib.ERR_INVALID_ARG
+    assert lib.qmoe_sub1_remap_tables(None, None, fake, fake, 0, None) == _lib.ERR_INVALID_ARG
+
+
 def test_cpu_tensors_are_rejected():
     import torch
     from qmoe_b200 import sub1_cuda
