@@ -238,6 +238,9 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
  * counterpart in the reference, which leaves these parts to HuggingFace's Switch Transformers
  * modules behind model.generate (sub1.py:373-379).
  *   qmoe_moe_combine_add: out = bf16(residual + qmoe_moe_combine(...)), one launch.
+ *   qmoe_moe_route_small: qmoe_moe_route + _rank + _scan + _permute for at most 32 tokens of one
+ *     sequence in one launch: prob bf16[n], offsets int32[n_experts + 1], slot int32[n] (-1 =
+ *     dropped by the capacity rule), xs[slot] = hidden[token].
  *   qmoe_rms_norm: out[r] = bf16(bf16(x[r] * rsqrt(mean(x[r]^2) + eps)) * weight), bf16 [rows, d].
  *   qmoe_decode_attention: one new token of causal self-attention.  qkv_dev bf16 [3][heads][head_dim]
  *     of the token; caches bf16 [heads][max_len][head_dim]; *pos_dev (device int64) is the token's
@@ -247,6 +250,9 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
 int qmoe_moe_combine_add(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev,
                          const void *prob_dev, const void *residual_dev, void *out_dev, int n_tokens,
                          int d_model, int device, void *stream);
+int qmoe_moe_route_small(const float *logits_dev, const void *hidden_dev, int n_tokens, int n_experts,
+                         int d_model, int capacity, void *prob_dev, int32_t *offsets_dev, int32_t *slot_dev,
+                         void *xs_dev, int device, void *stream);
 int qmoe_rms_norm(const void *x_dev, const void *weight_dev, void *out_dev, int rows, int d, float eps,
                   int device, void *stream);
 int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,

@@ -86,6 +86,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                        int device, cudaStream_t stream);
 int launch_combine_add(const void *ys, const void *hidden, const int32_t *slot, const void *prob,
                        const void *residual, void *out, int n_tokens, int d_model, cudaStream_t stream);
+int launch_route_small(const float *logits, const void *hidden, int n_tokens, int n_experts, int d_model,
+                       int capacity, void *prob, int32_t *offsets, int32_t *slot, void *xs, cudaStream_t stream);
 int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, float eps, cudaStream_t stream);
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
                             int heads, int hd, int max_len, cudaStream_t stream);
@@ -587,6 +589,21 @@ int qmoe_moe_combine_add(const void *ys_dev, const void *hidden_dev, const int32
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   return launch_combine_add(ys_dev, hidden_dev, slot_dev, prob_dev, residual_dev, out_dev, n_tokens, d_model,
                             as_stream(stream));
+}
+
+int qmoe_moe_route_small(const float *logits_dev, const void *hidden_dev, int n_tokens, int n_experts, int d_model,
+                         int capacity, void *prob_dev, int32_t *offsets_dev, int32_t *slot_dev, void *xs_dev,
+                         int device, void *stream) {
+  QMOE_REQUIRE(logits_dev && hidden_dev && prob_dev && offsets_dev && slot_dev && xs_dev, "null device pointer");
+  QMOE_REQUIRE(n_tokens >= 1 && n_experts >= 1 && d_model >= 1 && capacity >= 0, "bad shape");
+  if (n_tokens > 32) {
+    set_error("%s: at most 32 tokens (use qmoe_moe_route / _rank / _scan / _permute)", __func__);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_route_small(logits_dev, hidden_dev, n_tokens, n_experts, d_model, capacity, prob_dev, offsets_dev,
+                            slot_dev, xs_dev, as_stream(stream));
 }
 
 int qmoe_rms_norm(const void *x_dev, const void *weight_dev, void *out_dev, int rows, int d, float eps,

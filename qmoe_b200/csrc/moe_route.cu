@@ -49,18 +49,15 @@ __global__ void k_route_choose(const float *__restrict__ logits, int32_t *__rest
   }
 }
 
-// The same with one CTA of 256 threads per token, for the few tokens of a decode step (a single
-// warp walking 2048 logits three times is pure latency).
-__global__ void __launch_bounds__(256) k_route_choose_block(const float *__restrict__ logits,
-                                                            int32_t *__restrict__ choice,
-                                                            __nv_bfloat16 *__restrict__ prob, int n_experts) {
-  __shared__ float s_f[8];
-  __shared__ int s_i[8];
-  const int token = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const float *l = logits + (size_t)token * n_experts;
+// The same by a whole CTA of 256 threads, for the few tokens of a decode step (a single warp
+// walking 2048 logits three times is pure latency).  Every thread returns the result.
+__device__ __forceinline__ void route_token_block(const float *__restrict__ l, int n_experts, float *s_f, int *s_i,
+                                                  int &first_out, __nv_bfloat16 &pmax_out) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float m = -INFINITY;
   for (int i = tid; i < n_experts; i += 256) m = fmaxf(m, l[i]);
   m = warp_max(m);
+  __syncthreads();  // s_f / s_i may still be read from the previous token
   if (lane == 0) s_f[warp] = m;
   __syncthreads();
   m = s_f[0];
@@ -83,10 +80,92 @@ __global__ void __launch_bounds__(256) k_route_choose_block(const float *__restr
   first = warp_min(first);
   if (lane == 0) s_i[warp] = first;
   __syncthreads();
-  if (tid == 0) {
-    for (int w = 1; w < 8; w++) first = min(first, s_i[w]);
-    choice[token] = first < n_experts ? first : 0;
-    prob[token] = pmax;
+  first = s_i[0];
+  for (int w = 1; w < 8; w++) first = min(first, s_i[w]);
+  first_out = first < n_experts ? first : 0;
+  pmax_out = pmax;
+}
+
+__global__ void __launch_bounds__(256) k_route_choose_block(const float *__restrict__ logits,
+                                                            int32_t *__restrict__ choice,
+                                                            __nv_bfloat16 *__restrict__ prob, int n_experts) {
+  __shared__ float s_f[8];
+  __shared__ int s_i[8];
+  int first;
+  __nv_bfloat16 pmax;
+  route_token_block(logits + (size_t)blockIdx.x * n_experts, n_experts, s_f, s_i, first, pmax);
+  if (threadIdx.x == 0) {
+    choice[blockIdx.x] = first;
+    prob[blockIdx.x] = pmax;
+  }
+}
+
+// Route, capacity rule, stable ranks, bucket offsets and the permutation of the rows, for at most
+// 32 tokens of one sequence, in one launch of one CTA: what k_route_choose, k_capacity, k_rank,
+// k_exclusive_scan and k_permute do for a full layer, for the single-token steps of generation.
+constexpr int kSmallTokens = 32;
+__global__ void __launch_bounds__(256) k_route_small(const float *__restrict__ logits,
+                                                     const __nv_bfloat16 *__restrict__ hidden, int n_tokens,
+                                                     int n_experts, int d_model, int capacity,
+                                                     __nv_bfloat16 *__restrict__ prob, int32_t *__restrict__ offsets,
+                                                     int32_t *__restrict__ slot, __nv_bfloat16 *__restrict__ xs) {
+  __shared__ float s_f[8];
+  __shared__ int s_i[8];
+  __shared__ int s_choice[kSmallTokens], s_rank[kSmallTokens], s_slot[kSmallTokens];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int t = 0; t < n_tokens; t++) {
+    int first;
+    __nv_bfloat16 pmax;
+    route_token_block(logits + (size_t)t * n_experts, n_experts, s_f, s_i, first, pmax);
+    if (tid == 0) {
+      s_choice[t] = first;
+      prob[t] = pmax;
+    }
+  }
+  __syncthreads();
+  if (tid < n_tokens) {
+    int before = 0;
+    for (int u = 0; u < tid; u++) before += (s_choice[u] == s_choice[tid]);
+    s_rank[tid] = before < capacity ? before : -1;  // -1: dropped by the capacity rule
+  }
+  if (tid == 0) s_carry = 0;
+  __syncthreads();
+  // offsets = exclusive prefix sum over the experts of their kept tokens
+  for (int e0 = 0; e0 < n_experts; e0 += 256) {
+    const int e = e0 + tid;
+    int count = 0;
+    if (e < n_experts)
+      for (int t = 0; t < n_tokens; t++) count += (s_choice[t] == e && s_rank[t] >= 0);
+    int incl = count;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
+    }
+    if (lane == 31) s_i[warp] = incl;
+    __syncthreads();
+    int base = s_carry;
+    for (int w = 0; w < warp; w++) base += s_i[w];
+    if (e < n_experts) offsets[e] = base + incl - count;
+    if (e < n_experts && count > 0) {
+      for (int t = 0; t < n_tokens; t++)
+        if (s_choice[t] == e && s_rank[t] >= 0) s_slot[t] = base + incl - count + s_rank[t];
+    }
+    __syncthreads();
+    if (tid == 255) s_carry = base + incl;
+    __syncthreads();
+  }
+  if (tid == 0) offsets[n_experts] = s_carry;
+  if (tid < n_tokens) {
+    if (s_rank[tid] < 0) s_slot[tid] = -1;
+    slot[tid] = s_slot[tid];
+  }
+  __syncthreads();
+  for (int t = 0; t < n_tokens; t++) {
+    const int sl = s_slot[t];
+    if (sl < 0) continue;
+    for (int i = tid; i < d_model; i += 256) xs[(size_t)sl * d_model + i] = hidden[(size_t)t * d_model + i];
   }
 }
 
@@ -295,6 +374,15 @@ int launch_unpermute(const void *ys, const int32_t *slot, void *out, int n_token
 int launch_combine(const void *ys, const void *hidden, const int32_t *slot, const void *prob, void *out,
                    int n_tokens, int d_model, cudaStream_t stream) {
   QMOE_LAUNCH(k_combine, n_tokens, 128, 0, stream, reinterpret_cast<const __nv_bfloat16 *>(ys), reinterpret_cast<const __nv_bfloat16 *>(hidden), slot, reinterpret_cast<const __nv_bfloat16 *>(prob), reinterpret_cast<__nv_bfloat16 *>(out), d_model);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_route_small(const float *logits, const void *hidden, int n_tokens, int n_experts, int d_model,
+                       int capacity, void *prob, int32_t *offsets, int32_t *slot, void *xs, cudaStream_t stream) {
+  QMOE_LAUNCH(k_route_small, 1, 256, 0, stream, logits, reinterpret_cast<const __nv_bfloat16 *>(hidden), n_tokens,
+              n_experts, d_model, capacity, reinterpret_cast<__nv_bfloat16 *>(prob), offsets, slot,
+              reinterpret_cast<__nv_bfloat16 *>(xs));
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

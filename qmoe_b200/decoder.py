@@ -40,6 +40,14 @@ class ReplicatedTokenMoE:
     def __call__(self, hidden: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """MoE output for ``hidden``; with ``residual`` (single-rank only) ``residual + output``."""
         n, d = hidden.shape
+        if self.world == 1 and n <= 32:
+            # a decode step: routing, ranking and permutation in one launch
+            prob, offsets, slot, xs = sub1.route_small(self.router(hidden).contiguous(), hidden, self.n_experts,
+                                                       self.capacity)
+            ys = sub1.grouped_ffn(self.store, offsets, xs, n)
+            if residual is not None:
+                return sub1.combine_add(ys, hidden, slot, prob, residual)
+            return sub1.combine(ys, hidden, slot, prob)
         choice, prob = sub1.route_top1(self.router(hidden).contiguous())
         if self.world == 1:
             # all experts are local: the single-GPU layer (route, rank, permute, FFN, combine)

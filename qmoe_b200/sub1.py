@@ -386,6 +386,22 @@ def combine(ys: torch.Tensor, hidden: torch.Tensor, slot: torch.Tensor, prob: to
     return out
 
 
+def route_small(logits: torch.Tensor, hidden: torch.Tensor, n_experts: int, capacity: int):
+    """Routing, capacity rule, ranks, bucket offsets and the row permutation for at most 32 tokens
+    of one sequence in one launch; returns (prob bf16[n], offsets int32[E + 1], slot int32[n], xs)."""
+    n, d = hidden.shape
+    dev = hidden.device
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and hidden.is_contiguous() and n <= 32
+    prob = torch.empty(n, dtype=torch.bfloat16, device=dev)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    slot = torch.empty(n, dtype=torch.int32, device=dev)
+    xs = torch.empty_like(hidden)
+    _lib.check(_lib.load().qmoe_moe_route_small(logits.data_ptr(), hidden.data_ptr(), n, n_experts, d,
+                                                int(capacity), prob.data_ptr(), offsets.data_ptr(), slot.data_ptr(),
+                                                xs.data_ptr(), dev.index, _s(dev)))
+    return prob, offsets, slot, xs
+
+
 def combine_add(ys: torch.Tensor, hidden: torch.Tensor, slot: torch.Tensor, prob: torch.Tensor,
                 residual: torch.Tensor) -> torch.Tensor:
     """``residual + combine(ys, hidden, slot, prob)`` in one launch (bf16 addition)."""

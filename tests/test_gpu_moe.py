@@ -245,3 +245,25 @@ def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
     want = (hidden.float() @ dense[1].t()).bfloat16()
     assert rel_err(ys, want) <= TOL
     _lib.check(_lib.load().qmoe_sub1_release(0))
+
+
+@pytest.mark.parametrize("n,capacity", [(1, 1024), (5, 1024), (32, 1024), (32, 2), (7, 0)])
+def test_one_launch_routing_of_few_tokens_equals_the_general_kernels(dev, n, capacity):
+    n_exp, d = 300, 96                                    # not a multiple of the CTA size
+    g = torch.Generator().manual_seed(n * 31 + capacity)
+    logits = torch.randn(n, n_exp, generator=g)
+    hot = torch.randint(0, 6, (n,), generator=g)          # few experts: collisions, capacity drops
+    logits[torch.arange(n), hot] += 8.0
+    logits = logits.to(dev).contiguous()
+    hidden = torch.randn(n, d, generator=g).bfloat16().to(dev)
+    choice, prob = sub1.route_top1(logits)
+    bucket, rank, _, offsets = sub1.rank_buckets(choice, n_exp, n, capacity)
+    xs = torch.zeros_like(hidden)
+    slot = sub1.permute_rows(bucket, rank, offsets, hidden, xs)
+    prob2, offsets2, slot2, xs2 = sub1.route_small(logits, hidden, n_exp, capacity)
+    assert torch.equal(choice.cpu(), hot.to(torch.int32))
+    assert torch.equal(offsets2, offsets) and torch.equal(slot2, slot)
+    assert (prob2.float() - prob.float()).abs().max() <= 2 ** -7 * prob.float().max()
+    kept = int(offsets[-1])
+    assert torch.equal(xs2[:kept], xs[:kept])
+    assert kept == int((slot >= 0).sum())
