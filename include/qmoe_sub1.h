@@ -242,6 +242,10 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
  *     sequence in one launch: prob bf16[n], offsets int32[n_experts + 1], slot int32[n] (-1 =
  *     dropped by the capacity rule), xs[slot] = hidden[token].
  *   qmoe_rms_norm: out[r] = bf16(bf16(x[r] * rsqrt(mean(x[r]^2) + eps)) * weight), bf16 [rows, d].
+ *   qmoe_gemv: y = W x for one token, W bf16 [n][k] row-major (k a multiple of 8, k <= 8192,
+ *     16-byte aligned), fp32 accumulation.  ln_weight_dev != NULL: x is first RMS-normalised as in
+ *     qmoe_rms_norm (and stored to normed_out_dev if that is not NULL).  residual_dev != NULL:
+ *     y = bf16(residual + bf16(W x)).  f32_out: y is fp32[n], else bf16[n].
  *   qmoe_decode_attention: one new token of causal self-attention.  qkv_dev bf16 [3][heads][head_dim]
  *     of the token; caches bf16 [heads][max_len][head_dim]; *pos_dev (device int64) is the token's
  *     position: its key and value are written there, then
@@ -255,6 +259,8 @@ int qmoe_moe_route_small(const float *logits_dev, const void *hidden_dev, int n_
                          void *xs_dev, int device, void *stream);
 int qmoe_rms_norm(const void *x_dev, const void *weight_dev, void *out_dev, int rows, int d, float eps,
                   int device, void *stream);
+int qmoe_gemv(const void *x_dev, const void *ln_weight_dev, const void *w_dev, const void *residual_dev,
+              void *y_dev, void *normed_out_dev, int n, int k, float eps, int f32_out, int device, void *stream);
 int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
                           void *out_dev, int heads, int head_dim, int max_len, int device, void *stream);
 

@@ -88,6 +88,8 @@ int launch_combine_add(const void *ys, const void *hidden, const int32_t *slot, 
                        const void *residual, void *out, int n_tokens, int d_model, cudaStream_t stream);
 int launch_route_small(const float *logits, const void *hidden, int n_tokens, int n_experts, int d_model,
                        int capacity, void *prob, int32_t *offsets, int32_t *slot, void *xs, cudaStream_t stream);
+int launch_gemv(const void *x, const void *ln_w, const void *w, const void *residual, void *y, void *normed_out,
+                int n, int k, float eps, int f32_out, cudaStream_t stream);
 int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, float eps, cudaStream_t stream);
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
                             int heads, int hd, int max_len, cudaStream_t stream);
@@ -614,6 +616,23 @@ int qmoe_rms_norm(const void *x_dev, const void *weight_dev, void *out_dev, int 
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   return launch_rms_norm(x_dev, weight_dev, out_dev, rows, d, eps, as_stream(stream));
+}
+
+int qmoe_gemv(const void *x_dev, const void *ln_weight_dev, const void *w_dev, const void *residual_dev, void *y_dev,
+              void *normed_out_dev, int n, int k, float eps, int f32_out, int device, void *stream) {
+  QMOE_REQUIRE(x_dev && w_dev && y_dev, "null device pointer");
+  QMOE_REQUIRE(n >= 1 && k >= 8 && k % 8 == 0, "bad shape (k must be a multiple of 8)");
+  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(w_dev) & 15u) == 0, "matrix must be 16-byte aligned");
+  QMOE_REQUIRE(!(ln_weight_dev && residual_dev), "norm and residual cannot be combined");
+  QMOE_REQUIRE(!(residual_dev && f32_out), "residual output is bf16");
+  if (k > 8192) {
+    set_error("%s: k <= 8192 is supported", __func__);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_gemv(x_dev, ln_weight_dev, w_dev, residual_dev, y_dev, normed_out_dev, n, k, eps, f32_out,
+                     as_stream(stream));
 }
 
 int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,

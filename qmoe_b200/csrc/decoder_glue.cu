@@ -195,3 +195,100 @@ int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const
 }
 
 }  // namespace qmoe
+
+namespace qmoe {
+
+// y = W x for one token (a matrix-vector product streams W once: HBM-bound), optionally with the
+// T5 RMS norm of x fused in front (every CTA normalises x for itself: 4 KB against the megabytes
+// of W it reads) and a residual added behind.  W bf16 [n][k] row-major, k a multiple of 8, rows
+// 16-byte aligned; one warp per output row with 128-bit loads; fp32 accumulation.
+//   NORM: x := bf16(bf16(x * rsqrt(mean(x^2) + eps)) * ln_w); CTA 0 also stores it to normed_out.
+//   F32OUT: y fp32 (router logits, vocabulary logits), else bf16.
+//   ADD: y := bf16(residual + y).
+constexpr int kGemvThreads = 256;
+constexpr int kGemvRowsPerCta = 16;
+
+template <bool NORM, bool F32OUT, bool ADD>
+__global__ void __launch_bounds__(kGemvThreads) k_gemv(const __nv_bfloat16 *__restrict__ x,
+                                                       const __nv_bfloat16 *__restrict__ ln_w,
+                                                       const __nv_bfloat16 *__restrict__ w,
+                                                       const __nv_bfloat16 *__restrict__ residual, void *y,
+                                                       __nv_bfloat16 *normed_out, int n, int k, float eps) {
+  extern __shared__ __align__(16) float xs[];  // k
+  __shared__ float scratch[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (NORM) {
+    float ss = 0.f;
+    for (int i = tid; i < k; i += kGemvThreads) {
+      const float v = __bfloat162float(x[i]);
+      xs[i] = v;
+      ss += v * v;
+    }
+    const float r = rsqrtf(block_sum(ss, scratch) / (float)k + eps);
+    for (int i = tid; i < k; i += kGemvThreads) {
+      const __nv_bfloat16 a = __float2bfloat16_rn(xs[i] * r);
+      const __nv_bfloat16 b = __float2bfloat16_rn(__bfloat162float(a) * __bfloat162float(ln_w[i]));
+      xs[i] = __bfloat162float(b);
+      if (blockIdx.x == 0 && normed_out != nullptr) normed_out[i] = b;
+    }
+  } else {
+    for (int i = tid; i < k; i += kGemvThreads) xs[i] = __bfloat162float(x[i]);
+  }
+  __syncthreads();
+  const int row_end = min(n, (int)(blockIdx.x + 1) * kGemvRowsPerCta);
+  for (int row0 = blockIdx.x * kGemvRowsPerCta + warp * 2; row0 < row_end; row0 += 2 * (kGemvThreads / 32)) {
+    // two rows per warp at a time: twice the loads in flight
+    const bool two = row0 + 1 < row_end;
+    const uint4 *wa = reinterpret_cast<const uint4 *>(w + (size_t)row0 * k);
+    const uint4 *wb = reinterpret_cast<const uint4 *>(w + (size_t)(row0 + (two ? 1 : 0)) * k);
+    float sa = 0.f, sb = 0.f;
+#pragma unroll 4
+    for (int c = lane; c < k / 8; c += 32) {
+      const uint4 qa = __ldg(wa + c), qb = __ldg(wb + c);
+      const float4 x0 = *reinterpret_cast<const float4 *>(xs + 8 * c);
+      const float4 x1 = *reinterpret_cast<const float4 *>(xs + 8 * c + 4);
+      const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+      const uint32_t ua[4] = {qa.x, qa.y, qa.z, qa.w}, ub[4] = {qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        sa += xv[2 * j] * __uint_as_float(ua[j] << 16) + xv[2 * j + 1] * __uint_as_float(ua[j] & 0xffff0000u);
+        sb += xv[2 * j] * __uint_as_float(ub[j] << 16) + xv[2 * j + 1] * __uint_as_float(ub[j] & 0xffff0000u);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      sa += __shfl_xor_sync(0xffffffffu, sa, o);
+      sb += __shfl_xor_sync(0xffffffffu, sb, o);
+    }
+    if (lane < (two ? 2 : 1)) {
+      const int row = row0 + lane;
+      float v = lane == 0 ? sa : sb;
+      if (ADD) v = __bfloat162float(residual[row]) + __bfloat162float(__float2bfloat16_rn(v));
+      if (F32OUT) reinterpret_cast<float *>(y)[row] = v;
+      else reinterpret_cast<__nv_bfloat16 *>(y)[row] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+int launch_gemv(const void *x, const void *ln_w, const void *w, const void *residual, void *y, void *normed_out,
+                int n, int k, float eps, int f32_out, cudaStream_t stream) {
+  const unsigned grid = (unsigned)((n + kGemvRowsPerCta - 1) / kGemvRowsPerCta);
+  const size_t smem = sizeof(float) * (size_t)k;
+  const __nv_bfloat16 *xb = reinterpret_cast<const __nv_bfloat16 *>(x), *lb = reinterpret_cast<const __nv_bfloat16 *>(ln_w);
+  const __nv_bfloat16 *wb = reinterpret_cast<const __nv_bfloat16 *>(w), *rb = reinterpret_cast<const __nv_bfloat16 *>(residual);
+  __nv_bfloat16 *nb = reinterpret_cast<__nv_bfloat16 *>(normed_out);
+  if (ln_w != nullptr && f32_out)
+    QMOE_LAUNCH((k_gemv<true, true, false>), grid, kGemvThreads, smem, stream, xb, lb, wb, rb, y, nb, n, k, eps);
+  else if (ln_w != nullptr)
+    QMOE_LAUNCH((k_gemv<true, false, false>), grid, kGemvThreads, smem, stream, xb, lb, wb, rb, y, nb, n, k, eps);
+  else if (residual != nullptr)
+    QMOE_LAUNCH((k_gemv<false, false, true>), grid, kGemvThreads, smem, stream, xb, lb, wb, rb, y, nb, n, k, eps);
+  else if (f32_out)
+    QMOE_LAUNCH((k_gemv<false, true, false>), grid, kGemvThreads, smem, stream, xb, lb, wb, rb, y, nb, n, k, eps);
+  else
+    QMOE_LAUNCH((k_gemv<false, false, false>), grid, kGemvThreads, smem, stream, xb, lb, wb, rb, y, nb, n, k, eps);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+}  // namespace qmoe

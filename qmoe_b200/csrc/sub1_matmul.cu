@@ -218,7 +218,7 @@ __device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wli
   }
 }
 
-template <int T, bool GENERAL, class SinkT, class Lookup>
+template <int T, bool GENERAL, class SinkT, int G = 2, class Lookup>
 __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                                  int nrows, int tok0, int ntok, typename SinkT::elem *xs,
                                                  const Lookup &lookup);
@@ -345,6 +345,67 @@ __device__ __forceinline__ void warp_row_sum(const CodeAt &code_at, int n, const
   }
 }
 
+// The same with G groups of 32 codes per iteration (fewer dependent rounds for long rows).
+template <bool GENERAL, int G, class SinkT, class CodeAt, class Lookup>
+__device__ __forceinline__ void warp_row_sum_groups(const CodeAt &code_at, int n, const Lookup &lookup,
+                                             const int32_t *__restrict__ dec, uint32_t limit, SinkT &sink,
+                                             int lane) {
+  constexpr int S = SinkT::kShift;
+  uint32_t row_pos = 0;
+  // G groups of 32 codes per iteration (their dictionary lookups in flight together), and the
+  // codes of the next iteration are requested before this one is processed.
+  uint32_t code[G];
+#pragma unroll
+  for (int g = 0; g < G; g++) code[g] = 32 * g + lane < n ? code_at(32 * g + lane) : 0u;
+  for (int base = 0; base < n; base += 32 * G) {
+    uint32_t c[G], e[G], len[G];
+    bool dense[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      c[g] = code[g];
+      e[g] = base + 32 * g + lane < n ? lookup(c[g]) : kEntryNull;
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      const int next = base + 32 * (G + g) + lane;
+      if (next < n) code[g] = code_at(next);
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      len[g] = 2u * entry_len(e[g]);
+      dense[g] = false;
+      if (GENERAL) {
+        dense[g] = (e[g] & 0xffu) == 0x80u;
+        if (dense[g]) len[g] = 2u * min((uint32_t)__ldg(dec + 2 * c[g]) & 15u, 14u);
+      }
+    }
+    uint32_t incl[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) incl[g] = len[g];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+#pragma unroll
+      for (int g = 0; g < G; g++) {
+        const uint32_t u = __shfl_up_sync(0xffffffffu, incl[g], o);
+        if (lane >= o) incl[g] += u;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      const uint32_t total = __shfl_sync(0xffffffffu, incl[g], 31);
+      const uint32_t p = min(row_pos + incl[g] - len[g], limit);
+      if (GENERAL && dense[g]) dense_code(dec, c[g], (int)p, sink);
+      else sink.entry(e[g], p << S);
+      row_pos = min(row_pos + total, limit);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < (int)(sizeof(sink.acc) / sizeof(float)); t++) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sink.acc[t] += __shfl_xor_sync(0xffffffffu, sink.acc[t], o);
+  }
+}
+
 template <int T, bool GENERAL>
 __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nrows, int tok0, int ntok, float *xs) {
   using SinkT = MatSink<T, true>;
@@ -370,7 +431,7 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
 
 // The same for a work item of an interleaved store: code i of row l of a block is element i % 8
 // of the 16-byte entry (i / 8) * 32 + l.
-template <int T, bool GENERAL, class SinkT, class Lookup>
+template <int T, bool GENERAL, class SinkT, int G, class Lookup>
 __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                                  int nrows, int tok0, int ntok, typename SinkT::elem *xs,
                                                  const Lookup &lookup) {
@@ -390,8 +451,9 @@ __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
-    warp_row_sum<GENERAL>([&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); }, n, lookup,
-                          a.il_dec, (uint32_t)wlim, sink, lane);
+    const auto code_at = [&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); };
+    if constexpr (G == 2) warp_row_sum<GENERAL>(code_at, n, lookup, a.il_dec, (uint32_t)wlim, sink, lane);
+    else warp_row_sum_groups<GENERAL, G>(code_at, n, lookup, a.il_dec, (uint32_t)wlim, sink, lane);
     if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
   }
 }
@@ -401,7 +463,7 @@ __device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_m
                                                int tok0, int ntok, typename SinkT::elem *xs) {
   stage_tokens<T, SinkT>(a, d.width, (d.width + 1) & ~1, tok0, ntok, xs);
   __syncthreads();
-  warp_rows_staged<T, GENERAL, SinkT>(a, d, row0, nrows, tok0, ntok, xs, GlobalLookup{a.il_tab});
+  warp_rows_staged<T, GENERAL, SinkT, 4>(a, d, row0, nrows, tok0, ntok, xs, GlobalLookup{a.il_tab});
 }
 
 // grid.x = row blocks of a.rpc rows, grid.y = token groups of kMaxGroup tokens.
@@ -472,13 +534,9 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
 template <bool GENERAL>
 __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
-  __shared__ int s_item;
   const int n_items = a.header[0];
-  for (;;) {
-    if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
-    __syncthreads();
-    const int i = s_item;
-    if (i >= n_items) break;
+  // items are few and equal (eight rows each): a fixed assignment saves the fetch counter's latency
+  for (int i = blockIdx.x; i < n_items; i += gridDim.x) {
     const int4 it = a.items[i];
     const qmoe_matrix_desc d = a.descs[it.x];
     const int nrows = it.w & 0xffff, ntok = it.w >> 16;
@@ -490,7 +548,7 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const M
     else
       warp_rows_item<4, GENERAL, MatSink<4, false>>(a, d, it.y, nrows, it.z, ntok,
                                                     reinterpret_cast<__nv_bfloat16 *>(smem_u32));
-    __syncthreads();  // xs and s_item are rewritten by the next round
+    __syncthreads();  // xs is rewritten by the next round
   }
 }
 
@@ -1072,10 +1130,13 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
       w.items = ph[phase].warp_items;
       w.header = header + 10 + 2 * phase;
       const size_t wsmem = grouped_x_bytes(width, kMaxGroup);
+      int per_sm = (int)(kSmemPerCta / (wsmem + 1024));  // CTAs of 256 threads that fit one SM
+      per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
+      const unsigned wgrid = (unsigned)(per_sm * sms);
       if (tab.conforming)
-        QMOE_LAUNCH(k_matmul_grouped_warp<false>, (unsigned)(4 * sms), kWarpRowThreads, wsmem, stream, w);
+        QMOE_LAUNCH(k_matmul_grouped_warp<false>, wgrid, kWarpRowThreads, wsmem, stream, w);
       else
-        QMOE_LAUNCH(k_matmul_grouped_warp<true>, (unsigned)(4 * sms), kWarpRowThreads, wsmem, stream, w);
+        QMOE_LAUNCH(k_matmul_grouped_warp<true>, wgrid, kWarpRowThreads, wsmem, stream, w);
       QMOE_CUDA(cudaGetLastError());
     }
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));

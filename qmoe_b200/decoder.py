@@ -37,18 +37,28 @@ class ReplicatedTokenMoE:
         self.capacity = expert_capacity
         self.router = sub1.RouterClassifier(router_weight, store.device)
 
-    def __call__(self, hidden: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def decode_step(self, x: torch.Tensor, ln_weight: torch.Tensor) -> torch.Tensor:
+        """``x + moe(rms_norm(x))`` for one token; the norm rides on the router's matrix-vector
+        product when the router weights are exact in bf16."""
+        if self.router.w16 is not None and x.shape[0] == 1:
+            logits, hidden = sub1.gemv(x, self.router.w16, ln_weight=ln_weight, f32_out=True, want_normed=True)
+            return self(hidden, residual=x, logits=logits)
+        return self(sub1.rms_norm(x, ln_weight), residual=x)
+
+    def __call__(self, hidden: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                 logits: Optional[torch.Tensor] = None) -> torch.Tensor:
         """MoE output for ``hidden``; with ``residual`` (single-rank only) ``residual + output``."""
         n, d = hidden.shape
+        if logits is None:
+            logits = self.router(hidden).contiguous()
         if self.world == 1 and n <= 32:
             # a decode step: routing, ranking and permutation in one launch
-            prob, offsets, slot, xs = sub1.route_small(self.router(hidden).contiguous(), hidden, self.n_experts,
-                                                       self.capacity)
+            prob, offsets, slot, xs = sub1.route_small(logits, hidden, self.n_experts, self.capacity)
             ys = sub1.grouped_ffn(self.store, offsets, xs, n)
             if residual is not None:
                 return sub1.combine_add(ys, hidden, slot, prob, residual)
             return sub1.combine(ys, hidden, slot, prob)
-        choice, prob = sub1.route_top1(self.router(hidden).contiguous())
+        choice, prob = sub1.route_top1(logits)
         if self.world == 1:
             # all experts are local: the single-GPU layer (route, rank, permute, FFN, combine)
             bucket, rank, _, offsets = sub1.rank_buckets(choice, self.n_experts, n, self.capacity)
@@ -147,16 +157,17 @@ class SwitchDecoderLM:
         return (_rms_norm(x, self.final_norm) @ self.lm_head.t()).float()
 
     def _forward_one(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
-        """The same block arithmetic for a single token with one launch per group of element-wise
-        operations: fused RMS norm, one attention kernel that also stores the token's key and value,
-        and the MoE combine with the residual addition folded in."""
+        """The same block arithmetic for a single token with one launch per group of operations:
+        matrix-vector products with the RMS norm fused in front or the residual behind, one
+        attention kernel that also stores the token's key and value, one routing kernel, and the
+        MoE combine with the residual addition folded in."""
         x = self.embed[ids]
         for i, b in enumerate(self.blocks):
-            qkv = sub1.rms_norm(x, b["ln1"]) @ b["wqkv"].t()
+            qkv = sub1.gemv(x, b["wqkv"], ln_weight=b["ln1"])
             att = sub1.decode_attention(qkv, self.k_cache[i], self.v_cache[i], pos)
-            x = torch.addmm(x, att, b["wo"].t())
-            x = b["moe"](sub1.rms_norm(x, b["ln2"]), residual=x)
-        return (sub1.rms_norm(x, self.final_norm) @ self.lm_head.t()).float()
+            x = sub1.gemv(att, b["wo"], residual=x)
+            x = b["moe"].decode_step(x, b["ln2"])
+        return sub1.gemv(x, self.lm_head, ln_weight=self.final_norm, f32_out=True)
 
     @torch.no_grad()
     def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True) -> torch.Tensor:

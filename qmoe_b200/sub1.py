@@ -424,6 +424,23 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.
     return out
 
 
+def gemv(x: torch.Tensor, w: torch.Tensor, ln_weight: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, f32_out: bool = False, want_normed: bool = False):
+    """``w @ x`` for one token (``x`` bf16 [1, k], ``w`` bf16 [n, k]) in one launch, optionally with
+    the RMS norm of ``x`` in front (``ln_weight``) or a residual behind.  Returns ``y`` [1, n], or
+    ``(y, normed_x)`` with ``want_normed``."""
+    n, k = w.shape
+    dev = x.device
+    assert x.numel() == k and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous()
+    y = torch.empty((1, n), dtype=torch.float32 if f32_out else torch.bfloat16, device=dev)
+    normed = torch.empty((1, k), dtype=torch.bfloat16, device=dev) if want_normed else None
+    _lib.check(_lib.load().qmoe_gemv(
+        x.data_ptr(), None if ln_weight is None else ln_weight.data_ptr(), w.data_ptr(),
+        None if residual is None else residual.data_ptr(), y.data_ptr(),
+        None if normed is None else normed.data_ptr(), n, k, 1e-6, 1 if f32_out else 0, dev.index, _s(dev)))
+    return (y, normed) if want_normed else y
+
+
 def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
     """Causal self-attention of one new token (``qkv`` bf16 [3, heads, head_dim]) against caches
     bf16 [heads, max_len, head_dim]; the token's key / value are stored at ``pos`` (device int64[1])."""

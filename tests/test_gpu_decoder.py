@@ -105,3 +105,26 @@ def test_decode_attention_matches_masked_sdpa():
         want = F.scaled_dot_product_attention(qkv[0].float().unsqueeze(1), k_ref[:, :p + 1].float(),
                                               v_ref[:, :p + 1].float())[:, 0]
         assert float((got.float() - want).abs().max()) <= 2e-2 * max(float(want.abs().max()), 1e-3)
+
+
+def test_one_token_matrix_vector_kernel_variants():
+    from qmoe_b200 import sub1
+    from qmoe_b200.decoder import _rms_norm
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(8)
+    for n, k in ((6240, 2080), (37, 64), (1, 8), (300, 4096)):
+        x = torch.randn(1, k, generator=g).bfloat16().to(dev)
+        w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().to(dev)
+        ln = (1 + 0.1 * torch.randn(k, generator=g)).bfloat16().to(dev)
+        res = torch.randn(1, n, generator=g).bfloat16().to(dev)
+        ref = x.float() @ w.float().t()
+        scale = float(ref.abs().max())
+        assert float((sub1.gemv(x, w).float() - ref).abs().max()) <= 1e-2 * scale
+        assert float((sub1.gemv(x, w, f32_out=True) - ref).abs().max()) <= 1e-4 * scale
+        got = sub1.gemv(x, w, residual=res).float()
+        assert float((got - (res.float() + ref.bfloat16().float())).abs().max()) <= 2e-2 * max(scale, 1.0)
+        xn = _rms_norm(x, ln)
+        y, normed = sub1.gemv(x, w, ln_weight=ln, f32_out=True, want_normed=True)
+        assert float((normed.float() - xn.float()).abs().max()) <= 2 ** -6 * float(xn.float().abs().max())
+        ref_n = normed.float() @ w.float().t()
+        assert float((y - ref_n).abs().max()) <= 1e-4 * float(ref_n.abs().max())
