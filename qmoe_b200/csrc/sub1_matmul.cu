@@ -944,9 +944,22 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       }
       __syncthreads();
       const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
-      // The items of a lane's expert are written by its whole warp (hundreds of 8-row warp items
-      // per group would otherwise be one thread's serial loop).
-      unsigned busy = __ballot_sync(0xffffffffu, groups > 0);
+      // Items for the per-thread kernel (a few per group): every lane writes those of its expert.
+      for (int g = 0; g < groups && chunks > 0; g++) {
+        const int gi = base + g;
+        if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
+        const int tok0 = first + g * kMaxGroup;
+        const int ntok = min(kMaxGroup, count - g * kMaxGroup);
+        for (int k = 0; k < chunks; k++) {
+          const int row0 = k * rpc;
+          p.items[(size_t)gi * chunks + k] =
+              make_int4(2 * e + p.which, row0, tok0,
+                        min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) | (ntok << 16));
+        }
+      }
+      // Items for the warp kernel (hundreds per group, but only in steps with a handful of groups):
+      // the whole warp writes those of each lane's expert in turn.
+      unsigned busy = __ballot_sync(0xffffffffu, groups > 0 && wchunks > 0);
       while (busy) {
         const int src = __ffs(busy) - 1;
         busy &= busy - 1;
@@ -955,18 +968,9 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
         const int o_base = __shfl_sync(0xffffffffu, base, src);
         for (int g = 0; g < o_groups; g++) {
           const int gi = o_base + g;
-          // cannot happen for valid offsets
-          if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity ||
-              (long long)(gi + 1) * wchunks > p.warp_capacity)
-            break;
+          if (gi >= max_slots || (long long)(gi + 1) * wchunks > p.warp_capacity) break;
           const int tok0 = o_first + g * kMaxGroup;
           const int ntok = min(kMaxGroup, o_count - g * kMaxGroup);
-          for (int k = lane; k < chunks; k += 32) {
-            const int row0 = k * rpc;
-            p.items[(size_t)gi * chunks + k] =
-                make_int4(2 * o_e + p.which, row0, tok0,
-                          min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) | (ntok << 16));
-          }
           for (int k = lane; k < wchunks; k += 32) {
             const int row0 = k * kWarpItemRows;
             p.warp_items[(size_t)gi * wchunks + k] =
@@ -1002,8 +1006,8 @@ int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t 
 // Experts with at least this many tokens take the tile path (0 disables it).  The default is the
 // measured break-even on a switch-large-128 layer with a skewed router (eight hot experts share half
 // of the tokens): at about 140 tokens per hot expert the per-row kernel (36 passes of four tokens) is
-// still faster, 0.70 ms against 1.06 ms per layer; at about 560 tokens the tile path wins, 2.16 ms
-// against 2.45 ms; at about 2200 tokens, 5.03 ms against 6.99 ms.  The environment variable exists
+// still faster, 0.67 ms against 0.79 ms per layer; at about 560 tokens the tile path wins, 2.16 ms
+// against 2.41 ms; at about 2200 tokens, 5.05 ms against 6.96 ms.  The environment variable exists
 // for such measurements.
 static std::atomic<int> g_tile_min{-1};  // -1: not yet initialised from the environment
 static int clamp_tile_min(int t) { return t <= 0 ? 0 : (t < 8 ? 8 : t); }
