@@ -182,6 +182,7 @@ def cpu_baseline(args, d_model, d_ff, n_experts):
     import numpy as np
     from oracle import oracle as O
     from qmoe_b200 import synth
+    O.use_all_cores()
     x = synth.tokens(64, d_model, SEED)
     x_bits = x.view(__import__("torch").int16).numpy().view(np.uint16)
     probe = cpu_sample_experts(d_model, d_ff, [0])
@@ -206,6 +207,7 @@ def run_reference(args):
     from oracle import oracle as O
     from qmoe_b200 import synth
     O.build()
+    O.use_all_cores()                  # torchrun exports OMP_NUM_THREADS=1
     d_model, d_ff, n_experts, n_tokens = workload_dims(args)
     x = synth.tokens(64, d_model, SEED)
     x_bits = x.view(__import__("torch").int16).numpy().view(np.uint16)

@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_synth_ternary.restype = None
         L.oracle_num_threads.argtypes = []
         L.oracle_num_threads.restype = I
+        L.oracle_set_num_threads.argtypes = [I]
+        L.oracle_set_num_threads.restype = None
         _lib = L
     return _lib
 
@@ -164,6 +166,15 @@ def synth_ternary(count: int, seed: int, first_index: int, p_zero: float) -> np.
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Let the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says
+    (multi-process launchers set it to 1); returns the thread count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(n)
+    return num_threads()
 
 
 # ---------------------------------------------------------------------------------------------

@@ -331,3 +331,13 @@ int oracle_num_threads(void) {
   return 1;
 #endif
 }
+
+/* Launchers that start one process per GPU export OMP_NUM_THREADS=1; the CPU baseline is meant to use
+ * the host's cores, so the benchmark sets the count explicitly. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
