@@ -7,12 +7,16 @@
 //    loads, the running column position is a private register, nothing is shuffled or synchronised
 //    inside a row, and all 32 lanes do useful work;
 //  * a derived 4-byte sparse dictionary (common.cuh) turns a code into at most three gathers from
-//    the activation vector instead of 28 multiply-adds:
-//        y[r] = min_r * sum_{digit 1} x[c] + max_r * sum_{digit 2} x[c];
+//    the activation vector, each followed by one multiply-add with min_r or max_r, instead of 28
+//    multiply-adds;
 //  * the activations of up to four tokens are interleaved in shared memory so that one decode
-//    serves all of them (one 4/8/16-byte shared load per non-zero);
+//    serves all of them (one 4- or 8-byte shared load per non-zero: fp32 for one token, bf16 pairs
+//    or quads for more);
 //  * a work list of (matrix, row block, token group) items lets one launch cover every active
-//    expert of a MoE layer.
+//    expert of a MoE layer;
+//  * for such launches the code streams are read from a lane-interleaved copy (32 rows alternate
+//    chunk by chunk, so a warp's loads are contiguous) whose code values are renumbered by
+//    frequency, and the most frequent 45-53 thousand dictionary entries sit in shared memory.
 #include "common.cuh"
 #include "sub1_walk.cuh"
 

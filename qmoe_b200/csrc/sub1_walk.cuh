@@ -7,8 +7,9 @@
 // is no cross-lane dependency, no shuffle and no barrier inside a row.
 //
 // The inner loop is written for instruction count: a code costs one table load, one position
-// update and, per possible non-zero, one byte extract, one predicated shared load and two
-// predicated adds.  Full chunks of eight codes take a path without per-code range checks.
+// update and, per possible non-zero, one byte extract, one predicated shared load, one select of the
+// row's weight value and one multiply-add.  Only the first and the last group of four codes of a
+// row pay per-code range checks.
 #pragma once
 
 #include "common.cuh"
