@@ -56,6 +56,9 @@ def parse_args():
     p.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
     p.add_argument("--skew", type=int, default=0,
                    help="skewed router: this many hot experts receive half of the tokens (config 3 uses 8)")
+    p.add_argument("--kernel-times", action="store_true",
+                   help="generate mode: also time the kernels of a decode step (torch profiler, eager launches) "
+                        "and add their average durations to the JSON line")
     p.add_argument("--mode", default="moe", choices=["moe", "layers", "generate"],
                    help="moe: the MoE-layer benchmark (default); layers: the reference's per-layer matvec "
                         "benchmark (test.py --benchmark) on its six shapes")
@@ -571,9 +574,32 @@ def run_generate(args):
         if it > 0:
             times.append(time.perf_counter() - t0)
     secs = sum(times) / len(times)
+    kernel_times = None
+    if args.kernel_times and world == 1:
+        # five eager single-token steps under the torch profiler, after the timed samples
+        from torch.profiler import ProfilerActivity, profile
+        tok = out[-1:].clone()
+        pos = torch.full((1,), prompt_len + new_tokens - 1, dtype=torch.int64, device=dev)
+        with torch.no_grad():
+            for _ in range(3):
+                model.forward(tok, pos)
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(5):
+                    model.forward(tok, pos)
+                torch.cuda.synchronize()
+        rows = [e for e in prof.key_averages() if e.device_type == torch.autograd.DeviceType.CUDA]
+        total = sum(e.device_time_total for e in rows)
+        kernel_times = {
+            "per_step_us": round(total / 5, 1), "launches_per_step": sum(e.count for e in rows) / 5,
+            "kernels": [{"name": e.key[:60], "calls_per_step": e.count / 5,
+                         "avg_us": round(e.device_time_total / max(e.count, 1), 2),
+                         "share": round(e.device_time_total / total, 4)}
+                        for e in sorted(rows, key=lambda e: -e.device_time_total)[:12]]}
     if rank == 0:
         print(json.dumps({
             "mode": "generate", "metric": "generated_tokens_per_s", "value": new_tokens / secs, "unit": "tokens/s",
+            "decode_step_kernels": kernel_times,
             "n_gpus": world, "seconds_per_sample": secs, "samples": len(times),
             "config": {"workload": args.workload + " decoder", "layers": layers, "d_model": d_model, "d_ff": d_ff,
                        "experts": n_experts, "heads": 32, "vocab": 32128, "prompt": prompt_len,
