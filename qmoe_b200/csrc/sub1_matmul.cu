@@ -462,12 +462,12 @@ __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe
   }
 }
 
-template <int T, bool GENERAL, class SinkT>
+template <int T, bool GENERAL, class SinkT, int G>
 __device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
                                                int tok0, int ntok, typename SinkT::elem *xs) {
   stage_tokens<T, SinkT>(a, d.width, (d.width + 1) & ~1, tok0, ntok, xs);
   __syncthreads();
-  warp_rows_staged<T, GENERAL, SinkT, 4>(a, d, row0, nrows, tok0, ntok, xs, GlobalLookup{a.il_tab});
+  warp_rows_staged<T, GENERAL, SinkT, G>(a, d, row0, nrows, tok0, ntok, xs, GlobalLookup{a.il_tab});
 }
 
 // grid.x = row blocks of a.rpc rows, grid.y = token groups of kMaxGroup tokens.
@@ -535,7 +535,10 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
 // when a matrix's height is not a multiple of the 1024 rows a CTA of k_matmul_grouped takes, and
 // whole layers when so few experts are active (one token per step while generating) that rows per
 // thread could not fill the GPU.  Several CTAs per SM; the table is read through L1/L2.
-template <bool GENERAL>
+// G: groups of 32 codes per round of a row.  A row of w weights has about w / 23 codes; the host
+// picks nine groups for wide matrices, so that a 6144-wide row (about 265 codes) is one round of
+// dictionary lookups instead of three, and four otherwise (fewer registers, more CTAs per SM).
+template <bool GENERAL, int G>
 __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
   const int n_items = a.header[0];
@@ -545,13 +548,13 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const M
     const qmoe_matrix_desc d = a.descs[it.x];
     const int nrows = it.w & 0xffff, ntok = it.w >> 16;
     if (ntok <= 1)
-      warp_rows_item<1, GENERAL, MatSink<1, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(smem_u32));
+      warp_rows_item<1, GENERAL, MatSink<1, true>, G>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(smem_u32));
     else if (ntok == 2)
-      warp_rows_item<2, GENERAL, MatSink<2, false>>(a, d, it.y, nrows, it.z, ntok,
-                                                    reinterpret_cast<__nv_bfloat16 *>(smem_u32));
+      warp_rows_item<2, GENERAL, MatSink<2, false>, G>(a, d, it.y, nrows, it.z, ntok,
+                                                       reinterpret_cast<__nv_bfloat16 *>(smem_u32));
     else
-      warp_rows_item<4, GENERAL, MatSink<4, false>>(a, d, it.y, nrows, it.z, ntok,
-                                                    reinterpret_cast<__nv_bfloat16 *>(smem_u32));
+      warp_rows_item<4, GENERAL, MatSink<4, false>, G>(a, d, it.y, nrows, it.z, ntok,
+                                                       reinterpret_cast<__nv_bfloat16 *>(smem_u32));
     __syncthreads();  // xs is rewritten by the next round
   }
 }
@@ -632,7 +635,9 @@ static int set_smem_limits() {
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemPerCta));
-  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped_warp<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped_warp<GENERAL, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped_warp<GENERAL, 9>), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   return QMOE_OK;
 }
@@ -1141,10 +1146,15 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
       int per_sm = (int)(kSmemPerCta / (wsmem + 1024));  // CTAs of 256 threads that fit one SM
       per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
       const unsigned wgrid = (unsigned)(per_sm * sms);
-      if (tab.conforming)
-        QMOE_LAUNCH(k_matmul_grouped_warp<false>, wgrid, kWarpRowThreads, wsmem, stream, w);
+      const bool long_rows = width > 3072;
+      if (tab.conforming && long_rows)
+        QMOE_LAUNCH((k_matmul_grouped_warp<false, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
+      else if (tab.conforming)
+        QMOE_LAUNCH((k_matmul_grouped_warp<false, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
+      else if (long_rows)
+        QMOE_LAUNCH((k_matmul_grouped_warp<true, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
       else
-        QMOE_LAUNCH(k_matmul_grouped_warp<true>, wgrid, kWarpRowThreads, wsmem, stream, w);
+        QMOE_LAUNCH((k_matmul_grouped_warp<true, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
       QMOE_CUDA(cudaGetLastError());
     }
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
