@@ -250,7 +250,7 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
  *     of the token; caches bf16 [heads][max_len][head_dim]; *pos_dev (device int64) is the token's
  *     position: its key and value are written there, then
  *     out[head] = softmax(q . K[0..pos] / sqrt(head_dim)) V[0..pos] (fp32 arithmetic, bf16 result).
- *     head_dim <= 256, max_len <= 8192. */
+ *     head_dim <= 256. */
 int qmoe_moe_combine_add(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev,
                          const void *prob_dev, const void *residual_dev, void *out_dev, int n_tokens,
                          int d_model, int device, void *stream);

@@ -639,8 +639,8 @@ int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_
                           void *out_dev, int heads, int head_dim, int max_len, int device, void *stream) {
   QMOE_REQUIRE(qkv_dev && k_cache_dev && v_cache_dev && pos_dev && out_dev, "null device pointer");
   QMOE_REQUIRE(heads >= 1 && head_dim >= 1 && max_len >= 1, "bad shape");
-  if (head_dim > 256 || max_len > 8192) {
-    set_error("%s: head_dim <= 256 and max_len <= 8192 are supported", __func__);
+  if (head_dim > 256) {
+    set_error("%s: head_dim <= 256 is supported", __func__);
     return QMOE_ERR_UNSUPPORTED;
   }
   DeviceGuard guard(device);

@@ -62,15 +62,20 @@ __global__ void k_rms_norm(const __nv_bfloat16 *__restrict__ x, const __nv_bfloa
 // One new token of causal self-attention, one CTA per head.  qkv: [3][heads][hd] of the token;
 // caches: [heads][max_len][hd].  Writes the token's key and value at position *pos, then
 // out[head] = softmax(q . K[0..pos] / sqrt(hd)) V[0..pos], fp32 arithmetic, bf16 result.
+// Every warp runs a running-maximum softmax over its share of the positions (up to four at a
+// time, their key and value rows loaded together) and the warps' partial results are merged once.
 template <int J>  // ceil(head_dim / 32): values of a cache row per lane
-__global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __nv_bfloat16 *__restrict__ qkv, __nv_bfloat16 *__restrict__ k_cache,
+__global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __nv_bfloat16 *__restrict__ qkv,
+                                   __nv_bfloat16 *__restrict__ k_cache,
                                    __nv_bfloat16 *__restrict__ v_cache, const long long *__restrict__ pos_ptr,
                                    __nv_bfloat16 *__restrict__ out, int heads, int hd, int max_len) {
   extern __shared__ float smem[];
-  float *q = smem;            // hd
-  float *score = smem + hd;   // max_len
-  __shared__ float scratch[32];
-  const int head = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  constexpr int kWarps = kAttentionThreads / 32;
+  float *q = smem;                     // hd
+  float *partial = smem + hd;          // [kWarps][hd]
+  float *part_m = partial + kWarps * hd;  // [kWarps]
+  float *part_s = part_m + kWarps;        // [kWarps]
+  const int head = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   long long pos = *pos_ptr;
   pos = pos < 0 ? 0 : (pos >= max_len ? max_len - 1 : pos);
   __nv_bfloat16 *kc = k_cache + (size_t)head * max_len * hd;
@@ -82,78 +87,70 @@ __global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __
   }
   __syncthreads();
   const float scale = rsqrtf((float)hd);
-  // Positions are taken eight at a time per warp with every load of the eight issued before the
-  // first use: the loop is bound by the latency of the cache reads, not by their number.
-  constexpr int U = 8;
-  for (int t0 = warp * U; t0 <= pos; t0 += nwarps * U) {
-    float kv[U][J];
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-#pragma unroll
-      for (int j = 0; j < J; j++) {
-        const int i = lane + 32 * j;
-        kv[u][j] = (t0 + u <= pos && i < hd) ? __bfloat162float(kc[(size_t)(t0 + u) * hd + i]) : 0.f;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < J; j++) {
-        const int i = lane + 32 * j;
-        if (i < hd) s += q[i] * kv[u][j];
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (lane == 0 && t0 + u <= pos) score[t0 + u] = s * scale;
-    }
-  }
-  __syncthreads();
-  float m = -3.0e38f;
-  for (int t = tid; t <= pos; t += blockDim.x) m = fmaxf(m, score[t]);
-  m = block_max(m, scratch);
-  float sum = 0.f;
-  for (int t = tid; t <= pos; t += blockDim.x) {
-    const float p = __expf(score[t] - m);
-    score[t] = p;
-    sum += p;
-  }
-  sum = block_sum(sum, scratch);  // its barriers also publish score[]
-  const float inv = 1.f / sum;
-  // out[i] = sum_t p[t] V[t][i]: every warp takes the positions t = warp, warp + nwarps, ... with
-  // its lanes over i, then the warps' partial sums are added through shared memory (partial[]
-  // follows score[]).
-  float *partial = score + max_len;  // [nwarps][hd]
-  float acc[J];
+  // 2 * U * J cache values per lane stay in registers (64 registers per thread at 1024 threads)
+  constexpr int U = J <= 3 ? 4 : (J <= 4 ? 2 : 1);
+  float m = -INFINITY, ssum = 0.f, acc[J];
 #pragma unroll
   for (int j = 0; j < J; j++) acc[j] = 0.f;
-  for (int t0 = warp * U; t0 <= pos; t0 += nwarps * U) {
-    float vv[U][J];
+  for (int t0 = warp * U; t0 <= pos; t0 += kWarps * U) {
+    float kv[U][J], vv[U][J];
 #pragma unroll
     for (int u = 0; u < U; u++) {
 #pragma unroll
       for (int j = 0; j < J; j++) {
         const int i = lane + 32 * j;
-        vv[u][j] = (t0 + u <= pos && i < hd) ? __bfloat162float(vc[(size_t)(t0 + u) * hd + i]) : 0.f;
+        const bool ok = t0 + u <= pos && i < hd;
+        kv[u][j] = ok ? __bfloat162float(kc[(size_t)(t0 + u) * hd + i]) : 0.f;
+        vv[u][j] = ok ? __bfloat162float(vc[(size_t)(t0 + u) * hd + i]) : 0.f;
       }
     }
+    float sc[U], round_max = -INFINITY;
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      const float p = t0 + u <= pos ? score[t0 + u] : 0.f;
+      float d = 0.f;
+#pragma unroll
+      for (int j = 0; j < J; j++) {
+        const int i = lane + 32 * j;
+        if (i < hd) d += q[i] * kv[u][j];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      sc[u] = t0 + u <= pos ? d * scale : -INFINITY;  // the same in every lane
+      round_max = fmaxf(round_max, sc[u]);
+    }
+    // t0 <= pos: at least one score of the round is finite
+    const float m_new = fmaxf(m, round_max);
+    const float rescale = __expf(m - m_new);  // 0 on the first round (m = -inf)
+    ssum *= rescale;
+#pragma unroll
+    for (int j = 0; j < J; j++) acc[j] *= rescale;
+    m = m_new;
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const float p = __expf(sc[u] - m);
+      ssum += p;
 #pragma unroll
       for (int j = 0; j < J; j++) acc[j] += p * vv[u][j];
     }
   }
 #pragma unroll
-  for (int j = 0; j < kMaxHeadDim / 32; j++) {
+  for (int j = 0; j < J; j++) {
     const int i = lane + 32 * j;
     if (i < hd) partial[warp * hd + i] = acc[j];
   }
+  if (lane == 0) {
+    part_m[warp] = m;   // -inf for a warp without positions: weight 0 below
+    part_s[warp] = ssum;
+  }
   __syncthreads();
+  float top = -INFINITY;
+  for (int w = 0; w < kWarps; w++) top = fmaxf(top, part_m[w]);
+  float denom = 0.f;
+  for (int w = 0; w < kWarps; w++) denom += part_s[w] * __expf(part_m[w] - top);
   for (int i = tid; i < hd; i += blockDim.x) {
     float total = 0.f;
-    for (int w = 0; w < nwarps; w++) total += partial[w * hd + i];
-    out[(size_t)head * hd + i] = __float2bfloat16_rn(total * inv);
+    for (int w = 0; w < kWarps; w++) total += partial[w * hd + i] * __expf(part_m[w] - top);
+    out[(size_t)head * hd + i] = __float2bfloat16_rn(total / denom);
   }
 }
 
@@ -167,7 +164,7 @@ int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, fl
 
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
                             int heads, int hd, int max_len, cudaStream_t stream) {
-  const size_t smem = sizeof(float) * ((size_t)hd + (size_t)max_len + (size_t)(kAttentionThreads / 32) * hd);
+  const size_t smem = sizeof(float) * ((size_t)hd + (size_t)(kAttentionThreads / 32) * (hd + 2));
   static bool limit_set[64][kMaxHeadDim / 32 + 1] = {};  // per device and instantiation
   int device = 0;
   QMOE_CUDA(cudaGetDevice(&device));

@@ -87,12 +87,13 @@ def test_fused_rms_norm_matches_torch_formulation():
         assert float((got.float() - want.float()).abs().max()) <= 2 ** -6 * float(want.float().abs().max())
 
 
-def test_decode_attention_matches_masked_sdpa():
+@pytest.mark.parametrize("hd,max_len", [(65, 48), (128, 300), (200, 40), (16, 9000)])
+def test_decode_attention_matches_masked_sdpa(hd, max_len):
     import torch.nn.functional as F
     from qmoe_b200 import sub1
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(6)
-    heads, hd, max_len = 4, 65, 48
+    heads = 4
     k_cache = torch.randn(heads, max_len, hd, generator=g).bfloat16().to(dev)
     v_cache = torch.randn(heads, max_len, hd, generator=g).bfloat16().to(dev)
     for p in (0, 1, 17, max_len - 1):
