@@ -43,8 +43,14 @@ int qmoe_sub1_build_dictionary(int32_t *dec_host, int32_t *trie_host);
 
 /* Replaces sub1matvec (sub1_cuda.cpp:35-45 -> sub1matvec_cuda, sub1_cuda_kernel.cu:70-88 ->
  * Sub1MatVec, :129-202): y[r] += bf16(sum_c W[r,c] x[c]) for one compressed matrix and one bf16
- * vector.  Any height >= 1 and even width >= 2 (width <= QMOE_MAX_WIDTH) is accepted, not only
- * the reference's six hard-coded shapes.
+ * vector.  Any height >= 1 and any width >= 1 (odd widths included, width <= QMOE_MAX_WIDTH) is
+ * accepted, not only the reference's six hard-coded shapes.
+ *
+ * The library derives a 4-byte form of `dec` the first time it sees a (device, dec_dev) pair and
+ * keeps it, keyed by that ADDRESS.  The cache does not look at the contents again: after
+ * overwriting a dec tensor in place, or after freeing it (an allocator may hand the same address
+ * to a different table later), call qmoe_sub1_forget (or qmoe_sub1_release) before the address is
+ * used again.  The Python shim does this when a dec tensor is garbage collected.
  *   dec_dev        int32[131072]   decoder table (sub1.py:60-72)
  *   w_comp_dev     uint16[n_codes] code stream, rows concatenated
  *   row_off_dev    int32[height+1] exclusive prefix sums of codes per row
@@ -175,6 +181,15 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
  * QMOE_TILE_MIN_TOKENS), the measured break-even.  Returns the previous value.  No counterpart in
  * the reference, which runs one matvec per token (sub1.py:139-142). */
 int qmoe_moe_set_tile_min_tokens(int tokens);
+
+/* Host read-back (synchronises `stream`) of what the last qmoe_moe_grouped_ffn call that used
+ * work_dev planned, for tests and reports; max_slots / d_model / d_ff as in that call.
+ * out_host int32[8]: [0] / [1] row-per-thread work items of wi / wo, [2] / [3] row-per-warp work
+ * items of wi / wo, [4] wo items whose CTA also does the remainder rows of its matrix one per
+ * warp, [5] tokens decoded together, [6] / [7] tensor-core tile items of wi / wo.  No counterpart in
+ * the reference (one launch per token and matrix, sub1.py:139-142). */
+int qmoe_moe_work_summary(const void *work_dev, int max_slots, int d_model, int d_ff, int32_t *out_host,
+                          int device, void *stream);
 int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
                          const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
                          const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,
@@ -278,6 +293,22 @@ int qmoe_profile_read(float *wi_ms, float *wo_ms, int *n_calls);
 /* Frees every per-device cache the library holds (derived decoder tables keyed by the dec pointer).
  * Call it after overwriting a dec tensor in place, and before unloading. */
 int qmoe_sub1_release(int device);
+
+/* Frees the cached derived table of one (device, dec_dev) pair, if any: to be called when that dec
+ * tensor is freed or overwritten, so that a later table at the same address is derived afresh.  No
+ * counterpart in the reference, which reads `dec` directly in its kernel (sub1_cuda_kernel.cu:188). */
+int qmoe_sub1_forget(const int32_t *dec_dev, int device);
+
+/* Status of the tensor-core tile kernels inside qmoe_moe_grouped_ffn.  Each of their waits on an
+ * MMA-completion barrier is bounded; a CTA whose wait runs out stops, writes zeros for the output
+ * rows it did not finish and adds one to a per-device word that no later call clears.
+ * qmoe_moe_tile_timeouts synchronises the device, stores that word in *count_out and clears it when
+ * `reset` is non-zero: callers check it at their own synchronisation points, non-zero means that
+ * outputs since the last reset are incomplete.  qmoe_moe_set_tile_wait_limit(spins) lowers the
+ * number of polls such a wait makes before giving up (0 restores the default of 2^24); it exists
+ * so that a test can make a wait run out without anything hanging.  No counterpart in the reference. */
+int qmoe_moe_tile_timeouts(int device, int reset, int *count_out);
+int qmoe_moe_set_tile_wait_limit(uint32_t spins);
 
 #define QMOE_MAX_WIDTH 8192
 

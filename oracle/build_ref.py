@@ -17,7 +17,18 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-REF = os.environ.get("QMOE_REFERENCE", "/root/reference")
+
+
+def reference_dir():
+    """Where the reference checkout lies: ``$QMOE_REFERENCE``, else a directory named ``reference``
+    beside this repository.  None when neither exists."""
+    env = os.environ.get("QMOE_REFERENCE")
+    cands = [env] if env else [os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "sub1_cuda_kernel.cu")):
+            return c
+    return None
+
 
 
 def built_path():
@@ -26,9 +37,10 @@ def built_path():
 
 
 def build() -> str:
-    srcs = [os.path.join(REF, "sub1_cuda.cpp"), os.path.join(REF, "sub1_cuda_kernel.cu")]
-    if not all(os.path.exists(s) for s in srcs):
-        raise FileNotFoundError(f"reference sources not found under {REF}")
+    ref = reference_dir()
+    if ref is None:
+        raise FileNotFoundError("reference checkout not found: set QMOE_REFERENCE to its directory")
+    srcs = [os.path.join(ref, "sub1_cuda.cpp"), os.path.join(ref, "sub1_cuda_kernel.cu")]
     os.makedirs(OUT, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
     os.environ.setdefault("MAX_JOBS", "4")

@@ -1,7 +1,8 @@
 """ctypes loader of ``libqmoe_sub1.so`` (C ABI in include/qmoe_sub1.h).
 
 The library is the product: there is no Python or CPU fallback behind these calls.  If it is missing
-or stale it is rebuilt with nvcc; if that fails the import error is raised to the caller.
+or older than its sources it is rebuilt with nvcc; a failed rebuild is raised to the caller, also
+when an older library exists (``QMOE_NO_BUILD=1`` loads the existing one without looking).
 """
 from __future__ import annotations
 
@@ -80,6 +81,7 @@ SIGNATURES = {
     "qmoe_moe_unpermute": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _P]),
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
     "qmoe_moe_set_tile_min_tokens": (_I, [_I]),
+    "qmoe_moe_work_summary": (_I, [_P, _I, _I, _I, _P, _I, _P]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_interleave_count": (_I, [_P, _P, _P, _I, _P, _I, _P]),
@@ -96,6 +98,9 @@ SIGNATURES = {
     "qmoe_profile_enable": (_I, [_I]),
     "qmoe_profile_read": (_I, [_P, _P, _P]),
     "qmoe_sub1_release": (_I, [_I]),
+    "qmoe_sub1_forget": (_I, [_P, _I]),
+    "qmoe_moe_tile_timeouts": (_I, [_I, _I, _P]),
+    "qmoe_moe_set_tile_wait_limit": (_I, [ctypes.c_uint32]),
 }
 
 _lib: Optional[ctypes.CDLL] = None
@@ -108,11 +113,10 @@ def load() -> ctypes.CDLL:
         return _lib
     path = _build.LIB_PATH
     if os.environ.get("QMOE_NO_BUILD") != "1" and _build.is_stale():
-        try:
-            path = _build.build()
-        except Exception:
-            if not os.path.exists(path):
-                raise
+        # A failed rebuild is an error even when an older library exists: running a stale binary
+        # after a source edit would report results of code that is no longer there.  Set
+        # QMOE_NO_BUILD=1 to load whatever is built (boxes without nvcc).
+        path = _build.build()
     if not os.path.exists(path):
         raise ImportError(
             f"{path} is missing: build it with `python -m qmoe_b200.build` (needs nvcc). "

@@ -44,11 +44,27 @@ def _inputs() -> List[str]:
     return files
 
 
+STAMP_PATH = os.path.join(LIB_DIR, "build.stamp")
+
+
+def _digest() -> str:
+    """SHA-256 over the sources, headers and compiler flags the library is built from."""
+    import hashlib
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for f in _inputs():
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    return h.hexdigest()
+
+
 def is_stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+    """True when the library is missing or was built from other sources than the present ones
+    (content digest, so that copying the tree to another machine does not look like an edit)."""
+    if not os.path.exists(LIB_PATH) or not os.path.exists(STAMP_PATH):
         return True
-    t = os.path.getmtime(LIB_PATH)
-    return any(os.path.getmtime(f) > t for f in _inputs())
+    with open(STAMP_PATH) as f:
+        return f.read().strip() != _digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -83,6 +99,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
             "-Xcompiler", "-fPIC", "-o", tmp, *objs]
     subprocess.run(link, check=True)
     os.replace(tmp, LIB_PATH)
+    with open(STAMP_PATH, "w") as f:
+        f.write(_digest())
     return LIB_PATH
 
 

@@ -86,6 +86,18 @@ def read_sizes(path: str) -> Dict[str, int]:
     return torch.load(os.path.join(path, "sizes.pt"))
 
 
+def read_config(path: str) -> dict:
+    """``config.json`` of a checkpoint directory (the model configuration, sub1.py:232)."""
+    with open(os.path.join(path, "config.json")) as f:
+        return json.load(f)
+
+
+def read_nonexpert(path: str, device="cpu") -> Dict[str, torch.Tensor]:
+    """``noexp.pt``: the state dict of every non-expert parameter (router classifiers, attention,
+    embeddings), bf16, as the reference copies it into its model (sub1.py:284-292)."""
+    return torch.load(os.path.join(path, "noexp.pt"), map_location=torch.device(device))
+
+
 def layers_of_file(state: Dict[str, torch.Tensor]) -> Dict[str, List[int]]:
     """``{layer prefix: sorted expert indices}`` found in one expert file."""
     found: Dict[str, set] = {}

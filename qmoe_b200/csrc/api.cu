@@ -58,9 +58,31 @@ bool profile_begin(int device, cudaEvent_t **events) {
   return true;
 }
 
+std::mutex &setup_mutex() {
+  static std::mutex m;
+  return m;
+}
+
+int *tile_status_word(int device) {
+  static int *word[64] = {nullptr};
+  if (device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(setup_mutex());
+  if (word[device] == nullptr) {
+    int *p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+      cudaFree(p);
+      return nullptr;
+    }
+    word[device] = p;
+  }
+  return word[device];
+}
+
 int sm_count(int device) {
   static int cached[64] = {0};
   if (device < 0 || device >= 64) return 148;
+  std::lock_guard<std::mutex> lock(setup_mutex());
   if (cached[device] == 0) {
     int n = 0;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 148;
@@ -79,6 +101,8 @@ int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *co
                   uint8_t *sym, int32_t *status, int height, int width, int64_t n_codes, cudaStream_t stream);
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
 int set_tile_min_tokens(int tokens);
+int set_tile_wait_limit(uint32_t spins);
+int work_summary(const void *work, int max_slots, int d_model, int d_ff, int32_t *out, cudaStream_t stream);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
@@ -166,10 +190,11 @@ int get_sparse_table(const int32_t *dec_dev, int device, cudaStream_t stream, Sp
   return QMOE_OK;
 }
 
-static int release_tables(int device) {
+// dec == nullptr: every table of the device.
+static int release_tables(int device, const void *dec = nullptr) {
   std::lock_guard<std::mutex> lock(g_mutex);
   for (auto it = g_tables.begin(); it != g_tables.end();) {
-    if (it->first.first == device) {
+    if (it->first.first == device && (dec == nullptr || it->first.second == dec)) {
       cudaFree(it->second.entries);
       it = g_tables.erase(it);
     } else {
@@ -443,6 +468,15 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
   return moe_work_bytes(max_slots, d_model, d_ff);
 }
 
+int qmoe_moe_work_summary(const void *work_dev, int max_slots, int d_model, int d_ff, int32_t *out_host,
+                          int device, void *stream) {
+  QMOE_REQUIRE(work_dev != nullptr && out_host != nullptr, "null pointer");
+  QMOE_REQUIRE(max_slots >= 1 && d_model >= 1 && d_ff >= 1, "bad shape");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return work_summary(work_dev, max_slots, d_model, d_ff, out_host, as_stream(stream));
+}
+
 static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint16_t *codes_dev,
                              const int32_t *row_off_dev, const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
                              const qmoe_interleaved_store *ils, const int32_t *offsets_dev,
@@ -689,6 +723,27 @@ int qmoe_sub1_release(int device) {
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
   return release_tables(device);
+}
+
+int qmoe_sub1_forget(const int32_t *dec_dev, int device) {
+  QMOE_REQUIRE(dec_dev != nullptr, "null device pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return release_tables(device, dec_dev);
+}
+
+int qmoe_moe_set_tile_wait_limit(uint32_t spins) { return set_tile_wait_limit(spins); }
+
+int qmoe_moe_tile_timeouts(int device, int reset, int *count_out) {
+  QMOE_REQUIRE(count_out != nullptr, "null output pointer");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  int *word = tile_status_word(device);
+  if (word == nullptr) return cuda_fail(cudaGetLastError(), "tile status word");
+  QMOE_CUDA(cudaDeviceSynchronize());
+  QMOE_CUDA(cudaMemcpy(count_out, word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (reset) QMOE_CUDA(cudaMemset(word, 0, sizeof(int)));
+  return QMOE_OK;
 }
 
 }  // extern "C"

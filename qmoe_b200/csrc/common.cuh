@@ -5,6 +5,8 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "qmoe_sub1.h"
 
 namespace qmoe {
@@ -41,6 +43,15 @@ struct DeviceGuard {
 };
 
 int sm_count(int device);
+
+// One mutex for every "first call on a device" set-up step of the library (kernel attributes, the
+// SM count, the sticky status word): entry points may be called from several host threads.
+std::mutex &setup_mutex();
+
+// Sticky per-device status word of the tensor-core tile kernels: incremented (never cleared by a
+// launch) whenever a bounded wait gave up.  Allocated and zeroed on first use; read and optionally
+// reset through qmoe_moe_tile_timeouts().  nullptr if the allocation failed.
+int *tile_status_word(int device);
 
 // Event timing of the grouped launches (qmoe_profile_enable): returns true and four fresh events
 // when the next grouped call should be timed.

@@ -24,6 +24,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <type_traits>
+#include <vector>
 
 namespace qmoe {
 
@@ -648,6 +649,7 @@ static int ensure_smem_limits(int device) {
     set_error("device index %d out of range", device);
     return QMOE_ERR_INVALID_ARG;
   }
+  std::lock_guard<std::mutex> lock(setup_mutex());
   if (!done[device]) {
     int rc = set_smem_limits<false>();
     if (rc) return rc;
@@ -846,7 +848,7 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 // Work buffer layout: int header[16] | int4 items_wi[cap] | int4 items_wo[cap] | tile items of wi |
 // tile items of wo | warp items of wi | warp items of wo.
 // header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter,
-// [4] / [5] = tile items of wi / wo, [8] = timeouts seen by the tile kernels, [10] .. [13] = counts
+// [4] / [5] = tile items of wi / wo, [10] .. [13] = counts
 // and fetch counters of the warp items of wi and wo.
 //
 // Who takes which rows is decided here, on the device, from the number of (expert, token group)
@@ -1009,7 +1011,7 @@ int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, 
                            int max_slots, int *header, int4 *items_wi, int4 *items_wo, cudaStream_t stream);
 int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int4 *items, const int *n_items, int *status, int flags, int max_items, int device,
+                      const int4 *items, const int *n_items, int flags, int max_items, int device,
                       cudaStream_t stream);
 
 // Experts with at least this many tokens take the tile path (0 disables it).  The default is the
@@ -1048,6 +1050,36 @@ int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
   return 64 + (item_capacity(max_slots, d_ff) + item_capacity(max_slots, d_model) +
                2 * warp_item_capacity(max_slots)) * (int64_t)sizeof(int4) +
          tile_work_bytes(max_slots, d_model, d_ff);
+}
+
+// What the last qmoe_moe_grouped_ffn call with this work buffer planned (a host read-back for tests
+// and reports): out[0] / out[1] = per-thread items of wi / wo, out[2] / out[3] = row-per-warp items
+// of wi / wo, out[4] = wo items whose CTA also does the matrix's remainder rows one per warp,
+// out[5] = tokens decoded together, out[6] / out[7] = tile items of wi / wo.
+int work_summary(const void *work, int max_slots, int d_model, int d_ff, int32_t *out, cudaStream_t stream) {
+  int header[16];
+  QMOE_CUDA(cudaMemcpyAsync(header, work, sizeof(header), cudaMemcpyDeviceToHost, stream));
+  QMOE_CUDA(cudaStreamSynchronize(stream));
+  const int64_t cap_wi = item_capacity(max_slots, d_ff), cap_wo = item_capacity(max_slots, d_model);
+  int n_wo = header[2];
+  n_wo = n_wo < 0 ? 0 : (n_wo > cap_wo ? (int)cap_wo : n_wo);
+  std::vector<int4> items((size_t)n_wo);
+  if (n_wo > 0) {
+    const char *base = reinterpret_cast<const char *>(work) + 64 + cap_wi * sizeof(int4);
+    QMOE_CUDA(cudaMemcpyAsync(items.data(), base, sizeof(int4) * (size_t)n_wo, cudaMemcpyDeviceToHost, stream));
+    QMOE_CUDA(cudaStreamSynchronize(stream));
+  }
+  int flagged = 0;
+  for (const int4 &it : items) flagged += (it.w & 0x8000) ? 1 : 0;
+  out[0] = header[0];
+  out[1] = header[2];
+  out[2] = header[10];
+  out[3] = header[12];
+  out[4] = flagged;
+  out[5] = kMaxGroup;
+  out[6] = header[4];
+  out[7] = header[5];
+  return QMOE_OK;
 }
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
@@ -1120,7 +1152,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     if (tile_min > 0) {
       const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
       rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
-                             phase == 0 ? tile_wi : tile_wo, header + 4 + phase, header + 8, a.flags,
+                             phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
       if (rc) return rc;
     }

@@ -17,6 +17,8 @@
 #include "common.cuh"
 #include "sub1_walk.cuh"
 
+#include <atomic>
+
 namespace qmoe {
 
 constexpr int kTileM = 128;        // rows per CTA (== threads)
@@ -25,6 +27,15 @@ constexpr int kTileK = 128;        // matrix columns decoded per step
 constexpr int kTileChunks = kTileK / 8;
 constexpr uint32_t kTmemCols = 64; // fp32 accumulator columns (power of two >= 32)
 constexpr uint32_t kWaitLimit = 1u << 24;
+
+// Spins allowed to the waits that DECIDE whether a CTA gives up (tests lower it to make a wait run
+// out without anything hanging; 0 = kWaitLimit).  The clean-up waits before tensor memory is
+// released always get the full limit.
+static std::atomic<uint32_t> g_wait_limit{0};
+int set_tile_wait_limit(uint32_t spins) {
+  g_wait_limit.store(spins, std::memory_order_relaxed);
+  return QMOE_OK;
+}
 
 struct TileArgs {
   const uint32_t *tab;
@@ -37,8 +48,9 @@ struct TileArgs {
   long long x_stride, y_stride;
   const int4 *items;   // {matrix, first row, first token, tokens}
   const int *n_items;  // device scalar
-  int *status;         // device word: incremented when a bounded wait gives up
+  int *status;         // device word: incremented when a bounded wait gives up (sticky)
   int flags;
+  uint32_t wait_limit; // spins of the waits that decide to give up
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -88,8 +100,8 @@ __device__ __forceinline__ void mbar_init(uint32_t mbar_addr, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_addr), "r"(count) : "memory");
 }
 // Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint32_t mbar_addr, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitLimit; i++) {
+__device__ __forceinline__ bool mbar_wait(uint32_t mbar_addr, uint32_t parity, uint32_t limit = kWaitLimit) {
+  for (uint32_t i = 0; i < limit; i++) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -200,7 +212,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
           }
         }
         const uint32_t used = st ? uses1 : uses0;
-        if (used > 0 && !s_fail && !mbar_wait(st ? mbar1 : mbar0, (used - 1u) & 1u)) s_fail = 1;
+        if (used > 0 && !s_fail && !mbar_wait(st ? mbar1 : mbar0, (used - 1u) & 1u, a.wait_limit)) s_fail = 1;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < kTileChunks; c++)
@@ -313,11 +325,23 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
       // all MMAs of the item are complete when the last commit has arrived
       const int last = (n_windows - 1) & 1;
       const uint32_t used = last ? uses1 : uses0;
-      if (!s_fail && !mbar_wait(last ? mbar1 : mbar0, (used - 1u) & 1u)) s_fail = 1;
+      if (!s_fail && !mbar_wait(last ? mbar1 : mbar0, (used - 1u) & 1u, a.wait_limit)) s_fail = 1;
       tc_fence_after();
     }
     __syncthreads();
-    if (s_fail) break;  // uniform: read after the barrier
+    if (s_fail) {  // uniform: read after the barrier
+      // This CTA gives up.  The rows of this and of its remaining items are written as zeros so that
+      // what later stages read is defined; the sticky status word tells the host.
+      for (int rest = item; rest < n_items; rest += gridDim.x) {
+        const int4 ri = a.items[rest];
+        const qmoe_matrix_desc rd = a.descs[ri.x];
+        for (int i = tid; i < kTileM * ri.w; i += kTileThreads) {
+          const int r = ri.y + (i % kTileM), n = i / kTileM;
+          if (r < rd.height) a.y[(long long)(ri.z + n) * a.y_stride + r] = __float2bfloat16_rn(0.f);
+        }
+      }
+      break;
+    }
 
     if (decoder) {  // epilogue: row t of the accumulator -> y[token][row]
       const int row = it.y + t;
@@ -359,7 +383,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
 // ---- work list of the tile path ---------------------------------------------------------------------
 // Experts with at least `tile_min` tokens are cut into blocks of up to 64 tokens; every block becomes
 // ceil(height / 128) items per linear.  header[4] / header[5] receive the item counts of wi / wo,
-// header[8] is the timeout counter of the tile kernels (cleared here).
+// (timeouts are counted in the library's sticky per-device status word, not here).
 __global__ void __launch_bounds__(1024) k_build_tile_work(const int32_t *__restrict__ offsets, int n_experts,
                                                           int tile_min, int d_model, int d_ff, int cap_blocks,
                                                           int *header, int4 *items_wi, int4 *items_wo) {
@@ -387,7 +411,6 @@ __global__ void __launch_bounds__(1024) k_build_tile_work(const int32_t *__restr
     const int blocks = min(s_blocks, cap_blocks);
     header[4] = blocks * rb_wi;
     header[5] = blocks * rb_wo;
-    header[8] = 0;
   }
 }
 
@@ -409,7 +432,7 @@ int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, 
 // One linear (wi or wo) of every expert on the tile path.
 int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int4 *items, const int *n_items, int *status, int flags, int max_items, int device,
+                      const int4 *items, const int *n_items, int flags, int max_items, int device,
                       cudaStream_t stream) {
   TileArgs a{};
   a.tab = tab;
@@ -423,16 +446,21 @@ int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t 
   a.y_stride = y_stride;
   a.items = items;
   a.n_items = n_items;
-  a.status = status;
+  a.status = tile_status_word(device);
   a.flags = flags;
+  const uint32_t limit = g_wait_limit.load(std::memory_order_relaxed);
+  a.wait_limit = limit ? limit : kWaitLimit;
   int grid = 4 * sm_count(device);
   grid = grid > max_items ? max_items : grid;
   grid = grid < 1 ? 1 : grid;
   constexpr int kSmem = 2 * (kTileChunks * kTileM * 16) + 2 * (kTileChunks * kTileN * 16);
   static bool configured[64] = {false};
-  if (device >= 0 && device < 64 && !configured[device]) {
-    QMOE_CUDA(cudaFuncSetAttribute(k_tile_matmul, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    configured[device] = true;
+  if (device >= 0 && device < 64) {
+    std::lock_guard<std::mutex> lock(setup_mutex());
+    if (!configured[device]) {
+      QMOE_CUDA(cudaFuncSetAttribute(k_tile_matmul, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+      configured[device] = true;
+    }
   }
   QMOE_LAUNCH(k_tile_matmul, grid, kTileThreads, kSmem, stream, a);
   QMOE_CUDA(cudaGetLastError());

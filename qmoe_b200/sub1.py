@@ -151,6 +151,8 @@ class ExpertStore:
         self.descs = torch.from_numpy(raw).to(codes.device)
         self.device = codes.device
         self.dec = dec                                   # decoder table of these streams (None: the standard one)
+        if dec is not None and dec.is_cuda:
+            sub1_cuda.track_dec(dec)                     # the library's cache follows the tensor's life
         self.il_codes: Optional[torch.Tensor] = None     # lane-interleaved copy of the streams
         self.blk_base: Optional[torch.Tensor] = None     # int64, first 16-byte entry of every 32-row block
         if interleave and codes.is_cuda and d_model % 32 == 0 and d_ff % 32 == 0:
@@ -373,6 +375,37 @@ def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max
                                       xs.data_ptr(), hs.data_ptr(), ys.data_ptr(), work.data_ptr(),
                                       store.n_experts, max_slots, store.d_model, store.d_ff, dev.index, _s(dev)))
     return ys
+
+
+def work_plan(work: torch.Tensor, max_slots: int, d_model: int, d_ff: int) -> Dict[str, int]:
+    """What the last :func:`grouped_ffn` call that used ``work`` planned (synchronises): numbers of
+    row-per-thread and row-per-warp work items of wi and wo, how the remainder rows of a height that
+    is not a multiple of 1024 are covered, the tokens decoded together, and the tile items."""
+    out = (ctypes.c_int32 * 8)()
+    dev = work.device
+    _lib.check(_lib.load().qmoe_moe_work_summary(work.data_ptr(), int(max_slots), int(d_model), int(d_ff), out,
+                                                 dev.index, _s(dev)))
+    return {"wi_items": out[0], "wo_items": out[1], "wi_warp_items": out[2], "wo_warp_items": out[3],
+            "wo_items_with_remainder": out[4], "group_tokens": out[5], "tile_wi_items": out[6],
+            "tile_wo_items": out[7], "wo_remainder_rows": d_model % 1024 if d_model >= 1024 else 0,
+            "wo_remainder_units": out[4] + out[3]}
+
+
+def tile_timeouts(device, reset: bool = False) -> int:
+    """Number of tensor-core tile CTAs on ``device`` whose bounded wait gave up since the last reset
+    (0 in normal operation).  Synchronises the device: call it where the caller synchronises anyway.
+    A non-zero value means that grouped-FFN outputs produced since the last reset hold zeros for the
+    rows those CTAs did not finish."""
+    count = ctypes.c_int(0)
+    _lib.check(_lib.load().qmoe_moe_tile_timeouts(_dev_index(device), 1 if reset else 0, ctypes.byref(count)))
+    return int(count.value)
+
+
+def check_tile_status(device) -> None:
+    """Raise if a tile kernel on ``device`` reported a timeout (and clear the status)."""
+    n = tile_timeouts(device, reset=True)
+    if n:
+        raise _lib.QmoeError(_lib.ERR_TIMEOUT, f"{n} tensor-core tile CTA(s) gave up waiting; outputs are incomplete")
 
 
 def combine(ys: torch.Tensor, hidden: torch.Tensor, slot: torch.Tensor, prob: torch.Tensor) -> torch.Tensor:

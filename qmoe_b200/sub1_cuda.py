@@ -53,10 +53,38 @@ def _check_matrix(dec, w_comp, row_off, ter_minmax) -> Tuple[torch.device, int]:
     height = row_off.numel() - 1
     if height < 1 or ter_minmax.numel() != 2 * height:
         raise ValueError("row_off must have height + 1 entries and ter_minmax 2 * height")
+    track_dec(dec)
     return dev, height
 
 
 _MATVEC_CHECKED = {}
+_TRACKED_DEC = set()
+
+
+def track_dec(dec: torch.Tensor) -> None:
+    """Tie the library's cache for this decoder table to the life of the tensor.
+
+    The library keys its derived table by the address of ``dec``.  torch's allocator hands freed
+    addresses out again, so when ``dec`` is garbage collected the cached table (and the remembered
+    argument checks of :func:`sub1matvec`) for its address are dropped: a different table that
+    later lands on the same address is derived afresh.  Overwriting a table IN PLACE is not seen;
+    call ``qmoe_sub1_forget`` / ``qmoe_sub1_release`` after that."""
+    import weakref
+    ptr, index = dec.data_ptr(), dec.device.index
+    if (ptr, index) in _TRACKED_DEC:
+        return
+    _TRACKED_DEC.add((ptr, index))
+
+    def forget(ptr=ptr, index=index):
+        _TRACKED_DEC.discard((ptr, index))
+        for key in [k for k in _MATVEC_CHECKED if k[0] == ptr]:
+            del _MATVEC_CHECKED[key]
+        try:
+            _lib.load().qmoe_sub1_forget(ptr, index)
+        except Exception:  # interpreter shutdown
+            pass
+
+    weakref.finalize(dec, forget)
 
 
 def sub1matvec(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor,
@@ -135,6 +163,7 @@ def sub1decode(dec: torch.Tensor, w_comp: torch.Tensor, row_off: torch.Tensor, w
     of rows whose codes do not cover exactly ``width`` weights (a host synchronisation)."""
     _need(dec, "dec", torch.int32)
     dev = dec.device
+    track_dec(dec)
     _need(w_comp, "w_comp", (torch.int16, torch.uint16), dev)
     _need(row_off, "row_off", torch.int32, dev)
     height = row_off.numel() - 1

@@ -20,7 +20,16 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("QMOE_REFERENCE", "/root/reference")
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _reference_dir():
+    """``$QMOE_REFERENCE``, else a directory named ``reference`` beside this repository."""
+    env = os.environ.get("QMOE_REFERENCE")
+    return env if env else os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(_HERE))), "reference")
+
+
+REF = _reference_dir()
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "sub1_golden.npz")
 
 

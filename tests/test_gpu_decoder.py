@@ -11,6 +11,10 @@ pytestmark = pytest.mark.gpu
 
 
 def _dense_expert(store, m, dev):
+    """Dense weights of one matrix, decoded with this package's own ``sub1decode``.  That is sound
+    here only because the decoder is pinned elsewhere, bit for bit against the CPU oracle and the
+    reference's golden vectors (test_gpu_parity.py, test_gpu_configs.py); this file checks the stack
+    around the experts, not the decoding."""
     d = store.host_descs[m]
     w_comp, row_off, mm = store.matrix(m)
     sym = sub1_cuda.sub1decode(sub1.DEC(dev), w_comp.contiguous(), row_off.contiguous(), d.width).long()

@@ -114,7 +114,7 @@ def test_tensor_core_tile_path_for_heavily_loaded_experts(dev, small_layer):
     finally:
         _lib.load().qmoe_moe_set_tile_min_tokens(before)
     header = work[:64].view(torch.int32).cpu()
-    assert int(header[8]) == 0                       # no bounded wait gave up
+    assert sub1.tile_timeouts(dev) == 0              # no bounded wait gave up
     assert int(header[4]) == 5 * 3 and int(header[5]) == 5 * 1   # 2+1+1+1 token blocks x row blocks
     pos = 0
     for e, c in enumerate(counts):
@@ -245,6 +245,43 @@ def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
     want = (hidden.float() @ dense[1].t()).bfloat16()
     assert rel_err(ys, want) <= TOL
     _lib.check(_lib.load().qmoe_sub1_release(0))
+
+
+def test_tile_path_reports_a_wait_that_ran_out(dev, small_layer):
+    """Every wait of the tile kernel on an MMA-completion barrier is bounded.  With the bound lowered
+    to a single poll the first such wait gives up although nothing hangs: the CTA stops, writes
+    zeros for the rows it did not finish, and the library's sticky status word reports it until it
+    is read with reset.  (The clean-up waits before tensor memory is released keep the full bound.)"""
+    from qmoe_b200 import _lib
+    experts, store = small_layer
+    L = _lib.load()
+    counts = [0, 70, 0, 0, 0, 0, 0, 0]
+    n = sum(counts)
+    xs = synth.tokens(n, store.d_model, seed=12).to(dev)
+    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+    assert sub1.tile_timeouts(dev, reset=True) == 0
+    before = L.qmoe_moe_set_tile_min_tokens(16)
+    L.qmoe_moe_set_tile_wait_limit(1)
+    try:
+        ys = sub1.grouped_ffn(store, offsets, xs, n)
+        torch.cuda.synchronize()
+    finally:
+        L.qmoe_moe_set_tile_wait_limit(0)
+        L.qmoe_moe_set_tile_min_tokens(before)
+    assert torch.isfinite(ys.float()).all()
+    assert sub1.tile_timeouts(dev) > 0                     # sticky: still there on a second read
+    with pytest.raises(_lib.QmoeError):
+        sub1.check_tile_status(dev)                        # raises and clears
+    assert sub1.tile_timeouts(dev) == 0
+    # the same step with the default bound completes and matches the oracle
+    before = L.qmoe_moe_set_tile_min_tokens(16)
+    try:
+        ys = sub1.grouped_ffn(store, offsets, xs, n)
+        torch.cuda.synchronize()
+    finally:
+        L.qmoe_moe_set_tile_min_tokens(before)
+    assert sub1.tile_timeouts(dev) == 0
+    assert rel_err(ys, experts[1].oracle_ffn(xs.cpu())) <= TOL
 
 
 @pytest.mark.parametrize("n,capacity", [(1, 1024), (5, 1024), (32, 1024), (32, 2), (7, 0)])

@@ -96,15 +96,22 @@ def test_round_trip_reference_shapes(oracle_dict):
         assert 0.68 < bits < 0.70           # ~0.69 bit/weight at P(0)=0.90
 
 
-@pytest.mark.skipif(not os.path.exists("/root/reference/test.py"), reason="reference checkout absent")
-def test_against_live_reference(oracle_dict):
-    """Runs the reference's greedy()/decompress() (loaded with ast, executed unchanged) next to the
-    oracle on fresh random rows."""
+def _make_golden_module():
     import importlib.util
     spec = importlib.util.spec_from_file_location(
         "make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
     mg = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mg)
+    return mg
+
+
+def test_against_live_reference(oracle_dict):
+    """Runs the reference's greedy()/decompress() (loaded with ast, executed unchanged) next to the
+    oracle on fresh random rows.  Needs the reference checkout ($QMOE_REFERENCE, or a directory named
+    ``reference`` beside the repository); skipped where it is absent."""
+    mg = _make_golden_module()
+    if not os.path.exists(os.path.join(mg.REF, "test.py")):
+        pytest.skip("reference checkout absent (set QMOE_REFERENCE)")
     ns = mg.load_test_namespace()
     dec, trie = oracle_dict
     assert (ns["dec"].astype(np.int32) == dec).all()
