@@ -28,8 +28,8 @@ constexpr int kTileChunks = kTileK / 8;
 constexpr uint32_t kTmemCols = 64; // fp32 accumulator columns (power of two >= 32)
 constexpr uint32_t kWaitLimit = 1u << 24;
 
-// Spins allowed to the waits that DECIDE whether a CTA gives up (tests lower it to make a wait run
-// out without anything hanging; 0 = kWaitLimit).  The clean-up waits before tensor memory is
+// Bound of the waits that DECIDE whether a CTA gives up (tests lower it to 1, "do not poll at all",
+// to make a wait run out without anything hanging; 0 = kWaitLimit).  The clean-up waits before tensor memory is
 // released always get the full limit.
 static std::atomic<uint32_t> g_wait_limit{0};
 int set_tile_wait_limit(uint32_t spins) {
@@ -99,9 +99,10 @@ __device__ __forceinline__ void mma_commit(uint32_t mbar_addr) {
 __device__ __forceinline__ void mbar_init(uint32_t mbar_addr, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar_addr), "r"(count) : "memory");
 }
-// Bounded wait for the phase with the given parity; false if the limit ran out.
+// Bounded wait for the phase with the given parity: at most limit - 1 polls (each of which may itself
+// block for a short, hardware-defined time); false if they ran out.  A limit of 1 gives up at once.
 __device__ __forceinline__ bool mbar_wait(uint32_t mbar_addr, uint32_t parity, uint32_t limit = kWaitLimit) {
-  for (uint32_t i = 0; i < limit; i++) {
+  for (uint32_t i = 1; i < limit; i++) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
