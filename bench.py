@@ -56,18 +56,36 @@ def parse_args():
     p.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replay")
     p.add_argument("--skew", type=int, default=0,
                    help="skewed router: this many hot experts receive half of the tokens (config 3 uses 8)")
+    p.add_argument("--tokens-per-expert", type=int, default=0,
+                   help="router override: every expert receives exactly this many tokens (the token count becomes "
+                        "experts x this); 1 is the batch-1 case: every matrix is applied to one vector")
+    p.add_argument("--no-parity-check", action="store_true", help="skip the oracle check of sampled experts")
+    p.add_argument("--no-gpu-reference", action="store_true", help="skip the timing of the reference's own kernel")
+    p.add_argument("--min-seconds", type=float, default=1.0,
+                   help="the timed loop of --steps steps is repeated until this much time has been timed")
     p.add_argument("--kernel-times", action="store_true",
                    help="generate mode: also time the kernels of a decode step (torch profiler, eager launches) "
                         "and add their average durations to the JSON line")
-    p.add_argument("--mode", default="moe", choices=["moe", "layers", "generate"],
+    p.add_argument("--mode", default="moe", choices=["moe", "layers", "generate", "smem-ceiling"],
                    help="moe: the MoE-layer benchmark (default); layers: the reference's per-layer matvec "
-                        "benchmark (test.py --benchmark) on its six shapes")
+                        "benchmark (test.py --benchmark) on its six shapes; generate: end-to-end decoding; "
+                        "smem-ceiling: the grouped kernel on weights that stay in L2 (no HBM traffic)")
     return p.parse_args()
 
 
 def workload_dims(args):
     d_model, d_ff, experts, tokens = WORKLOADS[args.workload]
-    return d_model, d_ff, args.experts or experts, args.tokens or tokens
+    experts = args.experts or experts
+    tokens = experts * args.tokens_per_expert if args.tokens_per_expert > 0 else (args.tokens or tokens)
+    return d_model, d_ff, experts, tokens
+
+
+def forced_logits(n_tokens, n_experts):
+    """Router logits that send token t to expert t % n_experts with probability ~1."""
+    import torch
+    logits = torch.full((n_tokens, n_experts), -20.0)
+    logits[torch.arange(n_tokens), torch.arange(n_tokens) % n_experts] = 20.0
+    return logits
 
 
 # ---------------------------------------------------------------------------------------------
@@ -143,7 +161,7 @@ def measured_hbm_peak():
 def recorded_traffic_ratio():
     """DRAM bytes per algorithmic byte of the grouped kernel, from the committed ncu summary."""
     try:
-        with open(os.path.join(ROOT, "profiles", "k_matmul_grouped.traffic.json")) as f:
+        with open(os.path.join(ROOT, "profiles", "k_matmul_ring.traffic.json")) as f:
             return float(json.load(f)["dram_bytes_per_algorithmic_byte"])
     except Exception:
         return None
@@ -245,11 +263,140 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # this implementation
 # ---------------------------------------------------------------------------------------------
+def parity_leg(world, rank, dev, out, index, prob, hidden_all, d_model, d_ff, e_local):
+    """After the timed regions: outputs of the tokens of a few of rank 0's experts against the CPU
+    oracle (the experts are regenerated from the seed and encoded by the oracle's own encoder).
+    ``out`` / ``index`` / ``prob``: this rank's layer output, expert choice and router probability."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle as O
+    if world > 1:
+        outs = [torch.empty_like(out) for _ in range(world)]
+        idxs = [torch.empty_like(index) for _ in range(world)]
+        prbs = [torch.empty_like(prob) for _ in range(world)]
+        dist.all_gather(outs, out.contiguous())
+        dist.all_gather(idxs, index.contiguous())
+        dist.all_gather(prbs, prob.contiguous())
+        out, index, prob = torch.cat(outs), torch.cat(idxs), torch.cat(prbs)
+    if rank != 0:
+        return None
+    out, index, prob = out.float().cpu(), index.cpu().long(), prob.float().cpu()
+    counts = torch.bincount(index, minlength=e_local)[:e_local]
+    order = torch.argsort(counts, descending=True).tolist()
+    chosen = order[:1] + [e for e in order if counts[e] == 2][:1] + [e for e in order if counts[e] == 1][:2]
+    chosen = [e for e in dict.fromkeys(chosen) if counts[e] > 0]
+    O.use_all_cores()
+    dec, _ = O.build_dictionary()
+    worst, n_tok = 0.0, 0
+    for e in chosen:
+        wi, wo = cpu_sample_experts(d_model, d_ff, [e])[0]
+        tok = torch.nonzero(index == e).reshape(-1)
+        x_bits = hidden_all[tok].contiguous().view(torch.int16).numpy().view(np.uint16)
+        y = O.expert_ffn(dec, wi, wo, x_bits, d_model, d_ff)
+        ref = torch.from_numpy(y.view(np.int16)).view(torch.bfloat16).float() * prob[tok].unsqueeze(1)
+        ref = ref.bfloat16().float()
+        err = float((out[tok] - ref).abs().max() / max(float(ref.abs().max()), 1e-12))
+        worst = max(worst, err)
+        n_tok += len(tok)
+    return {"experts": chosen, "tokens": n_tok, "max_rel_err": worst, "tolerance": 1e-2,
+            "against": "CPU oracle (decode-then-matmul FFN, fp32 accumulation, bf16 hidden activation) x router "
+                       "probability; error = max|out - ref| / max|ref| per expert"}
+
+
+def gpu_reference_leg(store, dev, d_model, d_ff, counts, hidden_dev, ours_tokens_per_s):
+    """The reference's own kernel (built unmodified into oracle/_ref), driven as the reference drives
+    it -- per active expert, per token, zero y, sub1matvec, ReLU, sub1matvec (sub1.py:139-142,315-317)
+    -- on a bounded sample of this rank's experts."""
+    import torch
+    from qmoe_b200 import sub1
+    if (d_ff, d_model) not in LAYER_SHAPES or (d_model, d_ff) not in LAYER_SHAPES:
+        return {"unavailable": "the reference kernel handles its six hard-coded shapes only (sub1_cuda_kernel.cu:82-87)"}
+    if store.codes is None:
+        return {"unavailable": "the store dropped its row-by-row streams"}
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    try:
+        import build_ref
+        ref = build_ref.load()
+    except Exception as exc:
+        return {"unavailable": f"oracle/_ref could not be loaded: {exc}"}
+    if ref is None:
+        return {"unavailable": "oracle/_ref not built (python oracle/build_ref.py, needs the reference checkout)"}
+    dec = sub1.DEC(dev)
+    sample = [(e, c) for e, c in enumerate(counts) if c > 0][:16]
+    mats = [[tuple(t.contiguous() for t in store.matrix(2 * e + w)) for w in (0, 1)] for e, _ in sample]
+    n_tok = sum(c for _, c in sample)
+
+    def run():
+        pos = 0
+        for (e, c), (wi, wo) in zip(sample, mats):
+            x = hidden_dev[pos:pos + c]
+            h = torch.zeros((c, d_ff), dtype=torch.bfloat16, device=dev)
+            for i in range(c):
+                ref.sub1matvec(dec, wi[0], wi[1], wi[2], x[i], h[i])
+            h = torch.relu(h)
+            y = torch.zeros((c, d_model), dtype=torch.bfloat16, device=dev)
+            for i in range(c):
+                ref.sub1matvec(dec, wo[0], wo[1], wo[2], h[i], y[i])
+            pos += c
+
+    for _ in range(3):
+        run()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    reps = 0
+    t0 = time.perf_counter()
+    a.record()
+    while reps < 200 and (reps < 5 or time.perf_counter() - t0 < 0.5):
+        run()
+        reps += 1
+    b.record()
+    torch.cuda.synchronize()
+    value = n_tok * reps / (a.elapsed_time(b) * 1e-3)
+    return {"value": value, "unit": UNIT, "kind": "the reference's CUDA kernel, unmodified, built for sm_100",
+            "sample": f"{len(sample)} active experts of this layer with their {n_tok} routed tokens, {reps} repeats; one "
+                      "sub1matvec launch per token and linear plus torch zeros / relu, CUDA events, no host "
+                      "synchronisation between calls; every expert costs the same, so tokens/s of the sample is "
+                      "tokens/s of the layer",
+            "ours_over_reference": ours_tokens_per_s / value if value > 0 else None}
+
+
+def l2_resident_rate(dev, d_model, d_ff, lib):
+    """The grouped kernel on ONE expert's weights with hundreds of token pairs: every SM streams the
+    same 2.3 MB, which stay in L2, so the launch shows what the SMs sustain when HBM is out of the
+    picture (the kernel's on-chip ceiling).  Returns GB/s of algorithmic bytes per launch."""
+    import ctypes
+    import torch
+    from qmoe_b200 import _lib, sub1, synth
+    store = synth.build_store(d_model, d_ff, [0, 1], SEED, dev)
+    n = 2 * 4 * 148                                    # pairs of tokens: about eight rounds of wi items
+    xs = synth.tokens(n, d_model, SEED + 3).to(dev)
+    offsets = torch.tensor([0, n, n], dtype=torch.int32, device=dev)
+    before = lib.qmoe_moe_set_tile_min_tokens(0)
+    try:
+        for _ in range(3):
+            sub1.grouped_ffn(store, offsets, xs, n)
+        lib.qmoe_profile_enable(1)
+        for _ in range(10):
+            sub1.grouped_ffn(store, offsets, xs, n)
+        lib.qmoe_profile_enable(0)
+    finally:
+        lib.qmoe_moe_set_tile_min_tokens(before)
+    wi_ms, wo_ms, calls = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
+    _lib.check(lib.qmoe_profile_read(ctypes.byref(wi_ms), ctypes.byref(wo_ms), ctypes.byref(calls)))
+    groups = n // 2
+    alg = groups * (store.matrix_bytes(0) + store.matrix_bytes(1)) + 2 * 2 * n * (d_model + d_ff)
+    ms = (wi_ms.value + wo_ms.value) / max(calls.value, 1)
+    codes = groups * (store.host_descs[0].n_codes + store.host_descs[1].n_codes)
+    return alg / (ms * 1e-3) / 1e9, codes / (ms * 1e-3), groups
+
+
 def run_ours(args):
+    import ctypes
     import torch
     import torch.distributed as dist
     from qmoe_b200 import _lib, sub1, synth
-    from qmoe_b200.ep import ExpertParallelMLP
+    from qmoe_b200.ep import ExpertParallelMLP, default_pair_capacity
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -277,18 +424,30 @@ def run_ours(args):
     hidden_host = hidden_all[rank * t_local:(rank + 1) * t_local].contiguous().pin_memory()
     out_host = torch.empty_like(hidden_host).pin_memory()
     hidden_dev = hidden_host.to(dev)
-    skew_logits_all = skew_logits = None
-    if args.skew > 0:   # logits given directly: N(0,1) plus a large bias that sends half the tokens to the hot experts
-        skew_logits_all = synth.router_logits(n_tokens, n_experts, SEED, hot_experts=args.skew, hot_fraction=0.5)
+    # router logits given directly (skewed router, or exactly k tokens per expert); otherwise the
+    # layer's own classifier computes them from the hidden states
+    given_all = None
+    if args.tokens_per_expert > 0:
+        given_all = forced_logits(n_tokens, n_experts)
+        router = f"every expert receives exactly {args.tokens_per_expert} token(s)"
+    elif args.skew > 0:   # N(0,1) plus a large bias that sends half the tokens to the hot experts
+        given_all = synth.router_logits(n_tokens, n_experts, SEED, hot_experts=args.skew, hot_fraction=0.5)
         perm = torch.randperm(n_tokens, generator=torch.Generator().manual_seed(SEED))
-        skew_logits_all = skew_logits_all[perm].contiguous()      # spread the hot tokens over the ranks
-        skew_logits = skew_logits_all[rank * t_local:(rank + 1) * t_local].contiguous().to(dev)
+        given_all = given_all[perm].contiguous()                # spread the hot tokens over the ranks
+        router = f"skewed: {args.skew} experts get half of the tokens"
+    else:
+        router = "uniform top-1"
+    given = None if given_all is None else given_all[rank * t_local:(rank + 1) * t_local].contiguous().to(dev)
     if world > 1:
         layer = ExpertParallelMLP(router_weight, store, n_experts, expert_capacity=1024)
-        step = lambda h: layer(h, router_logits=skew_logits, seq_len=t_local)[0]  # noqa: E731
+        full = lambda h, lg: layer(h, router_logits=lg, seq_len=t_local)  # noqa: E731
     else:
         layer = sub1.FasterMLP(router_weight, store, expert_capacity=1024)
-        step = lambda h: layer(h.unsqueeze(0), router_logits=skew_logits)[0].squeeze(0)  # noqa: E731
+
+        def full(h, lg):
+            o, (rl, ix) = layer(h.unsqueeze(0), router_logits=None if lg is None else lg.unsqueeze(0))
+            return o.squeeze(0), (rl.squeeze(0), ix.squeeze(0))
+    step = lambda h: full(h, given)[0]  # noqa: E731
 
     def barrier():
         if world > 1:
@@ -311,19 +470,33 @@ def run_ours(args):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    def timed_repeats(fn, steps, finish=None):
+        """The loop of `steps` steps, repeated until args.min_seconds have been timed (rank 0
+        decides, every rank runs the same repeats); returns the per-repeat milliseconds."""
+        out, total = [], 0.0
+        go = torch.ones(1, device=dev)
+        while float(go.item()) > 0:
+            ms = timed(fn, steps, finish)
+            out.append(ms)
+            total += ms
+            go.fill_(1.0 if (total < args.min_seconds * 1e3 and len(out) < 200) else 0.0)
+            if world > 1:
+                dist.broadcast(go, 0)
+        return out
+
     # warm-up (also builds the per-device sparse table and sizes the allocator's pools)
     for _ in range(max(args.warmup, 3)):
         step(hidden_dev)
     barrier()
 
-    # eager pass: kernel durations (CUDA events around the two grouped launches, on their stream) and
-    # the launch count; the same kernels are then replayed from a CUDA graph for the headline number
+    # eager pass: kernel durations (CUDA events around the grouped launches of wi and of wo, on their
+    # stream) and the launch count; the same kernels are then replayed from a CUDA graph for the
+    # headline number
     launches0 = lib.qmoe_launch_count()
     lib.qmoe_profile_enable(1)
     ms_eager = timed(lambda: step(hidden_dev), args.steps)
     lib.qmoe_profile_enable(0)
     launches = (lib.qmoe_launch_count() - launches0) // max(args.steps, 1)
-    import ctypes
     wi_ms, wo_ms, n_calls = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
     _lib.check(lib.qmoe_profile_read(ctypes.byref(wi_ms), ctypes.byref(wo_ms), ctypes.byref(n_calls)))
 
@@ -363,7 +536,9 @@ def run_ours(args):
         if world > 1:
             dist.broadcast(go, 0)
     barrier()
-    ms_total = timed(run, args.steps)
+    reps = timed_repeats(run, args.steps)
+    ms_sorted = sorted(reps)
+    ms_total = ms_sorted[len(ms_sorted) // 2]               # the median repeat is the reported one
 
     # end to end: pinned host input -> device -> layer -> pinned host output, every step.  With the
     # step in a graph the copies of neighbouring steps overlap its execution (PipelinedStep).
@@ -382,13 +557,33 @@ def run_ours(args):
         e2e_step()
     if finish is not None:
         finish()
-    ms_e2e = timed(e2e_step, args.steps, finish)
+    e2e_reps = sorted(timed_repeats(e2e_step, args.steps, finish))
+    ms_e2e = e2e_reps[len(e2e_reps) // 2]
     clocks = sampler.stop() if rank == 0 else None
 
-    # algorithmic bytes of the grouped kernel on rank 0: matrices of experts that received tokens
-    logits = hidden_all.to(dev).float() @ router_weight.to(dev).t() if skew_logits_all is None else skew_logits_all.to(dev)
-    choice, _ = sub1.route_top1(logits.contiguous())
-    counts = torch.bincount(choice.long(), minlength=n_experts)[rank * e_local:(rank + 1) * e_local].cpu().tolist()
+    # status words of the timed steps: tile kernels that gave up, tokens that did not fit the exchange
+    tile_timeouts = sub1.tile_timeouts(dev, reset=True)
+    overflow = layer.overflow_count(reset=True) if world > 1 else 0
+    status = torch.tensor([tile_timeouts, overflow], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.SUM)
+    tile_timeouts, overflow = (int(v) for v in status.tolist())
+
+    # one more eager step whose output is checked: expert choice, router probability, layer output
+    out_chk, (rl_chk, index_chk) = full(hidden_dev, given)
+    _, prob_chk = sub1.route_top1(rl_chk.reshape(t_local, n_experts).float().contiguous())
+    parity = None
+    if not args.no_parity_check:
+        parity = parity_leg(world, rank, dev, out_chk, index_chk.reshape(-1).to(torch.int32), prob_chk, hidden_all,
+                            d_model, d_ff, e_local)
+
+    # algorithmic bytes of the grouped kernels on rank 0: matrices of experts that received tokens
+    idx_all = index_chk.reshape(-1).to(torch.int64)
+    if world > 1:
+        parts = [torch.empty_like(idx_all) for _ in range(world)]
+        dist.all_gather(parts, idx_all.contiguous())
+        idx_all = torch.cat(parts)
+    counts = torch.bincount(idx_all, minlength=n_experts)[rank * e_local:(rank + 1) * e_local].cpu().tolist()
     bytes_wi = bytes_wo = 0
     active = 0
     for e, c in enumerate(counts):
@@ -400,20 +595,26 @@ def run_ours(args):
     if rank == 0:
         peak, peak_kind = measured_hbm_peak()
         calls = max(n_calls.value, 1)
-        kernel_ms = (wi_ms.value + wo_ms.value) / (2 * calls)          # average launch of k_matmul_grouped
+        kernel_ms = (wi_ms.value + wo_ms.value) / (2 * calls)          # average grouped launch (wi, wo)
         alg_bytes = (bytes_wi + bytes_wo) / 2                          # average algorithmic bytes per launch
         achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9 if kernel_ms > 0 else 0.0
         ratio = recorded_traffic_ratio()
+        value = n_tokens * args.steps / (ms_total * 1e-3)
         line = {
-            "metric": METRIC, "value": n_tokens * args.steps / (ms_total * 1e-3), "unit": UNIT,
+            "metric": METRIC, "value": value, "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded ternary experts P(0)=0.90 packed by the GPU encoder; N(0,1) tokens; random router)",
+            "ms_per_step_repeats": {"repeats": len(reps), "median": ms_total / args.steps,
+                                    "min": ms_sorted[0] / args.steps, "max": ms_sorted[-1] / args.steps,
+                                    "timed_seconds": sum(reps) * 1e-3,
+                                    "note": f"the loop of {args.steps} steps repeated until {args.min_seconds} s were "
+                                            "timed; value and ms_per_step are the median repeat"},
             "config": {
                 "workload": args.workload, "d_model": d_model, "d_ff": d_ff, "experts": n_experts,
                 "tokens": n_tokens, "parallelism": f"ep{world}", "experts_per_gpu": e_local,
-                "router": f"skewed: {args.skew} experts get half of the tokens" if args.skew else "uniform top-1",
+                "router": router,
                 "max_tokens_per_expert_rank0": max(counts) if counts else 0,
                 "compressed_bytes_per_gpu": store.compressed_bytes, "active_experts_rank0": active,
                 "l2": f"inputs larger than L2 ({(bytes_wi + bytes_wo) / 1e6:.0f} MB of compressed experts "
@@ -421,19 +622,54 @@ def run_ours(args):
                 "setup_s": round(setup_s, 1),
                 "execution": "cuda-graph replay of the step" if gstep is not None else "eager launches",
                 "eager_ms_per_step": ms_eager / args.steps,
+                "pair_capacity": default_pair_capacity(t_local, world) if world > 1 else None,
             },
             "e2e": {"value": n_tokens * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": n_tokens * d_model * 2, "d2h_bytes_per_step": n_tokens * d_model * 2},
             "gpu_launches": int(launches),
             "roofline": {
-                "kernel": "k_matmul_grouped (wi and wo launches)", "bound": "hbm", "achieved": achieved,
+                "kernel": "k_matmul_ring + k_matmul_grouped_warp (the grouped launches of wi and of wo)",
+                "bound": "hbm", "achieved": achieved,
                 "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                 "algorithmic_bytes_per_launch": alg_bytes, "ms_per_launch": kernel_ms,
                 "wi_ms": wi_ms.value / calls, "wo_ms": wo_ms.value / calls,
                 "traffic": None if ratio is None else ratio * alg_bytes,
+                "timed_in": "the eager pass before the graph capture (CUDA events around the launches on their "
+                            "stream); value and e2e come from the graph replay of the same kernels",
             },
+            "status": {"tile_timeouts": tile_timeouts, "exchange_overflow_tokens": overflow},
+            "parity_check": parity,
             "clocks": clocks,
         }
+        if world == 1 and args.tokens_per_expert == 0 and args.experts == 0 and args.workload == "switch-c-2048":
+            # the batch-1 figure: the same layer with exactly one token per expert (every one of the
+            # 2048 experts active, each matrix applied to one vector), eager, event-timed launches
+            lg1 = forced_logits(n_experts, n_experts).to(dev)
+            h1 = synth.tokens(n_experts, d_model, SEED + 9).to(dev)
+            for _ in range(2):
+                full(h1, lg1)
+            lib.qmoe_profile_enable(1)
+            for _ in range(5):
+                full(h1, lg1)
+            lib.qmoe_profile_enable(0)
+            _lib.check(lib.qmoe_profile_read(ctypes.byref(wi_ms), ctypes.byref(wo_ms), ctypes.byref(n_calls)))
+            b1 = sum(store.matrix_bytes(m) for m in range(2 * n_experts)) / 2 + 2 * n_experts * (d_model + d_ff)
+            ms1 = (wi_ms.value + wo_ms.value) / (2 * max(n_calls.value, 1))
+            line["roofline_batch1"] = {
+                "what": "one token per expert, all 2048 experts active: every matrix of the layer applied to one "
+                        "vector in one grouped launch per linear",
+                "bound": "hbm", "achieved": b1 / (ms1 * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                "frac": b1 / (ms1 * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": b1, "ms_per_launch": ms1}
+        if world == 1:
+            gbs, codes_s, groups = l2_resident_rate(dev, d_model, d_ff, lib)
+            sm_hz = (clocks or {}).get("sm_mhz") or 1965.0
+            line["roofline_smem"] = {
+                "bound": "smem", "achieved": achieved, "peak": gbs, "unit": "GB/s", "frac": achieved / gbs if gbs else None,
+                "what": f"peak = the same kernels on ONE expert's matrices with {groups} token pairs: the weights stay "
+                        "in L2, no HBM traffic, so this is what the SMs' shared-memory and issue pipes sustain",
+                "codes_per_sm_per_clock_at_peak": codes_s / (148 * sm_hz * 1e6)}
+        if world == 1 and not args.no_gpu_reference:
+            line["gpu_reference"] = gpu_reference_leg(store, dev, d_model, d_ff, counts, hidden_dev, value)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args, d_model, d_ff, n_experts)
         print(json.dumps(line), flush=True)

@@ -153,6 +153,11 @@ int qmoe_moe_route(const float *logits_dev, int32_t *choice_dev, void *prob_dev,
 int qmoe_moe_rank(const int32_t *choice_dev, int32_t *bucket_dev, int32_t *rank_dev, int32_t *counts_dev,
                   int n_tokens, int n_buckets, int seq_len, int capacity, int device, void *stream);
 
+/* The capacity rule alone, one launch: expert_dev[t] = choice_dev[t] if kept, else -1 (must not
+ * alias choice_dev). */
+int qmoe_moe_keep(const int32_t *choice_dev, int32_t *expert_dev, int n_tokens, int n_experts, int seq_len,
+                  int capacity, int device, void *stream);
+
 /* offsets[0..n] = exclusive prefix sums of counts[0..n) (offsets has n+1 entries). */
 int qmoe_moe_scan(const int32_t *counts_dev, int32_t *offsets_dev, int n, int device, void *stream);
 
@@ -260,6 +265,45 @@ int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *cod
                                      const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,
                                      void *work_dev, int n_experts, int max_slots, int d_model, int d_ff,
                                      int device, void *stream);
+
+/* qmoe_moe_grouped_ffn(_interleaved) with row lists instead of sorted copies: token (slot) s reads
+ * its input from row x_rows_dev[s] of xs_dev (rows xs_stride elements apart) and its result goes to
+ * row y_rows_dev[s] of ys_dev (rows ys_stride apart); NULL lists mean s itself.  hs_dev stays
+ * bf16[max_slots, d_ff] indexed by slot.  store may be NULL (row-by-row streams).  With this the
+ * layer needs no permute / un-permute pass over its activations. */
+int qmoe_moe_grouped_ffn_rows(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                              const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
+                              const qmoe_interleaved_store *store, const int32_t *offsets_dev, const void *xs_dev,
+                              int64_t xs_stride, const int32_t *x_rows_dev, void *hs_dev, void *ys_dev,
+                              int64_t ys_stride, const int32_t *y_rows_dev, void *work_dev, int n_experts,
+                              int max_slots, int d_model, int d_ff, int device, void *stream);
+
+/* Dispatch metadata of the expert-parallel layer (qmoe_b200/ep.py); the reference only moves whole
+ * activations between GPUs (sub1.py:307-309,320) and loops over experts on the host (:315-317).
+ *
+ * qmoe_moe_ep_dispatch, two launches: (1) the router's capacity rule on the global expert choice
+ * (as qmoe_moe_rank: expert_dev[t] = choice or -1), the owning rank dest_dev[t] = expert /
+ * (n_experts / n_ranks), and the trailers of all n_ranks * pair_capacity exchange slots reset to -1;
+ * (2) per token: its stable rank among the kept tokens with the same destination, its slot
+ * dest * pair_capacity + rank (slot_dev[t]), the copy of its row into send_dev[slot] (rows of
+ * d_model + 8 bf16: the row, then a 16-byte trailer whose first int32 is the expert's index on its
+ * rank).  A token whose rank does not fit pair_capacity is not sent: slot -1 -- it passes through
+ * the layer scaled by its router probability, like a token dropped by the capacity rule -- and
+ * *overflow_dev is incremented (the caller zeroes it once and reads it at its own sync points).
+ *
+ * qmoe_moe_plan, one launch: buckets rows into n_buckets groups, stable in row order.  The bucket
+ * of row i is the int32 at element d_model of row i of rows_dev (rows row_stride elements apart:
+ * the trailer above) or, with rows_dev NULL, bucket_dev[i]; values outside [0, n_buckets) mean
+ * "no row".  offsets_dev int32[n_buckets + 1]: exclusive prefix sums of the bucket sizes;
+ * slot_of_row_dev[i] = offsets[bucket] + rank (or -1); row_of_slot_dev[slot] = i (entries at and
+ * beyond offsets[n_buckets] are left untouched).  At most 8192 buckets. */
+int qmoe_moe_ep_dispatch(const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
+                         int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *send_dev,
+                         int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks, int seq_len,
+                         int expert_capacity, int pair_capacity, int d_model, int device, void *stream);
+int qmoe_moe_plan(const void *rows_dev, int64_t row_stride, int d_model, const int32_t *bucket_dev, int n_rows,
+                  int n_buckets, int32_t *offsets_dev, int32_t *slot_of_row_dev, int32_t *row_of_slot_dev,
+                  int device, void *stream);
 
 /* out[token] = bf16(prob[token] * (slot >= 0 ? ys[slot] : hidden[token])): the scatter back to
  * token order, the pass-through of dropped tokens and the router-probability scaling of

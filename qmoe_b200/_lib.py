@@ -77,6 +77,7 @@ SIGNATURES = {
     "qmoe_synth_ternary": (_I, [_P, _L, _U64, _U64, ctypes.c_float, _I, _P]),
     "qmoe_moe_route": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "qmoe_moe_rank": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_keep": (_I, [_P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_scan": (_I, [_P, _P, _I, _I, _P]),
     "qmoe_moe_permute": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _L, _L, _I, _P]),
     "qmoe_moe_unpermute": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _P]),
@@ -85,6 +86,9 @@ SIGNATURES = {
     "qmoe_moe_work_summary": (_I, [_P, _P, _I, _P]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_grouped_ffn_rows": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_ep_dispatch": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_plan": (_I, [_P, _L, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
     "qmoe_moe_ring_prepare": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P, _I, _P]),
     "qmoe_moe_ring_plan_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P]),
     "qmoe_moe_ring_count": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _P]),

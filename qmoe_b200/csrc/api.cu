@@ -106,8 +106,17 @@ int work_summary(const void *work, int32_t *out, cudaStream_t stream);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
-                       void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
+                       int64_t xs_stride, const int32_t *x_rows, void *hs, void *ys, int64_t ys_stride,
+                       const int32_t *y_rows, void *work, int n_experts, int max_slots, int d_model, int d_ff,
                        int device, cudaStream_t stream);
+int launch_keep(const int32_t *choice, int32_t *expert, int n_tokens, int n_experts, int seq_len, int capacity,
+                cudaStream_t stream);
+int launch_ep_dispatch(const int32_t *choice, const void *hidden, int64_t hidden_stride, int32_t *expert,
+                       int32_t *dest, int32_t *slot, void *send, int *overflow, int n_tokens, int n_experts,
+                       int local_experts, int seq_len, int capacity, int n_ranks, int cap, int d_model,
+                       cudaStream_t stream);
+int launch_ep_plan(const void *rows, int64_t row_stride, int d_model, const int32_t *meta, int n_rows, int n_buckets,
+                   int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, cudaStream_t stream);
 int launch_combine_add(const void *ys, const void *hidden, const int32_t *slot, const void *prob,
                        const void *residual, void *out, int n_tokens, int d_model, cudaStream_t stream);
 int launch_route_small(const float *logits, const void *hidden, int n_tokens, int n_experts, int d_model,
@@ -436,6 +445,18 @@ int qmoe_moe_rank(const int32_t *choice_dev, int32_t *bucket_dev, int32_t *rank_
                      as_stream(stream));
 }
 
+int qmoe_moe_keep(const int32_t *choice_dev, int32_t *expert_dev, int n_tokens, int n_experts, int seq_len,
+                  int capacity, int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && n_experts >= 1, "bad shape");
+  if (n_tokens == 0) return QMOE_OK;
+  QMOE_REQUIRE(choice_dev && expert_dev && choice_dev != expert_dev, "null or aliased device pointer");
+  QMOE_REQUIRE(seq_len >= 1 && n_tokens % seq_len == 0, "n_tokens must be a multiple of seq_len");
+  QMOE_REQUIRE(capacity >= 0, "negative capacity");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_keep(choice_dev, expert_dev, n_tokens, n_experts, seq_len, capacity, as_stream(stream));
+}
+
 int qmoe_moe_scan(const int32_t *counts_dev, int32_t *offsets_dev, int n, int device, void *stream) {
   QMOE_REQUIRE(counts_dev && offsets_dev && n >= 1, "bad arguments");
   DeviceGuard guard(device);
@@ -485,8 +506,9 @@ int qmoe_moe_work_summary(const void *work_dev, int32_t *out_host, int device, v
 static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint16_t *codes_dev,
                              const int32_t *row_off_dev, const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
                              const qmoe_interleaved_store *ils, const int32_t *offsets_dev,
-                             const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
-                             int max_slots, int d_model, int d_ff, int device, void *stream) {
+                             const void *xs_dev, int64_t xs_stride, const int32_t *x_rows_dev, void *hs_dev,
+                             void *ys_dev, int64_t ys_stride, const int32_t *y_rows_dev, void *work_dev,
+                             int n_experts, int max_slots, int d_model, int d_ff, int device, void *stream) {
   if (!(dec_dev && (codes_dev || ils) && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev)) {
     set_error("%s: null device pointer", fn);
     return QMOE_ERR_INVALID_ARG;
@@ -512,6 +534,10 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     set_error("%s: null activation pointer", fn);
     return QMOE_ERR_INVALID_ARG;
   }
+  if (xs_stride < d_model || ys_stride < d_model) {
+    set_error("%s: row stride smaller than d_model", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
   if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 ||
       (ils && ((reinterpret_cast<uintptr_t>(ils->codes) | reinterpret_cast<uintptr_t>(ils->ring_table)) & 15u) != 0)) {
     set_error("%s: code stores must be 16-byte aligned", fn);
@@ -523,8 +549,8 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
   int rc = get_sparse_table(dec_dev, device, as_stream(stream), &tab);
   if (rc) return rc;
   return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, ils,
-                            offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff,
-                            device, as_stream(stream));
+                            offsets_dev, xs_dev, xs_stride, x_rows_dev, hs_dev, ys_dev, ys_stride, y_rows_dev,
+                            work_dev, n_experts, max_slots, d_model, d_ff, device, as_stream(stream));
 }
 
 int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
@@ -532,8 +558,8 @@ int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, cons
                          const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
                          int max_slots, int d_model, int d_ff, int device, void *stream) {
   return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, nullptr,
-                           offsets_dev, xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff,
-                           device, stream);
+                           offsets_dev, xs_dev, d_model, nullptr, hs_dev, ys_dev, d_model, nullptr, work_dev,
+                           n_experts, max_slots, d_model, d_ff, device, stream);
 }
 
 int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
@@ -544,7 +570,60 @@ int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *cod
                                      int device, void *stream) {
   QMOE_REQUIRE(store != nullptr, "null interleaved store");
   return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, store, offsets_dev,
-                           xs_dev, hs_dev, ys_dev, work_dev, n_experts, max_slots, d_model, d_ff, device, stream);
+                           xs_dev, d_model, nullptr, hs_dev, ys_dev, d_model, nullptr, work_dev, n_experts,
+                           max_slots, d_model, d_ff, device, stream);
+}
+
+int qmoe_moe_grouped_ffn_rows(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                              const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
+                              const qmoe_interleaved_store *store, const int32_t *offsets_dev, const void *xs_dev,
+                              int64_t xs_stride, const int32_t *x_rows_dev, void *hs_dev, void *ys_dev,
+                              int64_t ys_stride, const int32_t *y_rows_dev, void *work_dev, int n_experts,
+                              int max_slots, int d_model, int d_ff, int device, void *stream) {
+  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, store, offsets_dev,
+                           xs_dev, xs_stride, x_rows_dev, hs_dev, ys_dev, ys_stride, y_rows_dev, work_dev, n_experts,
+                           max_slots, d_model, d_ff, device, stream);
+}
+
+int qmoe_moe_ep_dispatch(const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
+                         int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *send_dev,
+                         int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks, int seq_len,
+                         int expert_capacity, int pair_capacity, int d_model, int device, void *stream) {
+  QMOE_REQUIRE(n_tokens >= 0 && n_experts >= 1 && n_ranks >= 1 && d_model >= 2 && pair_capacity >= 0, "bad shape");
+  QMOE_REQUIRE(n_experts % n_ranks == 0, "the number of experts must be a multiple of the number of ranks");
+  QMOE_REQUIRE(d_model % 2 == 0, "d_model must be even (the trailer is a 4-byte word)");
+  QMOE_REQUIRE(seq_len >= 1 && (n_tokens % seq_len == 0), "n_tokens must be a multiple of seq_len");
+  QMOE_REQUIRE(expert_capacity >= 0, "negative capacity");
+  if (n_tokens == 0 && pair_capacity == 0) return QMOE_OK;
+  QMOE_REQUIRE(send_dev && overflow_dev && (n_tokens == 0 || (choice_dev && hidden_dev && expert_dev && dest_dev && slot_dev)),
+               "null device pointer");
+  QMOE_REQUIRE(hidden_stride >= d_model, "row stride smaller than the row");
+  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(send_dev) & 3u) == 0, "send buffer must be 4-byte aligned");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_ep_dispatch(choice_dev, hidden_dev, hidden_stride, expert_dev, dest_dev, slot_dev, send_dev,
+                            overflow_dev, n_tokens, n_experts, n_experts / n_ranks, seq_len, expert_capacity,
+                            n_ranks, pair_capacity, d_model, as_stream(stream));
+}
+
+int qmoe_moe_plan(const void *rows_dev, int64_t row_stride, int d_model, const int32_t *bucket_dev, int n_rows,
+                  int n_buckets, int32_t *offsets_dev, int32_t *slot_of_row_dev, int32_t *row_of_slot_dev,
+                  int device, void *stream) {
+  QMOE_REQUIRE(n_rows >= 0 && n_buckets >= 1, "bad shape");
+  if (n_buckets > 8192) {
+    set_error("%s: at most 8192 buckets (their running sizes are kept in shared memory)", __func__);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  QMOE_REQUIRE(offsets_dev != nullptr, "null offsets pointer");
+  QMOE_REQUIRE(n_rows == 0 || ((rows_dev || bucket_dev) && slot_of_row_dev && row_of_slot_dev),
+               "null device pointer");
+  QMOE_REQUIRE(!rows_dev || (d_model >= 2 && d_model % 2 == 0 && row_stride >= d_model + 2 &&
+                             (reinterpret_cast<uintptr_t>(rows_dev) & 3u) == 0 && row_stride % 2 == 0),
+               "rows with a trailer need an even d_model, a stride that holds the trailer and 4-byte alignment");
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_ep_plan(rows_dev, row_stride, d_model, bucket_dev, n_rows, n_buckets, offsets_dev,
+                        slot_of_row_dev, row_of_slot_dev, as_stream(stream));
 }
 
 int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev, int device,

@@ -1,0 +1,203 @@
+// Dispatch metadata of the top-1 MoE layer in three launches: the capacity rule, the packing of rows
+// into fixed-size exchange slots (with each row's local expert id in a 16-byte trailer) and the plan
+// of the receiving side (tokens per local expert, their offsets and which received row feeds which
+// slot of the grouped FFN).  The reference has no counterpart: FasterMLP.forward (sub1.py:306-321)
+// loops over the active experts on the host with nonzero() and boolean masks, and hops whole
+// activations between GPUs (sub1.py:307-309,320) instead of exchanging rows.
+//
+// Nothing here copies a row twice: the grouped FFN reads its input rows through the plan's row list
+// and writes its output rows back to the same places, so there is no permute / un-permute pass.
+#include "common.cuh"
+
+namespace qmoe {
+
+__device__ __forceinline__ int block_sum(int v, int *s_warp) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) s_warp[warp] = v;
+  __syncthreads();
+  int total = 0;
+  for (int w = 0; w < nwarps; w++) total += s_warp[w];
+  return total;
+}
+
+// Thread t < n_tokens: the router's capacity rule (kept iff fewer than `capacity` earlier tokens of the
+// same sequence chose the same expert: cumsum(one_hot) <= expert_capacity).  expert[t] = choice or -1,
+// dest[t] = the rank that owns the expert or -1.  Thread i < n_slots: the trailer of exchange slot i is
+// reset to "empty" (-1).
+__global__ void k_ep_keep(const int32_t *__restrict__ choice, int32_t *__restrict__ expert,
+                          int32_t *__restrict__ dest, int n_tokens, int n_experts, int local_experts,
+                          int seq_len, int capacity, __nv_bfloat16 *__restrict__ send, int n_slots,
+                          long long row_stride, int d_model) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_slots) *reinterpret_cast<int32_t *>(send + (long long)i * row_stride + d_model) = -1;
+  if (i >= n_tokens) return;
+  const int c = choice[i];
+  int keep = c >= 0 && c < n_experts;
+  if (keep && capacity < seq_len) {
+    const int s0 = (i / seq_len) * seq_len;
+    int before = 0;
+    for (int u = s0; u < i; u++) before += (choice[u] == c);
+    keep = before < capacity;
+  }
+  expert[i] = keep ? c : -1;
+  dest[i] = keep ? c / local_experts : -1;
+}
+
+// One CTA per token: rank of the token among the earlier kept tokens with the same destination
+// (stable: token order), its exchange slot dest * cap + rank, the copy of its row and its trailer.
+// A token whose rank does not fit the pair capacity is not sent: slot -1 (it passes through the
+// layer like a token dropped by the capacity rule) and *overflow is incremented (never cleared here).
+__global__ void __launch_bounds__(128) k_ep_pack(const int32_t *__restrict__ expert, const int32_t *__restrict__ dest,
+                                                 const __nv_bfloat16 *__restrict__ hidden, long long hidden_stride,
+                                                 __nv_bfloat16 *__restrict__ send, long long row_stride,
+                                                 int32_t *__restrict__ slot, int *overflow, int d_model,
+                                                 int local_experts, int cap) {
+  __shared__ int s_warp[4];
+  const int t = blockIdx.x;
+  const int dst = dest[t];
+  if (dst < 0) {
+    if (threadIdx.x == 0) slot[t] = -1;
+    return;
+  }
+  int mine = 0;
+  for (int u = threadIdx.x; u < t; u += blockDim.x) mine += (dest[u] == dst);
+  const int rank = block_sum(mine, s_warp);
+  if (rank >= cap) {
+    if (threadIdx.x == 0) {
+      slot[t] = -1;
+      atomicAdd(overflow, 1);
+    }
+    return;
+  }
+  const int s = dst * cap + rank;
+  __nv_bfloat16 *row = send + (long long)s * row_stride;
+  const __nv_bfloat16 *src = hidden + (long long)t * hidden_stride;
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(row)) & 15u) == 0 && (d_model & 7) == 0) {
+    for (int i = threadIdx.x; i < d_model / 8; i += blockDim.x)
+      reinterpret_cast<uint4 *>(row)[i] = reinterpret_cast<const uint4 *>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < d_model; i += blockDim.x) row[i] = src[i];
+  }
+  if (threadIdx.x == 0) {
+    slot[t] = s;
+    *reinterpret_cast<int32_t *>(row + d_model) = expert[t] - dst * local_experts;
+  }
+}
+
+// One CTA.  The bucket of row i (-1 = no row) is read from the trailers of received rows (rows !=
+// nullptr) or from an int32 array.  Produces offsets[n_buckets + 1] (exclusive prefix sums of the
+// bucket sizes), slot_of_row[i] = offsets[bucket] + stable rank (or -1) and row_of_slot[slot] = i.
+// Stable ranks without comparing every pair of rows: rows are taken 1024 at a time in row order;
+// inside a warp __match_any_sync groups the lanes of one bucket, and the 32 warps add their groups to
+// the running bucket counts (dynamic shared memory, n_buckets ints) one after the other.
+__global__ void __launch_bounds__(1024) k_ep_plan(const __nv_bfloat16 *__restrict__ rows, long long row_stride,
+                                                  int d_model, const int32_t *__restrict__ meta_in, int n_rows,
+                                                  int n_buckets, int32_t *__restrict__ offsets,
+                                                  int32_t *__restrict__ slot_of_row, int32_t *__restrict__ row_of_slot) {
+  extern __shared__ int s_count[];  // running size of every bucket
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int b = tid; b < n_buckets; b += blockDim.x) s_count[b] = 0;
+  __syncthreads();
+  for (int i0 = 0; i0 < n_rows; i0 += blockDim.x) {
+    const int i = i0 + tid;
+    int b = -1;
+    if (i < n_rows) {
+      b = rows != nullptr ? *reinterpret_cast<const int32_t *>(rows + (long long)i * row_stride + d_model) : meta_in[i];
+      b = (b >= 0 && b < n_buckets) ? b : -1;
+    }
+    // lanes without a row get distinct negative keys so that they group with nobody
+    const unsigned same = __match_any_sync(0xffffffffu, b >= 0 ? b : -1 - lane);
+    const int before_in_warp = __popc(same & ((1u << lane) - 1u));
+    const bool leader = before_in_warp == 0;
+    int rank = -1;
+    for (int w = 0; w < 32; w++) {
+      if (warp == w && b >= 0) {
+        rank = s_count[b] + before_in_warp;
+        __syncwarp(same);
+        if (leader) s_count[b] += __popc(same);
+      }
+      __syncthreads();
+    }
+    if (i < n_rows) slot_of_row[i] = rank;  // the offset of the bucket is added below
+  }
+  // offsets = exclusive scan of the bucket sizes
+  if (tid == 0) {
+    s_carry = 0;
+    offsets[0] = 0;
+  }
+  __syncthreads();
+  for (int b0 = 0; b0 < n_buckets; b0 += blockDim.x) {
+    const int b = b0 + tid;
+    const int v = b < n_buckets ? s_count[b] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += u;
+      }
+      s_warp[lane] = w;
+    }
+    __syncthreads();
+    const int incl_all = s_carry + (warp ? s_warp[warp - 1] : 0) + incl;
+    if (b < n_buckets) {
+      offsets[1 + b] = incl_all;
+      s_count[b] = incl_all - v;  // now the bucket's first slot
+    }
+    __syncthreads();
+    if (tid == 0) s_carry += s_warp[31];
+    __syncthreads();
+  }
+  for (int i = tid; i < n_rows; i += blockDim.x) {
+    const int rank = slot_of_row[i];
+    if (rank < 0) continue;
+    int b = rows != nullptr ? *reinterpret_cast<const int32_t *>(rows + (long long)i * row_stride + d_model) : meta_in[i];
+    const int s = s_count[b] + rank;
+    slot_of_row[i] = s;
+    row_of_slot[s] = i;
+  }
+}
+
+int launch_ep_dispatch(const int32_t *choice, const void *hidden, int64_t hidden_stride, int32_t *expert,
+                       int32_t *dest, int32_t *slot, void *send, int *overflow, int n_tokens, int n_experts,
+                       int local_experts, int seq_len, int capacity, int n_ranks, int cap, int d_model,
+                       cudaStream_t stream) {
+  const int n_slots = n_ranks * cap;
+  const long long row_stride = d_model + 8;
+  const int threads = 256;
+  const int n = n_tokens > n_slots ? n_tokens : n_slots;
+  QMOE_LAUNCH(k_ep_keep, (n + threads - 1) / threads, threads, 0, stream, choice, expert, dest, n_tokens, n_experts,
+              local_experts, seq_len, capacity, reinterpret_cast<__nv_bfloat16 *>(send), n_slots, row_stride, d_model);
+  QMOE_CUDA(cudaGetLastError());
+  if (n_tokens > 0) {
+    QMOE_LAUNCH(k_ep_pack, n_tokens, 128, 0, stream, expert, dest, reinterpret_cast<const __nv_bfloat16 *>(hidden),
+                (long long)hidden_stride, reinterpret_cast<__nv_bfloat16 *>(send), row_stride, slot, overflow, d_model,
+                local_experts, cap);
+    QMOE_CUDA(cudaGetLastError());
+  }
+  return QMOE_OK;
+}
+
+int launch_ep_plan(const void *rows, int64_t row_stride, int d_model, const int32_t *meta, int n_rows, int n_buckets,
+                   int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, cudaStream_t stream) {
+  QMOE_LAUNCH(k_ep_plan, 1, 1024, sizeof(int) * (size_t)n_buckets, stream,
+              reinterpret_cast<const __nv_bfloat16 *>(rows), (long long)row_stride, d_model, meta, n_rows, n_buckets,
+              offsets, slot_of_row, row_of_slot);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+}  // namespace qmoe

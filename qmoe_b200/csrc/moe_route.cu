@@ -348,6 +348,15 @@ int launch_rank(const int32_t *choice, int32_t *bucket, int32_t *rank, int32_t *
   return QMOE_OK;
 }
 
+int launch_keep(const int32_t *choice, int32_t *expert, int n_tokens, int n_experts, int seq_len, int capacity,
+                cudaStream_t stream) {
+  const int threads = 256;
+  QMOE_LAUNCH(k_capacity, (n_tokens + threads - 1) / threads, threads, 0, stream, choice, expert, n_tokens, n_experts,
+              seq_len, capacity);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
 int launch_scan(const int32_t *counts, int32_t *offsets, int n, cudaStream_t stream) {
   QMOE_LAUNCH(k_exclusive_scan, 1, 1024, 0, stream, counts, offsets, n);
   QMOE_CUDA(cudaGetLastError());

@@ -183,6 +183,7 @@ struct MatmulArgs {
   const __nv_bfloat16 *x;
   __nv_bfloat16 *y;
   long long x_stride, y_stride;
+  const int32_t *x_rows, *y_rows;  // grouped mode: token t reads row x_rows[t] / writes row y_rows[t] (null: t)
   const int4 *items;  // grouped mode: {matrix, first row, first token, rows | tokens << 16}
   int *header;        // grouped mode: header[0] = item count, header[1] = fetch counter
   int chunks, rpc, tokens;  // uniform mode
@@ -200,7 +201,8 @@ __device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink
     if (t < ntok) {
       // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
       float v = bf16_round(sink.acc[t]);
-      __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
+      const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + t] : tok0 + t;
+      __nv_bfloat16 *yp = a.y + out_row * a.y_stride + row;
       if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
       if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
       *yp = __float2bfloat16_rn(v);
@@ -211,12 +213,18 @@ __device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink
 template <int T, class SinkT>
 __device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wlim, int tok0, int ntok,
                                              typename SinkT::elem *xs) {
-  // xs[c][t] = x[tok0 + t][c], zero beyond the width / token count.
+  // xs[c][t] = x[row of token tok0 + t][c], zero beyond the width / token count.
+  const __nv_bfloat16 *xp[T];
+#pragma unroll
+  for (int t = 0; t < T; t++) {
+    const int tok = tok0 + (t < ntok ? t : 0);
+    xp[t] = a.x + (a.x_rows != nullptr ? (long long)a.x_rows[tok] : (long long)tok) * a.x_stride;
+  }
   for (int c = threadIdx.x; c < wlim + kPad; c += blockDim.x) {
 #pragma unroll
     for (int t = 0; t < T; t++) {
       __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-      if (c < W && t < ntok) v = a.x[(long long)(tok0 + t) * a.x_stride + c];
+      if (c < W && t < ntok) v = xp[t][c];
       xs[c * T + t] = SinkT::stage(v);
     }
   }
@@ -880,8 +888,8 @@ int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, 
                            int max_slots, int *header, int4 *items_wi, int4 *items_wo, cudaStream_t stream);
 int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int4 *items, const int *n_items, int flags, int max_items, int device,
-                      cudaStream_t stream);
+                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, const int *n_items, int flags,
+                      int max_items, int device, cudaStream_t stream);
 
 // Experts with at least this many tokens take the tile path (0 disables it).  The default is the
 // measured break-even on a switch-large-128 layer with a skewed router (eight hot experts share half
@@ -946,12 +954,14 @@ int work_summary(const void *work, int32_t *out, cudaStream_t stream) {
 // The ring kernel of sub1_ring.cu.
 int launch_ring_phase(const uint32_t *ring_table, const void *il, const int64_t *blk_base, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int4 *items, int *header, int flags, int device, cudaStream_t stream);
+                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, int *header, int flags,
+                      int device, cudaStream_t stream);
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
-                       void *hs, void *ys, void *work, int n_experts, int max_slots, int d_model, int d_ff,
+                       int64_t xs_stride, const int32_t *x_rows, void *hs, void *ys, int64_t ys_stride,
+                       const int32_t *y_rows, void *work, int n_experts, int max_slots, int d_model, int d_ff,
                        int device, cudaStream_t stream) {
   int rc = ensure_smem_limits(device);
   if (rc) return rc;
@@ -1007,15 +1017,17 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     const int height = phase == 0 ? d_ff : d_model;
     a.x = reinterpret_cast<const __nv_bfloat16 *>(phase == 0 ? xs : hs);
     a.y = reinterpret_cast<__nv_bfloat16 *>(phase == 0 ? hs : ys);
-    a.x_stride = width;
-    a.y_stride = height;
+    a.x_stride = phase == 0 ? xs_stride : width;
+    a.y_stride = phase == 0 ? height : ys_stride;
+    a.x_rows = phase == 0 ? x_rows : nullptr;   // the hidden activation in between is indexed by slot
+    a.y_rows = phase == 0 ? nullptr : y_rows;
     a.items = ph[phase].items;
     a.header = header + 2 * phase;
     a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
     if (tile_min > 0) {
       const int rows_blocks = (height + 127) / 128;
       rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
-                             phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
+                             a.x_rows, a.y_rows, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
       if (rc) return rc;
     }
@@ -1023,7 +1035,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     if (il) {
       if ((long long)max_slots * height > kSmallRows) {  // smaller steps go to the warp kernel whole
         rc = launch_ring_phase(ils->ring_table, ils->codes, ils->blk_base, minmax, descs, a.x, a.y, a.x_stride,
-                               a.y_stride, a.items, a.header, a.flags, device, stream);
+                               a.y_stride, a.x_rows, a.y_rows, a.items, a.header, a.flags, device, stream);
         if (rc) return rc;
       }
       MatmulArgs w = a;

@@ -360,6 +360,7 @@ struct RingArgs {
   const __nv_bfloat16 *x;
   __nv_bfloat16 *y;
   long long x_stride, y_stride;
+  const int32_t *x_rows, *y_rows;  // token t reads row x_rows[t] / writes row y_rows[t] (null: t)
   const int4 *items;  // {matrix, first row, first token, rows | tokens << 16}
   int *header;        // header[0] = item count, header[1] = fetch counter
   int flags;
@@ -410,8 +411,9 @@ __device__ __forceinline__ void ring_item(const RingArgs &a, const qmoe_matrix_d
   float acc0 = 0.f, acc1 = 0.f;
 
   // activations of the item's tokens; columns at and beyond the width read as zero
-  const __nv_bfloat16 *x0 = a.x + (long long)tok0 * a.x_stride;
-  const __nv_bfloat16 *x1 = a.x + (long long)(tok0 + (ntok > 1 ? 1 : 0)) * a.x_stride;
+  const int tok1 = tok0 + (ntok > 1 ? 1 : 0);
+  const __nv_bfloat16 *x0 = a.x + (a.x_rows != nullptr ? (long long)a.x_rows[tok0] : (long long)tok0) * a.x_stride;
+  const __nv_bfloat16 *x1 = a.x + (a.x_rows != nullptr ? (long long)a.x_rows[tok1] : (long long)tok1) * a.x_stride;
   auto x_word = [&](uint32_t c) -> uint32_t {
     if (c >= (uint32_t)W) return 0u;
     if (T == 1) return __float_as_uint(__bfloat162float(x0[c]));
@@ -503,7 +505,8 @@ __device__ __forceinline__ void ring_item(const RingArgs &a, const qmoe_matrix_d
       if (t < ntok) {
         // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200)
         float v = __bfloat162float(__float2bfloat16_rn(t == 0 ? acc0 : acc1));
-        __nv_bfloat16 *yp = a.y + (long long)(tok0 + t) * a.y_stride + row;
+        const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + t] : tok0 + t;
+        __nv_bfloat16 *yp = a.y + out_row * a.y_stride + row;
         if (a.flags & QMOE_FLAG_ACCUMULATE) v = __bfloat162float(__float2bfloat16_rn(__bfloat162float(*yp) + v));
         if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
         *yp = __float2bfloat16_rn(v);
@@ -540,7 +543,8 @@ __global__ void __launch_bounds__(kRingThreads, 1) k_matmul_ring(const RingArgs 
 
 int launch_ring_phase(const uint32_t *ring_table, const void *il, const int64_t *blk_base, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int4 *items, int *header, int flags, int device, cudaStream_t stream) {
+                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, int *header, int flags,
+                      int device, cudaStream_t stream) {
   static bool configured[64] = {false};
   if (device < 0 || device >= 64) {
     set_error("device index %d out of range", device);
@@ -563,6 +567,8 @@ int launch_ring_phase(const uint32_t *ring_table, const void *il, const int64_t 
   a.y = reinterpret_cast<__nv_bfloat16 *>(y);
   a.x_stride = x_stride;
   a.y_stride = y_stride;
+  a.x_rows = x_rows;
+  a.y_rows = y_rows;
   a.items = items;
   a.header = header;
   a.flags = flags;

@@ -46,6 +46,7 @@ struct TileArgs {
   const __nv_bfloat16 *x;
   __nv_bfloat16 *y;
   long long x_stride, y_stride;
+  const int32_t *x_rows, *y_rows;  // token t reads row x_rows[t] / writes row y_rows[t] (null: t)
   const int4 *items;   // {matrix, first row, first token, tokens}
   const int *n_items;  // device scalar
   int *status;         // device word: incremented when a bounded wait gives up (sticky)
@@ -187,7 +188,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
         const int u = t + i * kTileM;
         const int n = u & (kTileN - 1), c = u >> 6;
         live[i] = n < ntok;
-        src[i] = a.x + (long long)(tok0 + (live[i] ? n : 0)) * a.x_stride + 8 * c;
+        const int tok = tok0 + (live[i] ? n : 0);
+        src[i] = a.x + (a.x_rows != nullptr ? (long long)a.x_rows[tok] : (long long)tok) * a.x_stride + 8 * c;
       }
       for (int w = 0; w < n_windows; w++) {
         const int st = w & 1, k0 = w * kTileK;
@@ -338,7 +340,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
         const qmoe_matrix_desc rd = a.descs[ri.x];
         for (int i = tid; i < kTileM * ri.w; i += kTileThreads) {
           const int r = ri.y + (i % kTileM), n = i / kTileM;
-          if (r < rd.height) a.y[(long long)(ri.z + n) * a.y_stride + r] = __float2bfloat16_rn(0.f);
+          const long long out_row = a.y_rows != nullptr ? a.y_rows[ri.z + n] : ri.z + n;
+          if (r < rd.height) a.y[out_row * a.y_stride + r] = __float2bfloat16_rn(0.f);
         }
       }
       break;
@@ -358,7 +361,8 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
           if (valid_row && n < ntok) {
             float r = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
             if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
-            a.y[(long long)(tok0 + n) * a.y_stride + row] = __float2bfloat16_rn(r);
+            const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + n] : tok0 + n;
+            a.y[out_row * a.y_stride + row] = __float2bfloat16_rn(r);
           }
         }
       }
@@ -433,8 +437,8 @@ int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, 
 // One linear (wi or wo) of every expert on the tile path.
 int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int4 *items, const int *n_items, int flags, int max_items, int device,
-                      cudaStream_t stream) {
+                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, const int *n_items, int flags,
+                      int max_items, int device, cudaStream_t stream) {
   TileArgs a{};
   a.tab = tab;
   a.codes = codes;
@@ -445,6 +449,8 @@ int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t 
   a.y = reinterpret_cast<__nv_bfloat16 *>(y);
   a.x_stride = x_stride;
   a.y_stride = y_stride;
+  a.x_rows = x_rows;
+  a.y_rows = y_rows;
   a.items = items;
   a.n_items = n_items;
   a.status = tile_status_word(device);

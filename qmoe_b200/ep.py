@@ -6,16 +6,23 @@ The reference places whole layers on GPUs and hops activations between them (sub
 
   route -> dispatch all-to-all -> local grouped expert FFN -> combine all-to-all -> scale.
 
-Both exchanges use fixed-size slots: every (source, destination) pair owns ``pair_capacity`` rows
-(by default the local token count, the worst case, so no token is ever dropped by the exchange).
+Both exchanges use fixed-size slots: every (source, destination) pair owns ``pair_capacity`` rows.
 That keeps all sizes known on the host: no count exchange, no device-to-host synchronisation, and
 the step can be replayed from a CUDA graph.  Each row carries its local expert id in a 16-byte
 trailer, so one collective moves payload and metadata together.  Received rows land in this GPU's
-own memory before any kernel reads them.
+own memory before any kernel reads them, and they are not copied again: the grouped FFN reads them
+through a row list and writes its results back to the same rows of the return buffer.
 
-The device work (ranking, permutation, grouped FFN, combine) goes through an ``ops`` namespace, by
-default the CUDA entry points of :mod:`qmoe_b200.sub1`; the CPU test-suite substitutes a torch
-re-statement to check the index arithmetic and the exchanges among gloo ranks.
+``pair_capacity`` defaults to twice the mean number of rows a pair exchanges under uniform routing
+plus 16 (about nine standard deviations at 8 ranks), capped by the local token count, which is the
+worst case.  A token that does not fit is not exchanged: it passes through the layer scaled by its
+router probability, exactly like a token dropped by the router's own capacity rule, and is counted
+in ``overflow_count()``.  ``pair_capacity=n_local`` (or ``exact=True``, which re-runs an overflowing
+step at the worst case after a host check) never drops one.
+
+The device work goes through an ``ops`` namespace, by default the CUDA entry points of
+:mod:`qmoe_b200.sub1`; the CPU test-suite substitutes a torch re-statement to check the index
+arithmetic and the exchanges among gloo ranks.
 """
 from __future__ import annotations
 
@@ -32,12 +39,20 @@ def _default_ops():
     return sub1
 
 
+def default_pair_capacity(n_local: int, world: int) -> int:
+    """Rows every (source, destination) pair can exchange per step."""
+    if world <= 1:
+        return n_local
+    mean = (n_local + world - 1) // world
+    return min(n_local, (2 * mean + 16 + 7) // 8 * 8)
+
+
 class ExpertParallelMLP:
     """``store`` holds this rank's experts; ``n_experts`` is the global count."""
 
     def __init__(self, router_weight: Optional[torch.Tensor], store, n_experts: int,
                  group: Optional[dist.ProcessGroup] = None, expert_capacity: int = 1024,
-                 pair_capacity: Optional[int] = None, ops=None):
+                 pair_capacity: Optional[int] = None, ops=None, exact: bool = False):
         self.ops = ops if ops is not None else _default_ops()
         self.store = store
         self.group = group
@@ -51,6 +66,8 @@ class ExpertParallelMLP:
             raise ValueError(f"store holds {store.n_experts} experts, expected {self.local_experts}")
         self.expert_capacity = int(expert_capacity)
         self.pair_capacity = pair_capacity
+        self.exact = bool(exact)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=store.device)
         self.router = None
         if router_weight is not None:
             from .sub1 import RouterClassifier
@@ -59,48 +76,49 @@ class ExpertParallelMLP:
     def router_logits(self, hidden2d: torch.Tensor) -> torch.Tensor:
         return self.router(hidden2d)
 
-    def forward(self, hidden: torch.Tensor, router_logits: Optional[torch.Tensor] = None, seq_len: int = 0):
+    def overflow_count(self, reset: bool = False) -> int:
+        """Tokens that did not fit their pair's exchange capacity since the last reset (a device-to-host
+        read: call it where the caller synchronises anyway)."""
+        n = int(self.overflow.item())
+        if reset:
+            self.overflow.zero_()
+        return n
+
+    def forward(self, hidden: torch.Tensor, router_logits: Optional[torch.Tensor] = None, seq_len: int = 0,
+                pair_capacity: Optional[int] = None):
         """``hidden`` bf16 [n_local, d_model] (every rank passes the same n_local)."""
         ops, G, d = self.ops, self.world, hidden.shape[1]
         n = hidden.shape[0]
-        dev = hidden.device
-        cap = int(self.pair_capacity or n)
+        cap = int(pair_capacity or self.pair_capacity or default_pair_capacity(n, G))
         seq_len = seq_len or n
         if router_logits is None:
             router_logits = self.router_logits(hidden)
         choice, prob = ops.route_top1(router_logits.reshape(n, self.n_experts).float().contiguous())
-        # capacity rule on the global expert id, then bucket by destination rank
-        expert, _, _, _ = ops.rank_buckets(choice, self.n_experts, seq_len, self.expert_capacity)
-        dest = torch.where(expert >= 0, torch.div(expert, self.local_experts, rounding_mode="floor"),
-                           expert).to(torch.int32)
-        bucket, rank, _, _ = ops.rank_buckets(dest, G, n, cap)
+        if self.exact and cap < n:
+            before = self.overflow_count()
+        # capacity rule on the global expert id, destination rank, rows packed into exchange slots
+        expert, slot, send = ops.ep_dispatch(choice, hidden, self.n_experts, G, seq_len, self.expert_capacity, cap,
+                                             self.overflow)
+        if self.exact and cap < n:
+            # every rank must take the same branch: the largest overflow decides
+            over = torch.tensor([self.overflow_count() - before], dtype=torch.int32, device=hidden.device)
+            if G > 1:
+                dist.all_reduce(over, op=dist.ReduceOp.MAX, group=self.group)
+            if int(over.item()) > 0:
+                self.overflow.fill_(before)
+                return self.forward(hidden, router_logits, seq_len, pair_capacity=n)
 
-        # send buffer: G * cap rows (+1 scratch row that absorbs the metadata of dropped tokens)
-        row = d + TRAILER
-        send = torch.empty((G * cap + 1, row), dtype=torch.bfloat16, device=dev)
-        meta = send.view(torch.int32)[:, d // 2]
-        meta.fill_(-1)
-        fixed = torch.arange(G + 1, dtype=torch.int32, device=dev) * cap
-        slot = ops.permute_rows(bucket, rank, fixed, hidden, send[:, :d])
-        local_id = (expert - dest * self.local_experts).to(torch.int32)
-        meta.index_copy_(0, torch.where(slot >= 0, slot, G * cap).to(torch.int64), local_id)
-
-        recv = torch.empty((G * cap, row), dtype=torch.bfloat16, device=dev)
         if G > 1:
-            dist.all_to_all_single(recv, send[:G * cap], group=self.group)
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=self.group)
         else:
-            recv.copy_(send[:G * cap])
-
-        meta_r = recv.view(torch.int32)[:, d // 2].contiguous()
-        bucket_r, rank_r, _, offsets_r = ops.rank_buckets(meta_r, self.local_experts, G * cap, G * cap)
-        xs = torch.empty((G * cap, d), dtype=torch.bfloat16, device=dev)
-        slot_r = ops.permute_rows(bucket_r, rank_r, offsets_r, recv[:, :d], xs)
-        ys = ops.grouped_ffn(self.store, offsets_r, xs, G * cap)
-        ret = torch.empty((G * cap, d), dtype=torch.bfloat16, device=dev)
-        ops.unpermute_rows(ys, slot_r, ret)
-
-        back = torch.empty_like(ret)
+            recv = send
+        # received rows grouped by local expert, in place: row lists instead of sorted copies
+        offsets_r, _, row_of_slot = ops.plan_rows(self.local_experts, rows=recv, d_model=d)
+        ret = torch.empty((G * cap, d), dtype=torch.bfloat16, device=hidden.device)
+        ops.grouped_ffn_rows(self.store, offsets_r, recv, row_of_slot, ret, row_of_slot, G * cap)
         if G > 1:
+            back = torch.empty_like(ret)
             dist.all_to_all_single(back, ret, group=self.group)
         else:
             back = ret

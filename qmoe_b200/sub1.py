@@ -370,6 +370,87 @@ def unpermute_rows(ys: torch.Tensor, slot: torch.Tensor, out: torch.Tensor) -> N
                                               ys.stride(0), out.stride(0), dev.index, _s(dev)))
 
 
+def capacity_rule(choice: torch.Tensor, n_experts: int, seq_len: int, capacity: int) -> torch.Tensor:
+    """``expert[t]`` = ``choice[t]`` if the router's capacity rule keeps token ``t`` (fewer than
+    ``capacity`` earlier tokens of its sequence chose the same expert), else -1.  One launch."""
+    n = choice.numel()
+    dev = choice.device
+    expert = torch.empty(n, dtype=torch.int32, device=dev)
+    _lib.check(_lib.load().qmoe_moe_keep(choice.data_ptr(), expert.data_ptr(), n, int(n_experts),
+                                         max(int(seq_len), 1), int(capacity), dev.index, _s(dev)))
+    return expert
+
+
+def plan_rows(n_buckets: int, bucket: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+              d_model: int = 0):
+    """Group rows by bucket, stable in row order, in one launch.  The bucket of row ``i`` is
+    ``bucket[i]`` or, with ``rows`` (bf16 ``[m, d_model + 8]`` as exchanged by the expert-parallel
+    layer), the int32 in the row's trailer; values outside ``[0, n_buckets)`` mean "no row".
+    Returns (offsets int32[n_buckets + 1], slot_of_row int32[m], row_of_slot int32[m])."""
+    src = rows if rows is not None else bucket
+    m = src.shape[0]
+    dev = src.device
+    offsets = torch.empty(n_buckets + 1, dtype=torch.int32, device=dev)
+    slot_of_row = torch.empty(m, dtype=torch.int32, device=dev)
+    row_of_slot = torch.zeros(m, dtype=torch.int32, device=dev)
+    if rows is not None:
+        assert rows.dtype == torch.bfloat16 and rows.stride(1) == 1 and rows.shape[1] >= d_model + 2
+        args = (rows.data_ptr(), rows.stride(0), int(d_model), None)
+    else:
+        assert bucket.dtype == torch.int32 and bucket.is_contiguous()
+        args = (None, 0, 0, bucket.data_ptr())
+    _lib.check(_lib.load().qmoe_moe_plan(*args, m, int(n_buckets), offsets.data_ptr(), slot_of_row.data_ptr(),
+                                         row_of_slot.data_ptr(), dev.index, _s(dev)))
+    return offsets, slot_of_row, row_of_slot
+
+
+def ep_dispatch(choice: torch.Tensor, hidden: torch.Tensor, n_experts: int, n_ranks: int, seq_len: int,
+                expert_capacity: int, pair_capacity: int, overflow: torch.Tensor):
+    """Capacity rule, destination ranks and the packing of the kept rows into ``n_ranks *
+    pair_capacity`` exchange slots of ``d_model + 8`` bf16 (row + 16-byte trailer with the expert's
+    index on its rank), in two launches.  Returns (expert int32[n] or -1, slot int32[n] or -1, send).
+    Tokens that do not fit their pair's capacity get slot -1 and are counted in ``overflow``
+    (int32[1], zeroed by the caller once)."""
+    n, d = hidden.shape
+    dev = hidden.device
+    expert = torch.empty(n, dtype=torch.int32, device=dev)
+    dest = torch.empty(n, dtype=torch.int32, device=dev)
+    slot = torch.empty(n, dtype=torch.int32, device=dev)
+    send = torch.empty((n_ranks * pair_capacity, d + 8), dtype=torch.bfloat16, device=dev)
+    assert hidden.dtype == torch.bfloat16 and hidden.stride(1) == 1 and choice.dtype == torch.int32
+    _lib.check(_lib.load().qmoe_moe_ep_dispatch(
+        choice.data_ptr(), hidden.data_ptr(), hidden.stride(0), expert.data_ptr(), dest.data_ptr(), slot.data_ptr(),
+        send.data_ptr(), overflow.data_ptr(), n, int(n_experts), int(n_ranks), max(int(seq_len), 1),
+        int(expert_capacity), int(pair_capacity), d, dev.index, _s(dev)))
+    return expert, slot, send
+
+
+def grouped_ffn_rows(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, x_rows: Optional[torch.Tensor],
+                     ys: torch.Tensor, y_rows: Optional[torch.Tensor], max_slots: int,
+                     work: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`grouped_ffn` through row lists: slot ``s`` reads row ``x_rows[s]`` of ``xs`` (any row
+    stride) and writes row ``y_rows[s]`` of ``ys``; ``None`` means ``s`` itself.  No sorted copy of
+    the activations is made."""
+    dev = store.device
+    L = _lib.load()
+    if max_slots == 0:
+        return ys
+    hs = torch.empty((max_slots, store.d_ff), dtype=torch.bfloat16, device=dev)
+    nbytes = int(L.qmoe_moe_work_bytes(store.n_experts, max_slots, store.d_model, store.d_ff))
+    if work is None or work.numel() < nbytes:
+        work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    assert xs.dtype == torch.bfloat16 and ys.dtype == torch.bfloat16 and xs.stride(1) == 1 and ys.stride(1) == 1
+    dec = store.dec if store.dec is not None else DEC(dev)
+    _lib.check(L.qmoe_moe_grouped_ffn_rows(
+        dec.data_ptr(), None if store.codes is None else store.codes.data_ptr(), store.row_off.data_ptr(),
+        store.minmax.data_ptr(), store.descs.data_ptr(),
+        ctypes.addressof(store.il_struct) if store.il_codes is not None else None, offsets.data_ptr(),
+        xs.data_ptr(), xs.stride(0), None if x_rows is None else x_rows.data_ptr(), hs.data_ptr(), ys.data_ptr(),
+        ys.stride(0), None if y_rows is None else y_rows.data_ptr(), work.data_ptr(), store.n_experts, max_slots,
+        store.d_model, store.d_ff, dev.index, _s(dev)))
+    return ys
+
+
 def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max_slots: int,
                 work: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``wo(ReLU(wi(x)))`` for tokens sorted by local expert (``offsets`` int32[E+1]); returns
@@ -517,7 +598,8 @@ class FasterMLP(nn.Module):
     ``store``: the layer's :class:`ExpertStore`; ``expert_capacity``: tokens of one sequence an
     expert accepts before the router drops them (dropped tokens pass through scaled by their router
     probability, sub1.py:312,318).  Unlike the reference there is no loop over active experts and
-    no host synchronisation: one grouped launch per linear covers every expert that got tokens."""
+    no host synchronisation: one grouped launch per linear covers every expert that got tokens, and
+    the tokens are not copied into expert order (the kernels read them through a row list)."""
 
     def __init__(self, router_weight: Optional[torch.Tensor], store: ExpertStore, expert_capacity: int = 1024):
         super().__init__()
@@ -539,12 +621,13 @@ class FasterMLP(nn.Module):
             router_logits = self.router_logits(hidden)
         logits2d = router_logits.reshape(n, -1).float().contiguous()
         choice, prob = route_top1(logits2d)
-        bucket, rank, _counts, offsets = rank_buckets(choice, self.store.n_experts, seq_len, self.expert_capacity)
-        xs = torch.empty_like(hidden)
-        slot = permute_rows(bucket, rank, offsets, hidden, xs)
-        ys = grouped_ffn(self.store, offsets, xs, n)
+        expert = capacity_rule(choice, self.store.n_experts, seq_len, self.expert_capacity)
+        # tokens grouped by expert without copying them: the grouped FFN reads row row_of_slot[s]
+        offsets, slot, row_of_slot = plan_rows(self.store.n_experts, bucket=expert)
+        ys = torch.empty_like(hidden)
+        grouped_ffn_rows(self.store, offsets, hidden, row_of_slot, ys, None, n)
         out = combine(ys, hidden, slot, prob)
-        expert_index = torch.clamp(bucket, min=0).to(torch.int64)
+        expert_index = torch.clamp(expert, min=0).to(torch.int64)
         lead = shape[:-1]
         return (out.reshape(shape).to(hidden_states.device),
                 (router_logits.reshape(*lead, -1), expert_index.reshape(lead)))

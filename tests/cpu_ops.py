@@ -54,6 +54,67 @@ def unpermute_rows(ys, slot, out):
         out[t] = ys[int(slot[t])] if slot[t] >= 0 else 0
 
 
+def ep_dispatch(choice, hidden, n_experts, n_ranks, seq_len, expert_capacity, pair_capacity, overflow):
+    n, d = hidden.shape
+    local = n_experts // n_ranks
+    expert, _, _, _ = rank_buckets(choice, n_experts, seq_len, expert_capacity)
+    send = torch.zeros((n_ranks * pair_capacity, d + 8), dtype=torch.bfloat16)
+    meta = send.view(torch.int32)[:, d // 2]
+    meta.fill_(-1)
+    slot = torch.full((n,), -1, dtype=torch.int32)
+    used = [0] * n_ranks
+    for t in range(n):
+        e = int(expert[t])
+        if e < 0:
+            continue
+        dst = e // local
+        if used[dst] >= pair_capacity:
+            overflow += 1
+            continue
+        s = dst * pair_capacity + used[dst]
+        used[dst] += 1
+        slot[t] = s
+        send[s, :d] = hidden[t]
+        meta[s] = e - dst * local
+    return expert, slot, send
+
+
+def plan_rows(n_buckets, bucket=None, rows=None, d_model=0):
+    if rows is not None:
+        bucket = rows.view(torch.int32)[:, d_model // 2].clone()
+    m = bucket.numel()
+    b = torch.where((bucket >= 0) & (bucket < n_buckets), bucket, torch.full_like(bucket, -1))
+    counts = torch.zeros(n_buckets, dtype=torch.int32)
+    offsets = torch.zeros(n_buckets + 1, dtype=torch.int32)
+    for i in range(m):
+        if b[i] >= 0:
+            counts[int(b[i])] += 1
+    offsets[1:] = torch.cumsum(counts, 0)
+    slot_of_row = torch.full((m,), -1, dtype=torch.int32)
+    row_of_slot = torch.zeros(m, dtype=torch.int32)
+    seen = [0] * n_buckets
+    for i in range(m):
+        if b[i] >= 0:
+            s = int(offsets[int(b[i])]) + seen[int(b[i])]
+            seen[int(b[i])] += 1
+            slot_of_row[i] = s
+            row_of_slot[s] = i
+    return offsets, slot_of_row, row_of_slot
+
+
+def grouped_ffn_rows(store, offsets, xs, x_rows, ys, y_rows, max_slots):
+    d = store.d_model
+    for e in range(store.n_experts):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            src = [int(x_rows[s]) if x_rows is not None else s for s in range(a, b)]
+            dst = [int(y_rows[s]) if y_rows is not None else s for s in range(a, b)]
+            y = store.experts[e].oracle_ffn(xs[src, :d].contiguous())
+            for k, r in enumerate(dst):
+                ys[r] = y[k]
+    return ys
+
+
 def grouped_ffn(store, offsets, xs, max_slots):
     ys = torch.zeros((max_slots, store.d_model), dtype=torch.bfloat16)
     for e in range(store.n_experts):
