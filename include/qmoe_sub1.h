@@ -201,63 +201,65 @@ int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, cons
 
 /* Paired-lane copy of a store's code streams, the layout the grouped kernel reads fastest.  No
  * counterpart in the reference, whose kernel (sub1_cuda_kernel.cu:129-202) reads w_comp row by row;
- * the copy decodes to exactly the same weights (qmoe_moe_ring_decode is the check) and is derived
+ * the copy decodes to exactly the same weights (qmoe_moe_paired_decode is the check) and is derived
  * on the device when a store is created; the reference's tensors stay what every other entry point
  * and every checkpoint holds.
  *
  * Layout: rows are taken in blocks of 32; a 32-bit word holds two codes (low half first); word k of
  * row l of a block is the uint32 at index blk_base[block] + k * 32 + l; every row of a block has the
- * block's number of words, padded with the null code QMOE_RING_TABLE - 1.  Heights must be
+ * block's number of words, padded with the null code QMOE_PAIRED_TABLE - 1.  Heights must be
  * multiples of 32 and the matrices' rows consecutive (minmax_base = rows before).
- * Numbering: code values are renumbered by decreasing frequency; the QMOE_RING_TABLE - 1 most
+ * Numbering: code values are renumbered by decreasing frequency; the QMOE_PAIRED_TABLE - 1 most
  * frequent dictionary entries are served from shared memory, and every other code of the reference
  * stream is replaced by the two or more frequent codes whose pair sequences concatenate to its own
  * (the dictionary contains every prefix and, where it matters, every suffix of its entries), so the
  * kernel never reads the table from global memory.
  *   1. qmoe_sub1_code_histogram over (a sample of) the store's streams;
- *   2. qmoe_moe_ring_prepare: reads dec and the histogram back (synchronises), and writes
- *      remap_out_dev uint32[65536] (code -> new number), ring_table_out_dev uint32[QMOE_RING_TABLE]
+ *   2. qmoe_moe_paired_prepare: reads dec and the histogram back (synchronises), and writes
+ *      remap_out_dev uint32[65536] (code -> new number), hot_table_out_dev uint32[QMOE_PAIRED_TABLE]
  *      (the kernel's table), table_out_dev uint32[65536] (the 4-byte table of the row-per-warp kernel
  *      in the new numbering), split_off_out_dev uint32[65537] and split_codes_out_dev
  *      uint16[split_capacity]: code c of the reference stream becomes
  *      split_codes[split_off[c] .. split_off[c+1]).  QMOE_ERR_UNSUPPORTED when the table has an entry
  *      with more than three non-zeros or a code that cannot be cut that way (the store then runs on
  *      its row-by-row streams);
- *   3. qmoe_moe_ring_count: blk_units_dev int32[total_rows / 32] := words per block * 32
+ *   3. qmoe_moe_paired_count: blk_units_dev int32[total_rows / 32] := words per block * 32
  *      (descs_host: the same descriptors in host memory, for validation);
  *   4. the caller forms blk_base int64[total_rows / 32 + 1], the exclusive prefix sum, and allocates
- *      4 * blk_base[last] bytes (16-byte aligned);
- *   5. qmoe_moe_ring_emit fills them;
+ *      4 * (blk_base[last] + QMOE_PAIRED_TAIL_WORDS) bytes (16-byte aligned);
+ *   5. qmoe_moe_paired_emit fills the first blk_base[last] words; the caller fills the tail with null
+ *      words (the kernel reads its stream a few words ahead without a range test);
  *   6. qmoe_moe_grouped_ffn_interleaved is qmoe_moe_grouped_ffn reading the copy.  Experts on the
  *      tensor-core tile path still read codes_dev with dec_dev; codes_dev may be NULL (a store that
  *      freed its row-by-row streams), which turns that path off.
- * qmoe_moe_ring_decode: ternary symbols uint8[height, width] of one matrix (a host copy of its
+ * qmoe_moe_paired_decode: ternary symbols uint8[height, width] of one matrix (a host copy of its
  * descriptor) decoded from the copy; status_dev as in qmoe_sub1_decode. */
-#define QMOE_RING_TABLE 40448
+#define QMOE_PAIRED_TABLE 40448
+#define QMOE_PAIRED_TAIL_WORDS 384   /* null words (code QMOE_PAIRED_TABLE - 1 in both halves) the copy must end with */
 typedef struct qmoe_interleaved_store {
   const void *codes;          /* uint32 words, device */
   const int64_t *blk_base;    /* [total_rows / 32 + 1], device */
-  const uint32_t *table;      /* uint32[65536] table_out of qmoe_moe_ring_prepare, device */
-  const uint32_t *ring_table; /* uint32[QMOE_RING_TABLE] ring_table_out of qmoe_moe_ring_prepare, device */
+  const uint32_t *table;      /* uint32[65536] table_out of qmoe_moe_paired_prepare, device */
+  const uint32_t *hot_table; /* uint32[QMOE_PAIRED_TABLE] hot_table_out of qmoe_moe_paired_prepare, device */
 } qmoe_interleaved_store;
 
 int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev /* [65536], added to */,
                              int device, void *stream);
-int qmoe_moe_ring_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
-                          uint32_t *ring_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
+int qmoe_moe_paired_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
+                          uint32_t *hot_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
                           uint16_t *split_codes_out_dev, int64_t split_capacity, int64_t *split_total_out_host,
                           int device, void *stream);
 /* Step 2 with every pointer in host memory (no device involved): the plan itself. */
-int qmoe_moe_ring_plan_host(const int32_t *dec_host, const uint64_t *hist_host, uint32_t *remap_out_host,
-                            uint32_t *ring_table_out_host, uint32_t *table_out_host, uint32_t *split_off_out_host,
+int qmoe_moe_paired_plan_host(const int32_t *dec_host, const uint64_t *hist_host, uint32_t *remap_out_host,
+                            uint32_t *hot_table_out_host, uint32_t *table_out_host, uint32_t *split_off_out_host,
                             uint16_t *split_codes_out_host, int64_t split_capacity, int64_t *split_total_out_host);
-int qmoe_moe_ring_count(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+int qmoe_moe_paired_count(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
                         const qmoe_matrix_desc *descs_host, int n_matrices, const uint32_t *split_off_dev,
                         int32_t *blk_units_dev, int device, void *stream);
-int qmoe_moe_ring_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+int qmoe_moe_paired_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
                        int n_matrices, const int64_t *blk_base_dev, const uint32_t *split_off_dev,
                        const uint16_t *split_codes_dev, void *il_codes_dev, int device, void *stream);
-int qmoe_moe_ring_decode(const qmoe_interleaved_store *store, const qmoe_matrix_desc *desc_host, uint8_t *sym_dev,
+int qmoe_moe_paired_decode(const qmoe_interleaved_store *store, const qmoe_matrix_desc *desc_host, uint8_t *sym_dev,
                          int32_t *status_dev, int device, void *stream);
 int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
                                      const int32_t *row_off_dev, const void *minmax_dev,

@@ -25,7 +25,8 @@ FLAG_RELU = 2
 DICT_COUNT = 65536
 TRIE_ROOT = 65536
 MAX_WIDTH = 8192
-RING_TABLE = 40448
+PAIRED_TABLE = 40448
+PAIRED_TAIL_WORDS = 384
 
 
 class QmoeError(RuntimeError):
@@ -53,7 +54,7 @@ class InterleavedStore(ctypes.Structure):
     """Mirror of ``qmoe_interleaved_store``."""
 
     _fields_ = [("codes", ctypes.c_void_p), ("blk_base", ctypes.c_void_p), ("table", ctypes.c_void_p),
-                ("ring_table", ctypes.c_void_p)]
+                ("hot_table", ctypes.c_void_p)]
 
 
 _P = ctypes.c_void_p
@@ -89,11 +90,11 @@ SIGNATURES = {
     "qmoe_moe_grouped_ffn_rows": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_ep_dispatch": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_plan": (_I, [_P, _L, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
-    "qmoe_moe_ring_prepare": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P, _I, _P]),
-    "qmoe_moe_ring_plan_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P]),
-    "qmoe_moe_ring_count": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _P]),
-    "qmoe_moe_ring_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P]),
-    "qmoe_moe_ring_decode": (_I, [_P, _P, _P, _P, _I, _P]),
+    "qmoe_moe_paired_prepare": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P, _I, _P]),
+    "qmoe_moe_paired_plan_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P]),
+    "qmoe_moe_paired_count": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _P]),
+    "qmoe_moe_paired_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P]),
+    "qmoe_moe_paired_decode": (_I, [_P, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine_add": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_moe_route_small": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "qmoe_rms_norm": (_I, [_P, _P, _P, _I, _I, ctypes.c_float, _I, _P]),

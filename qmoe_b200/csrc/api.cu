@@ -127,19 +127,19 @@ int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, fl
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
                             int heads, int hd, int max_len, cudaStream_t stream);
 int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream);
-int ring_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
-                 uint32_t *ring_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
+int paired_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
+                 uint32_t *hot_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
                  uint16_t *split_codes_out_dev, int64_t split_capacity, int64_t *split_total_out,
                  cudaStream_t stream);
-int ring_plan_host(const int32_t *dec, const uint64_t *hist, uint32_t *remap_out, uint32_t *ring_table_out,
+int paired_plan_host(const int32_t *dec, const uint64_t *hist, uint32_t *remap_out, uint32_t *hot_table_out,
                    uint32_t *table_out, uint32_t *split_off_out, uint16_t *split_codes_out, int64_t split_capacity,
                    int64_t *split_total_out);
-int launch_ring_count(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+int launch_paired_count(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
                       const uint32_t *split_off, int32_t *blk_units, cudaStream_t stream);
-int launch_ring_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+int launch_paired_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
                      const int64_t *blk_base, const uint32_t *split_off, const uint16_t *split_codes, void *il,
                      cudaStream_t stream);
-int launch_ring_decode(const uint32_t *ring_table, const void *il, const int64_t *blk_base,
+int launch_paired_decode(const uint32_t *hot_table, const void *il, const int64_t *blk_base,
                        const qmoe_matrix_desc &desc, uint8_t *sym, int32_t *status, cudaStream_t stream);
 int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
                         cudaStream_t stream);
@@ -521,7 +521,7 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     set_error("%s: d_model/d_ff exceed QMOE_MAX_WIDTH (%d)", fn, QMOE_MAX_WIDTH);
     return QMOE_ERR_UNSUPPORTED;
   }
-  if (ils && !(ils->codes && ils->blk_base && ils->table && ils->ring_table)) {
+  if (ils && !(ils->codes && ils->blk_base && ils->table && ils->hot_table)) {
     set_error("%s: null pointer in the interleaved store", fn);
     return QMOE_ERR_INVALID_ARG;
   }
@@ -539,7 +539,7 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     return QMOE_ERR_INVALID_ARG;
   }
   if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 ||
-      (ils && ((reinterpret_cast<uintptr_t>(ils->codes) | reinterpret_cast<uintptr_t>(ils->ring_table)) & 15u) != 0)) {
+      (ils && ((reinterpret_cast<uintptr_t>(ils->codes) | reinterpret_cast<uintptr_t>(ils->hot_table)) & 15u) != 0)) {
     set_error("%s: code stores must be 16-byte aligned", fn);
     return QMOE_ERR_INVALID_ARG;
   }
@@ -636,32 +636,32 @@ int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_
   return launch_code_histogram(codes_dev, n_codes, hist_dev, as_stream(stream));
 }
 
-int qmoe_moe_ring_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
-                          uint32_t *ring_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
+int qmoe_moe_paired_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
+                          uint32_t *hot_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
                           uint16_t *split_codes_out_dev, int64_t split_capacity, int64_t *split_total_out_host,
                           int device, void *stream) {
-  QMOE_REQUIRE(dec_dev && hist_dev && remap_out_dev && ring_table_out_dev && table_out_dev && split_off_out_dev &&
+  QMOE_REQUIRE(dec_dev && hist_dev && remap_out_dev && hot_table_out_dev && table_out_dev && split_off_out_dev &&
                    split_codes_out_dev && split_total_out_host,
                "null pointer");
   QMOE_REQUIRE(split_capacity >= QMOE_DICT_COUNT, "split_capacity must be at least 65536");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return ring_prepare(dec_dev, hist_dev, remap_out_dev, ring_table_out_dev, table_out_dev, split_off_out_dev,
+  return paired_prepare(dec_dev, hist_dev, remap_out_dev, hot_table_out_dev, table_out_dev, split_off_out_dev,
                       split_codes_out_dev, split_capacity, split_total_out_host, as_stream(stream));
 }
 
-int qmoe_moe_ring_plan_host(const int32_t *dec_host, const uint64_t *hist_host, uint32_t *remap_out_host,
-                            uint32_t *ring_table_out_host, uint32_t *table_out_host, uint32_t *split_off_out_host,
+int qmoe_moe_paired_plan_host(const int32_t *dec_host, const uint64_t *hist_host, uint32_t *remap_out_host,
+                            uint32_t *hot_table_out_host, uint32_t *table_out_host, uint32_t *split_off_out_host,
                             uint16_t *split_codes_out_host, int64_t split_capacity, int64_t *split_total_out_host) {
-  QMOE_REQUIRE(dec_host && hist_host && remap_out_host && ring_table_out_host && table_out_host &&
+  QMOE_REQUIRE(dec_host && hist_host && remap_out_host && hot_table_out_host && table_out_host &&
                    split_off_out_host && split_codes_out_host && split_total_out_host,
                "null pointer");
   QMOE_REQUIRE(split_capacity >= QMOE_DICT_COUNT, "split_capacity must be at least 65536");
-  return ring_plan_host(dec_host, hist_host, remap_out_host, ring_table_out_host, table_out_host,
+  return paired_plan_host(dec_host, hist_host, remap_out_host, hot_table_out_host, table_out_host,
                         split_off_out_host, split_codes_out_host, split_capacity, split_total_out_host);
 }
 
-int qmoe_moe_ring_count(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+int qmoe_moe_paired_count(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
                         const qmoe_matrix_desc *descs_host, int n_matrices, const uint32_t *split_off_dev,
                         int32_t *blk_units_dev, int device, void *stream) {
   QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && descs_host && split_off_dev && blk_units_dev, "null pointer");
@@ -676,11 +676,11 @@ int qmoe_moe_ring_count(const uint16_t *codes_dev, const int32_t *row_off_dev, c
   }
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_ring_count(codes_dev, row_off_dev, descs_dev, n_matrices, split_off_dev, blk_units_dev,
+  return launch_paired_count(codes_dev, row_off_dev, descs_dev, n_matrices, split_off_dev, blk_units_dev,
                            as_stream(stream));
 }
 
-int qmoe_moe_ring_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+int qmoe_moe_paired_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
                        int n_matrices, const int64_t *blk_base_dev, const uint32_t *split_off_dev,
                        const uint16_t *split_codes_dev, void *il_codes_dev, int device, void *stream) {
   QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && blk_base_dev && split_off_dev && split_codes_dev &&
@@ -690,20 +690,20 @@ int qmoe_moe_ring_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, co
   QMOE_REQUIRE((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) == 0, "the copy must be 16-byte aligned");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_ring_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, split_off_dev,
+  return launch_paired_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, split_off_dev,
                           split_codes_dev, il_codes_dev, as_stream(stream));
 }
 
-int qmoe_moe_ring_decode(const qmoe_interleaved_store *store, const qmoe_matrix_desc *desc_host, uint8_t *sym_dev,
+int qmoe_moe_paired_decode(const qmoe_interleaved_store *store, const qmoe_matrix_desc *desc_host, uint8_t *sym_dev,
                          int32_t *status_dev, int device, void *stream) {
   QMOE_REQUIRE(store && desc_host && sym_dev, "null pointer");
-  QMOE_REQUIRE(store->codes && store->blk_base && store->ring_table, "null pointer in the store");
+  QMOE_REQUIRE(store->codes && store->blk_base && store->hot_table, "null pointer in the store");
   QMOE_REQUIRE(desc_host->height >= 1 && desc_host->width >= 1 && desc_host->height % 32 == 0 &&
                    desc_host->minmax_base % 32 == 0,
                "bad matrix descriptor");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_ring_decode(store->ring_table, store->codes, store->blk_base, *desc_host, sym_dev, status_dev,
+  return launch_paired_decode(store->hot_table, store->codes, store->blk_base, *desc_host, sym_dev, status_dev,
                             as_stream(stream));
 }
 

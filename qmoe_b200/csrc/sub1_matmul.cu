@@ -15,9 +15,10 @@
 //  * a work list of (matrix, row block, token group) items lets one launch cover every active
 //    expert of a MoE layer;
 //  * stores that carry a paired-lane copy of their streams run the layer's bulk through the kernel
-//    of sub1_ring.cu (conflict-free gathers from a lane-private activation window); the kernels of
-//    this file then take what that kernel leaves: rows beyond a matrix's last 1024-row block and
-//    steps with very few active experts (one row per WARP), and stores without such a copy.
+//    of sub1_paired.cu (re-tokenised streams, the whole table in shared memory, a leaner inner
+//    loop); the kernels of this file then take what that kernel leaves: rows beyond a matrix's last
+//    1024-row block and steps with very few active experts (one row per WARP), and stores without
+//    such a copy.
 #include "common.cuh"
 #include "sub1_walk.cuh"
 
@@ -422,7 +423,7 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
   }
 }
 
-// The same for a work item of a store with paired-lane streams (sub1_ring.cu): code i of row l of
+// The same for a work item of a store with paired-lane streams (sub1_paired.cu): code i of row l of
 // a 32-row block is half i % 2 of the word (i / 2) * 32 + l; every row of a block has the block's
 // number of words, padded with a code whose entry is null.
 template <int T, class SinkT, int G>
@@ -508,7 +509,7 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
 }
 
 // Work items of a store with paired-lane streams whose rows are shared out one per WARP: the rows
-// that are left when a matrix's height is not a multiple of the 1024 rows a CTA of the ring kernel
+// that are left when a matrix's height is not a multiple of the 1024 rows a CTA of k_matmul_paired
 // takes, and whole layers when so few experts are active (one token per step while generating) that
 // rows per thread could not fill the GPU.  Several CTAs per SM; the table is read through L1/L2.
 // G: groups of 32 codes per round of a row.  A row of w weights has about w / 23 codes; the host
@@ -716,9 +717,9 @@ int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cuda
 //  * Stores without a paired-lane copy: groups of up to four tokens, every matrix cut into equal
 //    items of at most 1024 rows for k_matmul_grouped (finer when there are few pairs, until there
 //    are about two items per SM).
-//  * Stores with a paired-lane copy: groups of up to two tokens (the activation window of the ring
-//    kernel holds one 4-byte word per column).  Rows up to the last multiple of 1024 go to the ring
-//    kernel in c equal items per pair, c chosen so that the items fill whole rounds of the SMs as
+//  * Stores with a paired-lane copy: groups of up to four tokens as well.  Rows up to the last
+//    multiple of 1024 go to k_matmul_paired in c equal items per pair, c chosen so that the items
+//    fill whole rounds of the SMs as
 //    well as they can (190 pairs x 2 items over 148 SMs would be 2.6 rounds that cost 3); a remainder
 //    of at most 256 rows (2080 = 2 x 1024 + 32) goes to k_matmul_grouped_warp, one row per warp; and
 //    when so few pairs exist (one token per step while generating) that rows per thread could not
@@ -728,8 +729,7 @@ constexpr int kWarpItemRows = 8;             // one row per warp of a k_matmul_g
 constexpr int kWarpRemainderMax = 256;      // most rows of a matrix that are left to the warp kernel
 constexpr int kSmallRows = 148 * 8 * 32;    // fewer rows in total (less than eight warps of rows per SM):
                                             // the warp kernel takes all of them
-constexpr int kRingGroup = 2;               // tokens decoded together by the ring kernel
-constexpr int kItemOverheadRows = 96;       // fixed cost of a ring item, in rows of work (window fill, barriers)
+constexpr int kItemOverheadRows = 64;       // fixed cost of a work item, in rows of work (staging the activations)
 
 struct WorkPhase {
   int4 *items;
@@ -741,13 +741,13 @@ struct WorkPhase {
 };
 
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
-                                                     int max_slots, int tile_min, int sms, int ring,
+                                                     int max_slots, int tile_min, int sms, int paired,
                                                      int *header, WorkPhase p0, WorkPhase p1) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_total;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int group = ring ? kRingGroup : kMaxGroup;
+  const int group = kMaxGroup;
   auto group_count = [&](int e, int &first, int &count) {
     first = 0;
     count = 0;
@@ -777,9 +777,9 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
     const int H = p.height;
     // rows [0, main_rows) in items of rpc rows for the per-thread kernel, the rest in warp items
     int rpc = rows_per_chunk_dev(H, kGroupedThreads), main_rows = H;
-    if (ring && (long long)total * H <= kSmallRows) {
+    if (paired && (long long)total * H <= kSmallRows) {
       main_rows = 0;
-    } else if (ring && total > 0) {
+    } else if (paired && total > 0) {
       const int rest = H % kGroupedThreads;
       if (H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) main_rows = H - rest;
       const int c0 = (main_rows + kGroupedThreads - 1) / kGroupedThreads;
@@ -804,7 +804,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       if (fine < rpc && (long long)total * ((H + fine - 1) / fine) <= p.capacity) rpc = fine;  // few pairs
     }
     const int chunks = (main_rows + rpc - 1) / rpc;
-    const int wchunks = ring ? (H - main_rows + kWarpItemRows - 1) / kWarpItemRows : 0;
+    const int wchunks = paired ? (H - main_rows + kWarpItemRows - 1) / kWarpItemRows : 0;
     if (tid == 0) s_base = 0;
     __syncthreads();
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
@@ -951,11 +951,11 @@ int work_summary(const void *work, int32_t *out, cudaStream_t stream) {
   return QMOE_OK;
 }
 
-// The ring kernel of sub1_ring.cu.
-int launch_ring_phase(const uint32_t *ring_table, const void *il, const int64_t *blk_base, const void *minmax,
+// The kernel of sub1_paired.cu.
+int launch_paired_phase(const uint32_t *hot_table, const void *il, const int64_t *blk_base, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
                       const int32_t *x_rows, const int32_t *y_rows, const int4 *items, int *header, int flags,
-                      int device, cudaStream_t stream);
+                      int width, int device, cudaStream_t stream);
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
@@ -1034,14 +1034,14 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
     if (il) {
       if ((long long)max_slots * height > kSmallRows) {  // smaller steps go to the warp kernel whole
-        rc = launch_ring_phase(ils->ring_table, ils->codes, ils->blk_base, minmax, descs, a.x, a.y, a.x_stride,
-                               a.y_stride, a.x_rows, a.y_rows, a.items, a.header, a.flags, device, stream);
+        rc = launch_paired_phase(ils->hot_table, ils->codes, ils->blk_base, minmax, descs, a.x, a.y, a.x_stride,
+                               a.y_stride, a.x_rows, a.y_rows, a.items, a.header, a.flags, width, device, stream);
         if (rc) return rc;
       }
       MatmulArgs w = a;
       w.items = ph[phase].warp_items;
       w.header = header + 10 + 2 * phase;
-      const size_t wsmem = grouped_x_bytes(width, kRingGroup);
+      const size_t wsmem = grouped_x_bytes(width, kMaxGroup);
       int per_sm = (int)(kSmemPerCta / (wsmem + 1024));  // CTAs of 256 threads that fit one SM
       per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
       const unsigned wgrid = (unsigned)(per_sm * sms);

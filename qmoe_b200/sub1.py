@@ -162,7 +162,7 @@ class ExpertStore:
         """Build the paired-lane copy of the code streams that the grouped kernel reads (layout in
         include/qmoe_sub1.h): two codes per word, the words of the 32 rows of a block side by side,
         code values renumbered by decreasing frequency, and every code outside the most frequent
-        ``RING_TABLE - 1`` replaced by frequent codes that spell the same weights, so that the kernel
+        ``PAIRED_TABLE - 1`` replaced by frequent codes that spell the same weights, so that the kernel
         serves every lookup from shared memory.  One-time cost when a store is created.  A decoder
         table the kernel cannot serve (an entry with more than three non-zeros) leaves the store
         without a copy; it then runs on its row-by-row streams."""
@@ -175,13 +175,13 @@ class ExpertStore:
         n = min(last.code_base + last.n_codes, self.codes.numel())
         _lib.check(L.qmoe_sub1_code_histogram(self.codes.data_ptr(), n, hist.data_ptr(), dev.index, _s(dev)))
         remap = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
-        ring_table = torch.empty(_lib.RING_TABLE, dtype=torch.int32, device=dev)
+        hot_table = torch.empty(_lib.PAIRED_TABLE, dtype=torch.int32, device=dev)
         table = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
         split_off = torch.empty(_lib.DICT_COUNT + 1, dtype=torch.int32, device=dev)
         split_cap = 14 * _lib.DICT_COUNT                                    # a code is at most 14 pairs
         split_codes = torch.empty(split_cap, dtype=torch.int16, device=dev)
         total = ctypes.c_int64(0)
-        rc = L.qmoe_moe_ring_prepare(dec.data_ptr(), hist.data_ptr(), remap.data_ptr(), ring_table.data_ptr(),
+        rc = L.qmoe_moe_paired_prepare(dec.data_ptr(), hist.data_ptr(), remap.data_ptr(), hot_table.data_ptr(),
                                      table.data_ptr(), split_off.data_ptr(), split_codes.data_ptr(), split_cap,
                                      ctypes.byref(total), dev.index, _s(dev))
         if rc == _lib.ERR_UNSUPPORTED:
@@ -190,22 +190,24 @@ class ExpertStore:
         split_codes = split_codes[:int(total.value)].clone()
         rows = sum(d.height for d in self.host_descs)
         units = torch.empty(rows // 32, dtype=torch.int32, device=dev)
-        _lib.check(L.qmoe_moe_ring_count(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
+        _lib.check(L.qmoe_moe_paired_count(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
                                          ctypes.addressof(self._desc_array), n_mat, split_off.data_ptr(),
                                          units.data_ptr(), dev.index, _s(dev)))
         base = torch.zeros(rows // 32 + 1, dtype=torch.int64, device=dev)
         base[1:] = torch.cumsum(units, 0, dtype=torch.int64)
         words = int(base[-1].item())
-        il = torch.empty(max((words + 3) // 4, 1) * 4, dtype=torch.int32, device=dev)
-        _lib.check(L.qmoe_moe_ring_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
+        # the kernel reads its stream a few words ahead without a range test: null words at the end
+        null_word = (_lib.PAIRED_TABLE - 1) | ((_lib.PAIRED_TABLE - 1) << 16)
+        il = torch.full((words + _lib.PAIRED_TAIL_WORDS,), null_word - (1 << 32), dtype=torch.int32, device=dev)
+        _lib.check(L.qmoe_moe_paired_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
                                         n_mat, base.data_ptr(), split_off.data_ptr(), split_codes.data_ptr(),
                                         il.data_ptr(), dev.index, _s(dev)))
         self.remap, self.split_off, self.split_codes = remap, split_off, split_codes
-        self.il_table, self.ring_table = table, ring_table
+        self.il_table, self.hot_table = table, hot_table
         self.il_codes, self.blk_base = il, base
         self.il_words = words
         self.il_struct = _lib.InterleavedStore(il.data_ptr(), base.data_ptr(), table.data_ptr(),
-                                               ring_table.data_ptr())
+                                               hot_table.data_ptr())
 
     def decode_copy(self, m: int, return_status: bool = False):
         """Ternary symbols ``uint8[height, width]`` of matrix ``m`` decoded from the paired-lane copy
@@ -216,7 +218,7 @@ class ExpertStore:
         dev = self.device
         sym = torch.empty((d.height, d.width), dtype=torch.uint8, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
-        _lib.check(_lib.load().qmoe_moe_ring_decode(ctypes.addressof(self.il_struct), ctypes.byref(d), sym.data_ptr(),
+        _lib.check(_lib.load().qmoe_moe_paired_decode(ctypes.addressof(self.il_struct), ctypes.byref(d), sym.data_ptr(),
                                                     status.data_ptr(), dev.index, _s(dev)))
         return (sym, int(status.item())) if return_status else sym
 
@@ -227,7 +229,7 @@ class ExpertStore:
         if self.codes is not None:
             total += self.codes.numel() * 2
         if self.il_codes is not None:
-            total += self.il_codes.numel() * 4 + self.blk_base.numel() * 8 + 4 * (_lib.DICT_COUNT + _lib.RING_TABLE)
+            total += self.il_codes.numel() * 4 + self.blk_base.numel() * 8 + 4 * (_lib.DICT_COUNT + _lib.PAIRED_TABLE)
         return total
 
     def drop_reference_layout(self) -> None:

@@ -2,8 +2,8 @@
 
 ``bench.py`` times a switch-c-2048 layer: d_model 2080, d_ff 6144, hundreds of active experts with
 one to a few tokens each.  With that many (expert, token group) pairs the work list cuts every matrix
-into items of up to 1024 rows for the persistent ring kernel (one row per thread, groups of one or
-two tokens); ``wo`` has 2080 = 2 * 1024 + 32 rows, so its last 32 rows are not part of such an item
+into items of up to 1024 rows for the persistent row-per-thread kernel (groups of one to four
+tokens); ``wo`` has 2080 = 2 * 1024 + 32 rows, so its last 32 rows are not part of such an item
 and are done one row per warp by a second kernel.  No small layer and no single expert reaches
 that combination, so this file runs a SLICE of the benchmark's layer: 160 experts of the real
 shape, 300 uniformly routed tokens (one to six tokens per active expert).
@@ -83,8 +83,8 @@ def test_switch_c_2048_slice_grouped_path_against_the_oracle():
     # all rows of wi, and the 32 remainder rows of wo (2080 = 2 * 1024 + 32) in four 8-row warp items
     plan = sub1.work_plan(work)
     counts = torch.bincount(choice.cpu().long(), minlength=N_EXPERTS)
-    assert plan["group_tokens"] == 2
-    groups = int(sum((int(c) + 1) // 2 for c in counts))
+    assert plan["group_tokens"] == 4
+    groups = int(sum((int(c) + 3) // 4 for c in counts))
     assert plan["wi_items"] >= groups * (d_ff // 1024) and plan["wi_items"] % groups == 0
     assert plan["wo_items"] >= groups * (d_model // 1024) and plan["wo_items"] % groups == 0
     assert 32 <= plan["wi_rows_per_item"] <= 1024 and 32 <= plan["wo_rows_per_item"] <= 1024

@@ -146,7 +146,7 @@ def test_paired_lane_copy_decodes_to_the_same_weights(dev, small_layer):
     # layout: two codes per word, every code below the table size, rows padded with the null code
     words = store.il_codes[:store.il_words].cpu().numpy().view(np.uint32)
     lo, hi = words & 0xffff, words >> 16
-    assert int(max(lo.max(), hi.max())) <= _lib.RING_TABLE - 1
+    assert int(max(lo.max(), hi.max())) <= _lib.PAIRED_TABLE - 1
     base = store.blk_base.cpu().numpy()
     assert base[0] == 0 and base[-1] == store.il_words and ((base[1:] - base[:-1]) % 32 == 0).all()
     # the replacement lists spell every code: frequent codes map to themselves
@@ -154,7 +154,7 @@ def test_paired_lane_copy_decodes_to_the_same_weights(dev, small_layer):
     remap = store.remap.cpu().numpy().view(np.uint32)
     pieces = store.split_codes.cpu().numpy().view(np.uint16)
     single = (off[1:] - off[:-1]) == 1
-    assert single.sum() == _lib.RING_TABLE - 1 and (pieces[off[:-1][single]] == remap[single]).all()
+    assert single.sum() == _lib.PAIRED_TABLE - 1 and (pieces[off[:-1][single]] == remap[single]).all()
     assert ((off[1:] - off[:-1])[~single] >= 2).all()
 
 
@@ -181,10 +181,11 @@ def test_paired_lane_and_row_by_row_stores_give_identical_results(dev, small_lay
     assert rel_err(got[:counts[0]], experts[0].oracle_ffn(xs[:counts[0]].cpu())) <= TOL
 
 
-def test_ring_kernel_on_a_layer_large_enough_for_it(dev):
+def test_paired_lane_kernel_on_a_layer_large_enough_for_it(dev):
     """Small layers run on the row-per-warp kernel; this one (96 experts of 1056 x 384) has enough
-    rows for the ring kernel: wi in items of up to 1024 rows plus a 32-row remainder for the warps, wo
-    in items of up to 384 rows, one- and two-token groups, experts without tokens, against the oracle."""
+    rows for the row-per-thread kernel: wi in items of up to 1024 rows plus a 32-row remainder for the
+    warps, wo in items of up to 384 rows, groups of one to four tokens, experts without tokens,
+    against the oracle."""
     d_model, d_ff, n_exp = 384, 1056, 96
     experts = [Expert(d_model, d_ff, seed=2, expert_id=e) for e in range(n_exp)]
     store = store_from_experts(experts, dev)
@@ -198,8 +199,8 @@ def test_ring_kernel_on_a_layer_large_enough_for_it(dev):
     work = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
     ys = sub1.grouped_ffn(store, offsets, xs.to(dev), n, work=work)
     plan = sub1.work_plan(work)
-    groups = sum((c + 1) // 2 for c in counts)
-    assert plan["group_tokens"] == 2 and plan["wi_items"] >= groups and plan["wi_warp_items"] == groups * 4
+    groups = sum((c + 3) // 4 for c in counts)
+    assert plan["group_tokens"] == 4 and plan["wi_items"] >= groups and plan["wi_warp_items"] == groups * 4
     assert plan["wo_items"] >= groups and plan["wo_warp_items"] == 0
     plain = _plain_copy(store, interleave=False)
     ys_plain = sub1.grouped_ffn(plain, offsets, xs.to(dev), n)
