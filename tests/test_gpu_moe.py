@@ -182,11 +182,11 @@ def test_paired_lane_and_row_by_row_stores_give_identical_results(dev, small_lay
 
 
 def test_paired_lane_kernel_on_a_layer_large_enough_for_it(dev):
-    """Small layers run on the row-per-warp kernel; this one (96 experts of 1056 x 384) has enough
+    """Small layers run on the row-per-warp kernel; this one (96 experts of 1056 x 640) has enough
     rows for the row-per-thread kernel: wi in items of up to 1024 rows plus a 32-row remainder for the
-    warps, wo in items of up to 384 rows, groups of one to four tokens, experts without tokens,
+    warps, wo in items of up to 640 rows, groups of one to four tokens, experts without tokens,
     against the oracle."""
-    d_model, d_ff, n_exp = 384, 1056, 96
+    d_model, d_ff, n_exp = 640, 1056, 96
     experts = [Expert(d_model, d_ff, seed=2, expert_id=e) for e in range(n_exp)]
     store = store_from_experts(experts, dev)
     assert store.il_codes is not None
