@@ -22,8 +22,9 @@
 //    divergence and no per-code bounds test;
 //  * a table entry is laid out so that every field costs two or three instructions: the digits of
 //    its (at most three) non-zeros are 2-bit fields that one multiply-add turns into the selector of
-//    a byte permute, which picks the row's min, its max or zero out of the packed bf16 pair -- no
-//    flag tests, no selects, no predicates in the inner loop.
+//    a byte permute, which picks the row's min or max out of the packed bf16 pair, and one compare
+//    of the same field predicates the gather and its multiply-adds away where there is no non-zero
+//    (a gather that is not issued cannot collide with another lane's in a shared-memory bank).
 //
 // The copy decodes to exactly the same weights as the reference's streams (tested bit for bit); the
 // reference's tensors stay what the C ABI takes and what checkpoints hold.
@@ -405,13 +406,54 @@ __device__ __forceinline__ uint32_t clamp_codes(uint32_t w) {
   return r;
 }
 
+// One non-zero slot of a code: if the slot's digit field `d` differs from `none` (the field's value
+// for "no non-zero"), gather the activations at `addr` and add weight * activation to the sums.
+// Gather and multiply-adds are predicated together: a slot without a non-zero costs no shared-memory
+// bandwidth (and no bank conflicts), which matters because that pipe is the busiest unit of the SM.
+template <uint32_t NONE>
+__device__ __forceinline__ void paired_slot1(float &a0, float w, uint32_t addr, uint32_t d) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .f32 v;\n\t"
+      "setp.ne.u32 p, %3, %4;\n\t"
+      "@p ld.shared.f32 v, [%2];\n\t"
+      "@p fma.rn.f32 %0, %1, v, %0;\n\t}"
+      : "+f"(a0) : "f"(w), "r"(addr), "r"(d), "n"(NONE));
+}
+template <uint32_t NONE>
+__device__ __forceinline__ void paired_slot2(float &a0, float &a1, float w, uint32_t addr, uint32_t d) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b32 v, lo, hi;\n\t"
+      "setp.ne.u32 p, %4, %5;\n\t"
+      "@p ld.shared.b32 v, [%3];\n\t"
+      "@p shl.b32 lo, v, 16;\n\t"
+      "@p and.b32 hi, v, 0xffff0000;\n\t"
+      "@p fma.rn.f32 %0, %2, lo, %0;\n\t"
+      "@p fma.rn.f32 %1, %2, hi, %1;\n\t}"
+      : "+f"(a0), "+f"(a1) : "f"(w), "r"(addr), "r"(d), "n"(NONE));
+}
+template <uint32_t NONE>
+__device__ __forceinline__ void paired_slot4(float &a0, float &a1, float &a2, float &a3, float w, uint32_t addr,
+                                             uint32_t d) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b32 v0, v1, t0, t1, t2, t3;\n\t"
+      "setp.ne.u32 p, %6, %7;\n\t"
+      "@p ld.shared.v2.b32 {v0, v1}, [%5];\n\t"
+      "@p shl.b32 t0, v0, 16;\n\t"
+      "@p and.b32 t1, v0, 0xffff0000;\n\t"
+      "@p shl.b32 t2, v1, 16;\n\t"
+      "@p and.b32 t3, v1, 0xffff0000;\n\t"
+      "@p fma.rn.f32 %0, %4, t0, %0;\n\t"
+      "@p fma.rn.f32 %1, %4, t1, %1;\n\t"
+      "@p fma.rn.f32 %2, %4, t2, %2;\n\t"
+      "@p fma.rn.f32 %3, %4, t3, %3;\n\t}"
+      : "+f"(a0), "+f"(a1), "+f"(a2), "+f"(a3) : "f"(w), "r"(addr), "r"(d), "n"(NONE));
+}
+
 // One code for T tokens.  pa: shared-memory address of the activations at the row's position
 // (advanced by the code's width); mm: the row's (min, max) as packed bf16; acc: fp32 sums.
 // Per non-zero: its position (a masked field, already scaled to bytes), one gather, the weight
-// {min, max, 0} picked by a byte permute whose selector is digit * 0x2200 + 0x1044, and one
-// multiply-add per token (the reference's fp32 multiply-add per weight, sub1_cuda_kernel.cu:188-192;
-// a slot without a non-zero multiplies whatever it gathered by zero, as the reference does with
-// every zero weight).
+// {min, max} picked by a byte permute whose selector is digit * 0x2200 + 0x1044, and one
+// multiply-add per token (the reference's fp32 multiply-add per weight, sub1_cuda_kernel.cu:188-192).
 template <int T>
 __device__ __forceinline__ void paired_code(uint32_t e, uint32_t &pa, uint32_t mm, float (&acc)[T]) {
   constexpr int kBytes = T == 4 ? 8 : 4;               // bytes per column in shared memory
@@ -425,27 +467,22 @@ __device__ __forceinline__ void paired_code(uint32_t e, uint32_t &pa, uint32_t m
     off[1] = (e >> 8) & 0xf8u;
     off[2] = (e >> 13) & 0xf8u;
   }
-  const uint32_t sel0 = (e & 3u) * 0x2200u + 0x1044u;
-  const uint32_t sel1 = (e & 0x180u) * 0x44u + 0x1044u;
-  const uint32_t sel2 = (e & 0x600u) * 0x11u + 0x1044u;
-  const float w[3] = {__uint_as_float(__byte_perm(mm, 0u, sel0)), __uint_as_float(__byte_perm(mm, 0u, sel1)),
-                      __uint_as_float(__byte_perm(mm, 0u, sel2))};
-#pragma unroll
-  for (int k = 0; k < 3; k++) {
-    if (T == 1) {
-      acc[0] = fmaf(w[k], __uint_as_float(lds_u32(pa + off[k])), acc[0]);
-    } else if (T == 2) {
-      const uint32_t v = lds_u32(pa + off[k]);
-      acc[0] = fmaf(w[k], __uint_as_float(v << 16), acc[0]);
-      acc[1] = fmaf(w[k], __uint_as_float(v & 0xffff0000u), acc[1]);
-    } else {
-      uint32_t lo, hi;
-      lds_u64(pa + off[k], lo, hi);
-      acc[0] = fmaf(w[k], __uint_as_float(lo << 16), acc[0]);
-      acc[1] = fmaf(w[k], __uint_as_float(lo & 0xffff0000u), acc[1]);
-      acc[2] = fmaf(w[k], __uint_as_float(hi << 16), acc[2]);
-      acc[3] = fmaf(w[k], __uint_as_float(hi & 0xffff0000u), acc[3]);
-    }
+  const uint32_t d0 = e & 3u, d1 = e & 0x180u, d2 = e & 0x600u;   // digit fields in place; "none" = 2, 0x100, 0x400
+  const float w0 = __uint_as_float(__byte_perm(mm, 0u, d0 * 0x2200u + 0x1044u));
+  const float w1 = __uint_as_float(__byte_perm(mm, 0u, d1 * 0x44u + 0x1044u));
+  const float w2 = __uint_as_float(__byte_perm(mm, 0u, d2 * 0x11u + 0x1044u));
+  if constexpr (T == 1) {
+    paired_slot1<2u>(acc[0], w0, pa + off[0], d0);
+    paired_slot1<0x100u>(acc[0], w1, pa + off[1], d1);
+    paired_slot1<0x400u>(acc[0], w2, pa + off[2], d2);
+  } else if constexpr (T == 2) {
+    paired_slot2<2u>(acc[0], acc[1], w0, pa + off[0], d0);
+    paired_slot2<0x100u>(acc[0], acc[1], w1, pa + off[1], d1);
+    paired_slot2<0x400u>(acc[0], acc[1], w2, pa + off[2], d2);
+  } else {
+    paired_slot4<2u>(acc[0], acc[1], acc[2], acc[3], w0, pa + off[0], d0);
+    paired_slot4<0x100u>(acc[0], acc[1], acc[2], acc[3], w1, pa + off[1], d1);
+    paired_slot4<0x400u>(acc[0], acc[1], acc[2], acc[3], w2, pa + off[2], d2);
   }
   pa += kBytes == 4 ? ((e >> 19) & 0x7cu) : ((e >> 18) & 0xf8u);
 }
@@ -454,7 +491,7 @@ __device__ __forceinline__ void paired_code(uint32_t e, uint32_t &pa, uint32_t m
 // per thread.  xs: T activations per column in shared memory (T = 1: fp32; T = 2, 4: bf16), followed
 // by kPairedPad zero columns.
 template <int T>
-__device__ __forceinline__ void paired_item(const PairedArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
+__device__ __noinline__ void paired_item(const PairedArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
                                           int tok0, int ntok, uint32_t tab_addr, uint32_t *xs) {
   constexpr int kBytes = T == 4 ? 8 : 4;
   const int tid = threadIdx.x, lane = tid & 31;
@@ -506,7 +543,9 @@ __device__ __forceinline__ void paired_item(const PairedArgs &a, const qmoe_matr
       e1 = lds_u32(tab_addr + ((w0 >> 16) << 2));
     }
     const uint32_t *wnext = wp + 96;
-#pragma unroll 3
+    // one-token items have registers to spare: unrolling by three lets the word registers rotate
+    // without copies
+#pragma unroll(T == 1 ? 3 : 1)
     for (int k = 0; k < n_words; k++) {
       const uint32_t w = w1;
       w1 = w2;
