@@ -543,9 +543,7 @@ __device__ __noinline__ void paired_item(const PairedArgs &a, const qmoe_matrix_
       e1 = lds_u32(tab_addr + ((w0 >> 16) << 2));
     }
     const uint32_t *wnext = wp + 96;
-    // one-token items have registers to spare: unrolling by three lets the word registers rotate
-    // without copies
-#pragma unroll(T == 1 ? 3 : 1)
+#pragma unroll 1
     for (int k = 0; k < n_words; k++) {
       const uint32_t w = w1;
       w1 = w2;
