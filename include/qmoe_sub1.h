@@ -188,79 +188,59 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
 int qmoe_moe_set_tile_min_tokens(int tokens);
 
 /* Host read-back (synchronises `stream`) of what the last qmoe_moe_grouped_ffn call that used
- * work_dev planned, for tests and reports.  out_host int32[9]: [0] / [1] row-per-thread work items
- * of wi / wo, [2] / [3] row-per-warp work items of wi / wo, [4] / [5] rows per row-per-thread item
- * of wi / wo, [6] / [7] tensor-core tile items of wi / wo, [8] tokens decoded together.  No
- * counterpart in the reference (one launch per token and matrix, sub1.py:139-142). */
-int qmoe_moe_work_summary(const void *work_dev, int32_t *out_host, int device, void *stream);
+ * work_dev planned, for tests and reports; max_slots / d_ff as in that call.  out_host int32[10]:
+ * [0] / [1] row-per-thread work items of wi / wo, [2] / [3] row-per-warp work items of wi / wo,
+ * [4] / [5] rows per row-per-thread item of wi / wo, [6] / [7] tensor-core tile items of wi / wo,
+ * [8] tokens decoded together, [9] wo items whose CTA also does the remainder rows of its matrix
+ * (a height that is not a multiple of 1024) one row per warp.  No counterpart in the reference
+ * (one launch per token and matrix, sub1.py:139-142). */
+int qmoe_moe_work_summary(const void *work_dev, int max_slots, int d_ff, int32_t *out_host, int device,
+                          void *stream);
 int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
                          const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
                          const int32_t *offsets_dev, const void *xs_dev, void *hs_dev, void *ys_dev,
                          void *work_dev, int n_experts, int max_slots, int d_model, int d_ff,
                          int device, void *stream);
 
-/* Paired-lane copy of a store's code streams, the layout the grouped kernel reads fastest.  No
- * counterpart in the reference, whose kernel (sub1_cuda_kernel.cu:129-202) reads w_comp row by row;
- * the copy decodes to exactly the same weights (qmoe_moe_paired_decode is the check) and is derived
- * on the device when a store is created; the reference's tensors stay what every other entry point
- * and every checkpoint holds.
+/* Lane-interleaved copy of a store's code streams, the layout the grouped kernel reads fastest.
+ * No counterpart in the reference, whose kernel (sub1_cuda_kernel.cu:129-202) reads w_comp row by
+ * row; the copy holds the same codes (optionally renumbered) and decodes to the same weights.
+ * Rows are taken in blocks of 32; chunk k (codes 8k..8k+7) of row l of a block is the 16-byte entry
+ * k * 32 + l of the block, and every row of a block is zero-padded to the block's longest row
+ * rounded up to 8 codes.  Heights must be multiples of 32 and the matrices' rows consecutive
+ * (minmax_base = rows before).
  *
- * Layout: rows are taken in blocks of 32; a 32-bit word holds two codes (low half first); word k of
- * row l of a block is the uint32 at index blk_base[block] + k * 32 + l; every row of a block has the
- * block's number of words, padded with the null code QMOE_PAIRED_TABLE - 1.  Heights must be
- * multiples of 32 and the matrices' rows consecutive (minmax_base = rows before).
- * Numbering: code values are renumbered by decreasing frequency; the QMOE_PAIRED_TABLE - 1 most
- * frequent dictionary entries are served from shared memory, and every other code of the reference
- * stream is replaced by the two or more frequent codes whose pair sequences concatenate to its own
- * (the dictionary contains every prefix and, where it matters, every suffix of its entries), so the
- * kernel never reads the table from global memory.
- *   1. qmoe_sub1_code_histogram over (a sample of) the store's streams;
- *   2. qmoe_moe_paired_prepare: reads dec and the histogram back (synchronises), and writes
- *      remap_out_dev uint32[65536] (code -> new number), hot_table_out_dev uint32[QMOE_PAIRED_TABLE]
- *      (the kernel's table), table_out_dev uint32[65536] (the 4-byte table of the row-per-warp kernel
- *      in the new numbering), split_off_out_dev uint32[65537] and split_codes_out_dev
- *      uint16[split_capacity]: code c of the reference stream becomes
- *      split_codes[split_off[c] .. split_off[c+1]).  QMOE_ERR_UNSUPPORTED when the table has an entry
- *      with more than three non-zeros or a code that cannot be cut that way (the store then runs on
- *      its row-by-row streams);
- *   3. qmoe_moe_paired_count: blk_units_dev int32[total_rows / 32] := words per block * 32
+ * Renumbering: the kernel keeps the first entries of the table in shared memory (as many as the
+ * activations leave room for, 45 000 - 53 000 of the 65 536), so the copy may store remap[code]
+ * instead of code, with remap a permutation that gives frequent codes small numbers
+ * (qmoe_sub1_code_histogram counts them); qmoe_sub1_remap_tables writes the sparse table and the
+ * reference table words in the new order (remap_dev NULL = identity).
+ *   1. qmoe_moe_interleave_count: blk_units_dev int32[total_rows / 32] := 16-byte entries per block
  *      (descs_host: the same descriptors in host memory, for validation);
- *   4. the caller forms blk_base int64[total_rows / 32 + 1], the exclusive prefix sum, and allocates
- *      4 * (blk_base[last] + QMOE_PAIRED_TAIL_WORDS) bytes (16-byte aligned);
- *   5. qmoe_moe_paired_emit fills the first blk_base[last] words; the caller fills the tail with null
- *      words (the kernel reads its stream a few words ahead without a range test);
- *   6. qmoe_moe_grouped_ffn_interleaved is qmoe_moe_grouped_ffn reading the copy.  Experts on the
+ *   2. the caller forms blk_base int64[total_rows / 32 + 1], the exclusive prefix sum, and allocates
+ *      16 * blk_base[last] bytes;
+ *   3. qmoe_moe_interleave_emit fills them;
+ *   4. qmoe_moe_grouped_ffn_interleaved is qmoe_moe_grouped_ffn reading the copy.  Experts on the
  *      tensor-core tile path still read codes_dev with dec_dev; codes_dev may be NULL (a store that
- *      freed its row-by-row streams), which turns that path off.
- * qmoe_moe_paired_decode: ternary symbols uint8[height, width] of one matrix (a host copy of its
- * descriptor) decoded from the copy; status_dev as in qmoe_sub1_decode. */
-#define QMOE_PAIRED_TABLE 40448
-#define QMOE_PAIRED_TAIL_WORDS 384   /* null words (code QMOE_PAIRED_TABLE - 1 in both halves) the copy must end with */
+ *      freed its row-by-row streams), which turns that path off. */
 typedef struct qmoe_interleaved_store {
-  const void *codes;          /* uint32 words, device */
-  const int64_t *blk_base;    /* [total_rows / 32 + 1], device */
-  const uint32_t *table;      /* uint32[65536] table_out of qmoe_moe_paired_prepare, device */
-  const uint32_t *hot_table; /* uint32[QMOE_PAIRED_TABLE] hot_table_out of qmoe_moe_paired_prepare, device */
+  const void *codes;       /* 16-byte entries, device */
+  const int64_t *blk_base; /* [total_rows / 32 + 1], device */
+  const uint32_t *table;   /* uint32[65536] from qmoe_sub1_remap_tables, device */
+  const int32_t *dec;      /* int32[131072] from qmoe_sub1_remap_tables, device */
 } qmoe_interleaved_store;
 
 int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev /* [65536], added to */,
                              int device, void *stream);
-int qmoe_moe_paired_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
-                          uint32_t *hot_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
-                          uint16_t *split_codes_out_dev, int64_t split_capacity, int64_t *split_total_out_host,
-                          int device, void *stream);
-/* Step 2 with every pointer in host memory (no device involved): the plan itself. */
-int qmoe_moe_paired_plan_host(const int32_t *dec_host, const uint64_t *hist_host, uint32_t *remap_out_host,
-                            uint32_t *hot_table_out_host, uint32_t *table_out_host, uint32_t *split_off_out_host,
-                            uint16_t *split_codes_out_host, int64_t split_capacity, int64_t *split_total_out_host);
-int qmoe_moe_paired_count(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
-                        const qmoe_matrix_desc *descs_host, int n_matrices, const uint32_t *split_off_dev,
-                        int32_t *blk_units_dev, int device, void *stream);
-int qmoe_moe_paired_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
-                       int n_matrices, const int64_t *blk_base_dev, const uint32_t *split_off_dev,
-                       const uint16_t *split_codes_dev, void *il_codes_dev, int device, void *stream);
-int qmoe_moe_paired_decode(const qmoe_interleaved_store *store, const qmoe_matrix_desc *desc_host, uint8_t *sym_dev,
-                         int32_t *status_dev, int device, void *stream);
+int qmoe_sub1_remap_tables(const int32_t *dec_dev, const uint32_t *remap_dev /* [65536] or NULL */,
+                           uint32_t *table_out_dev, int32_t *dec_out_dev, int device, void *stream);
+int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                              const qmoe_matrix_desc *descs_host, int n_matrices, int32_t *blk_units_dev,
+                              int device, void *stream);
+int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_dev,
+                             const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
+                             const uint32_t *remap_dev /* [65536] or NULL */, void *il_codes_dev, int device,
+                             void *stream);
 int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
                                      const int32_t *row_off_dev, const void *minmax_dev,
                                      const qmoe_matrix_desc *descs_dev, const qmoe_interleaved_store *store,

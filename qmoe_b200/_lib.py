@@ -25,8 +25,6 @@ FLAG_RELU = 2
 DICT_COUNT = 65536
 TRIE_ROOT = 65536
 MAX_WIDTH = 8192
-PAIRED_TABLE = 40448
-PAIRED_TAIL_WORDS = 384
 
 
 class QmoeError(RuntimeError):
@@ -54,7 +52,7 @@ class InterleavedStore(ctypes.Structure):
     """Mirror of ``qmoe_interleaved_store``."""
 
     _fields_ = [("codes", ctypes.c_void_p), ("blk_base", ctypes.c_void_p), ("table", ctypes.c_void_p),
-                ("hot_table", ctypes.c_void_p)]
+                ("dec", ctypes.c_void_p)]
 
 
 _P = ctypes.c_void_p
@@ -84,23 +82,21 @@ SIGNATURES = {
     "qmoe_moe_unpermute": (_I, [_P, _P, _P, _I, _I, _L, _L, _I, _P]),
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
     "qmoe_moe_set_tile_min_tokens": (_I, [_I]),
-    "qmoe_moe_work_summary": (_I, [_P, _P, _I, _P]),
+    "qmoe_moe_work_summary": (_I, [_P, _I, _I, _P, _I, _P]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_grouped_ffn_rows": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_ep_dispatch": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_plan": (_I, [_P, _L, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
-    "qmoe_moe_paired_prepare": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P, _I, _P]),
-    "qmoe_moe_paired_plan_host": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _P]),
-    "qmoe_moe_paired_count": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _P]),
-    "qmoe_moe_paired_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P]),
-    "qmoe_moe_paired_decode": (_I, [_P, _P, _P, _P, _I, _P]),
+    "qmoe_moe_interleave_count": (_I, [_P, _P, _P, _I, _P, _I, _P]),
+    "qmoe_moe_interleave_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine_add": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_moe_route_small": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "qmoe_rms_norm": (_I, [_P, _P, _P, _I, _I, ctypes.c_float, _I, _P]),
     "qmoe_gemv": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, ctypes.c_float, _I, _I, _P]),
     "qmoe_decode_attention": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "qmoe_sub1_code_histogram": (_I, [_P, _L, _P, _I, _P]),
+    "qmoe_sub1_remap_tables": (_I, [_P, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_launch_count": (_L, []),
     "qmoe_profile_enable": (_I, [_I]),

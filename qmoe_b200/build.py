@@ -20,7 +20,7 @@ INCLUDE = os.path.join(_ROOT, "include")
 LIB_DIR = os.path.join(_PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libqmoe_sub1.so")
 
-SOURCES = ["api.cu", "sub1_matmul.cu", "sub1_paired.cu", "sub1_tile.cu", "sub1_pack.cu", "moe_route.cu", "moe_ep.cu", "decoder_glue.cu"]
+SOURCES = ["api.cu", "sub1_matmul.cu", "sub1_tile.cu", "sub1_pack.cu", "moe_route.cu", "moe_ep.cu", "decoder_glue.cu"]
 HEADERS = ["common.cuh", "sub1_walk.cuh"]
 
 NVCC_FLAGS = [

@@ -102,7 +102,7 @@ int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *co
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
 int set_tile_min_tokens(int tokens);
 int set_tile_wait_limit(uint32_t spins);
-int work_summary(const void *work, int32_t *out, cudaStream_t stream);
+int work_summary(const void *work, int max_slots, int d_ff, int32_t *out, cudaStream_t stream);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
@@ -127,20 +127,13 @@ int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, fl
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
                             int heads, int hd, int max_len, cudaStream_t stream);
 int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream);
-int paired_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
-                 uint32_t *hot_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
-                 uint16_t *split_codes_out_dev, int64_t split_capacity, int64_t *split_total_out,
-                 cudaStream_t stream);
-int paired_plan_host(const int32_t *dec, const uint64_t *hist, uint32_t *remap_out, uint32_t *hot_table_out,
-                   uint32_t *table_out, uint32_t *split_off_out, uint16_t *split_codes_out, int64_t split_capacity,
-                   int64_t *split_total_out);
-int launch_paired_count(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
-                      const uint32_t *split_off, int32_t *blk_units, cudaStream_t stream);
-int launch_paired_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
-                     const int64_t *blk_base, const uint32_t *split_off, const uint16_t *split_codes, void *il,
-                     cudaStream_t stream);
-int launch_paired_decode(const uint32_t *hot_table, const void *il, const int64_t *blk_base,
-                       const qmoe_matrix_desc &desc, uint8_t *sym, int32_t *status, cudaStream_t stream);
+int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
+                        int *scratch2, cudaStream_t stream);
+int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+                            int32_t *blk_units, cudaStream_t stream);
+int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
+                           int n_matrices, const int64_t *blk_base, const uint32_t *remap, void *il,
+                           cudaStream_t stream);
 int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
                         cudaStream_t stream);
 int launch_pack_emit(const int32_t *w_tern, const int32_t *row_off, uint16_t *w_comp, int height, int width,
@@ -496,11 +489,13 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
   return moe_work_bytes(max_slots, d_model, d_ff);
 }
 
-int qmoe_moe_work_summary(const void *work_dev, int32_t *out_host, int device, void *stream) {
+int qmoe_moe_work_summary(const void *work_dev, int max_slots, int d_ff, int32_t *out_host, int device,
+                          void *stream) {
   QMOE_REQUIRE(work_dev != nullptr && out_host != nullptr, "null pointer");
+  QMOE_REQUIRE(max_slots >= 1 && d_ff >= 1, "bad shape");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return work_summary(work_dev, out_host, as_stream(stream));
+  return work_summary(work_dev, max_slots, d_ff, out_host, as_stream(stream));
 }
 
 static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint16_t *codes_dev,
@@ -521,12 +516,12 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     set_error("%s: d_model/d_ff exceed QMOE_MAX_WIDTH (%d)", fn, QMOE_MAX_WIDTH);
     return QMOE_ERR_UNSUPPORTED;
   }
-  if (ils && !(ils->codes && ils->blk_base && ils->table && ils->hot_table)) {
+  if (ils && !(ils->codes && ils->blk_base && ils->table && ils->dec)) {
     set_error("%s: null pointer in the interleaved store", fn);
     return QMOE_ERR_INVALID_ARG;
   }
   if (ils && (d_model % 32 != 0 || d_ff % 32 != 0)) {
-    set_error("%s: paired-lane streams need d_model and d_ff to be multiples of 32", fn);
+    set_error("%s: lane-interleaved streams need d_model and d_ff to be multiples of 32", fn);
     return QMOE_ERR_UNSUPPORTED;
   }
   if (max_slots == 0) return QMOE_OK;
@@ -539,7 +534,7 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     return QMOE_ERR_INVALID_ARG;
   }
   if ((reinterpret_cast<uintptr_t>(codes_dev) & 15u) != 0 ||
-      (ils && ((reinterpret_cast<uintptr_t>(ils->codes) | reinterpret_cast<uintptr_t>(ils->hot_table)) & 15u) != 0)) {
+      (ils && ((reinterpret_cast<uintptr_t>(ils->codes) | reinterpret_cast<uintptr_t>(ils->table)) & 15u) != 0)) {
     set_error("%s: code stores must be 16-byte aligned", fn);
     return QMOE_ERR_INVALID_ARG;
   }
@@ -636,35 +631,33 @@ int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_
   return launch_code_histogram(codes_dev, n_codes, hist_dev, as_stream(stream));
 }
 
-int qmoe_moe_paired_prepare(const int32_t *dec_dev, const uint64_t *hist_dev, uint32_t *remap_out_dev,
-                          uint32_t *hot_table_out_dev, uint32_t *table_out_dev, uint32_t *split_off_out_dev,
-                          uint16_t *split_codes_out_dev, int64_t split_capacity, int64_t *split_total_out_host,
-                          int device, void *stream) {
-  QMOE_REQUIRE(dec_dev && hist_dev && remap_out_dev && hot_table_out_dev && table_out_dev && split_off_out_dev &&
-                   split_codes_out_dev && split_total_out_host,
-               "null pointer");
-  QMOE_REQUIRE(split_capacity >= QMOE_DICT_COUNT, "split_capacity must be at least 65536");
+int qmoe_sub1_remap_tables(const int32_t *dec_dev, const uint32_t *remap_dev, uint32_t *table_out_dev,
+                           int32_t *dec_out_dev, int device, void *stream) {
+  QMOE_REQUIRE(dec_dev && table_out_dev && dec_out_dev, "null device pointer");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return paired_prepare(dec_dev, hist_dev, remap_out_dev, hot_table_out_dev, table_out_dev, split_off_out_dev,
-                      split_codes_out_dev, split_capacity, split_total_out_host, as_stream(stream));
+  int *scratch = nullptr;
+  QMOE_CUDA(cudaMalloc(&scratch, 2 * sizeof(int)));
+  int rc = launch_remap_tables(dec_dev, remap_dev, table_out_dev, dec_out_dev, scratch, as_stream(stream));
+  int host[2] = {0, 0};
+  if (rc == QMOE_OK) {
+    cudaError_t e = cudaMemcpyAsync(host, scratch, sizeof(host), cudaMemcpyDeviceToHost, as_stream(stream));
+    if (e == cudaSuccess) e = cudaStreamSynchronize(as_stream(stream));
+    if (e != cudaSuccess) rc = cuda_fail(e, "remap tables");
+  }
+  cudaFree(scratch);
+  if (rc) return rc;
+  if (host[0] != 0) {
+    set_error("%s: remap is not a permutation of 0..65535", __func__);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  return QMOE_OK;
 }
 
-int qmoe_moe_paired_plan_host(const int32_t *dec_host, const uint64_t *hist_host, uint32_t *remap_out_host,
-                            uint32_t *hot_table_out_host, uint32_t *table_out_host, uint32_t *split_off_out_host,
-                            uint16_t *split_codes_out_host, int64_t split_capacity, int64_t *split_total_out_host) {
-  QMOE_REQUIRE(dec_host && hist_host && remap_out_host && hot_table_out_host && table_out_host &&
-                   split_off_out_host && split_codes_out_host && split_total_out_host,
-               "null pointer");
-  QMOE_REQUIRE(split_capacity >= QMOE_DICT_COUNT, "split_capacity must be at least 65536");
-  return paired_plan_host(dec_host, hist_host, remap_out_host, hot_table_out_host, table_out_host,
-                        split_off_out_host, split_codes_out_host, split_capacity, split_total_out_host);
-}
-
-int qmoe_moe_paired_count(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
-                        const qmoe_matrix_desc *descs_host, int n_matrices, const uint32_t *split_off_dev,
-                        int32_t *blk_units_dev, int device, void *stream) {
-  QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && descs_host && split_off_dev && blk_units_dev, "null pointer");
+int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                              const qmoe_matrix_desc *descs_host, int n_matrices, int32_t *blk_units_dev,
+                              int device, void *stream) {
+  QMOE_REQUIRE(row_off_dev && descs_dev && descs_host && blk_units_dev, "null pointer");
   QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
   int64_t rows = 0;
   for (int m = 0; m < n_matrices; m++) {
@@ -676,35 +669,19 @@ int qmoe_moe_paired_count(const uint16_t *codes_dev, const int32_t *row_off_dev,
   }
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_paired_count(codes_dev, row_off_dev, descs_dev, n_matrices, split_off_dev, blk_units_dev,
-                           as_stream(stream));
+  return launch_interleave_count(row_off_dev, descs_dev, n_matrices, blk_units_dev, as_stream(stream));
 }
 
-int qmoe_moe_paired_emit(const uint16_t *codes_dev, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
-                       int n_matrices, const int64_t *blk_base_dev, const uint32_t *split_off_dev,
-                       const uint16_t *split_codes_dev, void *il_codes_dev, int device, void *stream) {
-  QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && blk_base_dev && split_off_dev && split_codes_dev &&
-                   il_codes_dev,
-               "null pointer");
+int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_dev,
+                             const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
+                             const uint32_t *remap_dev, void *il_codes_dev, int device, void *stream) {
+  QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && blk_base_dev && il_codes_dev, "null pointer");
   QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
-  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) == 0, "the copy must be 16-byte aligned");
+  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) == 0, "interleaved store must be 16-byte aligned");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_paired_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, split_off_dev,
-                          split_codes_dev, il_codes_dev, as_stream(stream));
-}
-
-int qmoe_moe_paired_decode(const qmoe_interleaved_store *store, const qmoe_matrix_desc *desc_host, uint8_t *sym_dev,
-                         int32_t *status_dev, int device, void *stream) {
-  QMOE_REQUIRE(store && desc_host && sym_dev, "null pointer");
-  QMOE_REQUIRE(store->codes && store->blk_base && store->hot_table, "null pointer in the store");
-  QMOE_REQUIRE(desc_host->height >= 1 && desc_host->width >= 1 && desc_host->height % 32 == 0 &&
-                   desc_host->minmax_base % 32 == 0,
-               "bad matrix descriptor");
-  DeviceGuard guard(device);
-  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_paired_decode(store->hot_table, store->codes, store->blk_base, *desc_host, sym_dev, status_dev,
-                            as_stream(stream));
+  return launch_interleave_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, remap_dev,
+                                il_codes_dev, as_stream(stream));
 }
 
 int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev, const void *prob_dev,

@@ -14,11 +14,9 @@
 //    or quads for more);
 //  * a work list of (matrix, row block, token group) items lets one launch cover every active
 //    expert of a MoE layer;
-//  * stores that carry a paired-lane copy of their streams run the layer's bulk through the kernel
-//    of sub1_paired.cu (re-tokenised streams, the whole table in shared memory, a leaner inner
-//    loop); the kernels of this file then take what that kernel leaves: rows beyond a matrix's last
-//    1024-row block and steps with very few active experts (one row per WARP), and stores without
-//    such a copy.
+//  * for such launches the code streams are read from a lane-interleaved copy (32 rows alternate
+//    chunk by chunk, so a warp's loads are contiguous) whose code values are renumbered by
+//    frequency, and the most frequent 45-53 thousand dictionary entries sit in shared memory.
 #include "common.cuh"
 #include "sub1_walk.cuh"
 
@@ -177,9 +175,11 @@ struct MatmulArgs {
   const int32_t *row_off;
   const __nv_bfloat162 *minmax;
   const qmoe_matrix_desc *descs;  // grouped mode
-  const uint32_t *il;             // grouped mode, paired-lane streams (or null): two codes per word
-  const long long *blk_base;      // first word of every 32-row block of `il`, plus the end
-  const uint32_t *il_tab;         // sparse table in the numbering of the paired-lane streams
+  const uint4 *il;                // grouped mode, lane-interleaved streams (or null)
+  const long long *blk_base;      // first uint4 of every 32-row block of `il`, plus the end
+  const uint32_t *il_tab;         // sparse table in the order of the interleaved store's code values
+  const int32_t *il_dec;          // reference table words in that order
+  int n_hot;                      // entries of il_tab kept in shared memory
   qmoe_matrix_desc single;        // uniform mode
   const __nv_bfloat16 *x;
   __nv_bfloat16 *y;
@@ -231,11 +231,17 @@ __device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wli
   }
 }
 
-// Rows [row0, row0 + nrows) one per thread.
-template <int T, bool GENERAL, class SinkT, class Lookup>
+template <int T, bool GENERAL, class SinkT, int G = 2, class Lookup>
+__device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
+                                                 int nrows, int tok0, int ntok, typename SinkT::elem *xs,
+                                                 const Lookup &lookup);
+
+// Rows [row0, row0 + nrows) one per thread; with an interleaved store, `tail_rows` further rows
+// (what a height like 2080 leaves after blocks of 1024) one per warp, against the same staged x.
+template <int T, bool GENERAL, class SinkT, bool IL = false, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                              int nrows, int tok0, int ntok, typename SinkT::elem *xs,
-                                             const Lookup &lookup) {
+                                             const Lookup &lookup, int tail_rows = 0) {
   const int tid = threadIdx.x;
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
@@ -253,10 +259,23 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
-    const uint16_t *codes_m = a.codes + d.code_base;
-    const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
-    walk_row<GENERAL>(StreamFetch{codes_m - mis}, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
+    if constexpr (IL) {
+      // Row blocks of 32 rows start at multiples of 32 in every matrix and in the store.
+      const long long gblk = (d.minmax_base + row) >> 5;
+      const long long first = a.blk_base[gblk];
+      const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;  // codes per row of this block
+      const long long n = e - b < room ? e - b : room;
+      walk_row<GENERAL>(LaneFetch{a.il + first + (row & 31)}, 0, (int)n, lookup, a.il_dec, wlim, sink);
+    } else {
+      const uint16_t *codes_m = a.codes + d.code_base;
+      const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
+      walk_row<GENERAL>(StreamFetch{codes_m - mis}, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
+    }
+
     store_row<T>(a, sink, row, tok0, ntok);
+  }
+  if constexpr (IL) {
+    if (tail_rows > 0) warp_rows_staged<T, GENERAL, SinkT>(a, d, row0 + nrows, tail_rows, tok0, ntok, xs, lookup);
   }
 }
 
@@ -423,40 +442,41 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
   }
 }
 
-// The same for a work item of a store with paired-lane streams (sub1_paired.cu): code i of row l of
-// a 32-row block is half i % 2 of the word (i / 2) * 32 + l; every row of a block has the block's
-// number of words, padded with a code whose entry is null.
-template <int T, class SinkT, int G>
+// The same for a work item of an interleaved store: code i of row l of a block is element i % 8
+// of the 16-byte entry (i / 8) * 32 + l.
+template <int T, bool GENERAL, class SinkT, int G, class Lookup>
 __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
-                                                 int nrows, int tok0, int ntok, typename SinkT::elem *xs) {
+                                                 int nrows, int tok0, int ntok, typename SinkT::elem *xs,
+                                                 const Lookup &lookup) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int wlim = (d.width + 1) & ~1;
-  const GlobalLookup lookup{a.il_tab};
+  const int32_t *ro = a.row_off + d.rowoff_base;
   for (int r = warp; r < nrows; r += nwarps) {
     const int row = row0 + r;
+    long long b = ro[row], e = ro[row + 1];
+    b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+    e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
     const long long gblk = (d.minmax_base + row) >> 5;
     const long long first = a.blk_base[gblk];
-    const int n = (int)((a.blk_base[gblk + 1] - first) >> 5) * 2;
-    const uint32_t *src = a.il + first + (row & 31);
+    const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;
+    const int n = (int)(e - b < room ? e - b : room);
+    const uint16_t *src = reinterpret_cast<const uint16_t *>(a.il + first + (row & 31));
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
-    const auto code_at = [&](int i) {
-      const uint32_t w = __ldg(src + (long long)(i >> 1) * 32);
-      return (i & 1) ? (w >> 16) : (w & 0xffffu);
-    };
-    if constexpr (G == 2) warp_row_sum<false>(code_at, n, lookup, nullptr, (uint32_t)wlim, sink, lane);
-    else warp_row_sum_groups<false, G>(code_at, n, lookup, nullptr, (uint32_t)wlim, sink, lane);
+    const auto code_at = [&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); };
+    if constexpr (G == 2) warp_row_sum<GENERAL>(code_at, n, lookup, a.il_dec, (uint32_t)wlim, sink, lane);
+    else warp_row_sum_groups<GENERAL, G>(code_at, n, lookup, a.il_dec, (uint32_t)wlim, sink, lane);
     if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
   }
 }
 
-template <int T, class SinkT, int G>
+template <int T, bool GENERAL, class SinkT, int G>
 __device__ __forceinline__ void warp_rows_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0, int nrows,
                                                int tok0, int ntok, typename SinkT::elem *xs) {
   stage_tokens<T, SinkT>(a, d.width, (d.width + 1) & ~1, tok0, ntok, xs);
   __syncthreads();
-  warp_rows_staged<T, SinkT, G>(a, d, row0, nrows, tok0, ntok, xs);
+  warp_rows_staged<T, GENERAL, SinkT, G>(a, d, row0, nrows, tok0, ntok, xs, GlobalLookup{a.il_tab});
 }
 
 // grid.x = row blocks of a.rpc rows, grid.y = token groups of kMaxGroup tokens.
@@ -472,20 +492,30 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_warp_rows(const Matm
   else warp_rows<4, GENERAL>(a, row0, nrows, tok0, ntok, xs_f32);
 }
 
-// Persistent CTAs (one per SM) pulling items of a device-built work list, for stores without a
-// paired-lane copy.  Shared memory holds the hot part of the sparse table (loaded once per CTA)
-// followed by the activations of the current item.
-template <bool GENERAL>
+// Persistent CTAs (one per SM) pulling items of a device-built work list.  Shared memory holds the
+// hot part of the sparse table (loaded once per CTA) followed by the bf16 activations of the
+// current item.
+template <bool GENERAL, bool IL>
 __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
   __shared__ int s_item;
   uint32_t *hot = smem_u32;
-  void *xs = smem_u32 + kHotSlots;
+  const uint32_t n_hot = IL ? (uint32_t)a.n_hot : kHotSlots;
+  void *xs = smem_u32 + n_hot;
   const int n_items = a.header[0];
   if (n_items <= 0) return;
-  for (uint32_t i = threadIdx.x; i < kHotSlots; i += blockDim.x)
-    hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
-  const HotLookup lookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
+  using Lookup = typename std::conditional<IL, HotLookupLow, HotLookup>::type;
+  Lookup lookup;
+  if constexpr (IL) {
+    // n_hot is a multiple of 1024 and both tables are 16-byte aligned
+    for (uint32_t i = threadIdx.x; i < n_hot / 4; i += blockDim.x)
+      reinterpret_cast<uint4 *>(hot)[i] = __ldg(reinterpret_cast<const uint4 *>(a.il_tab) + i);
+    lookup = HotLookupLow{(uint32_t)__cvta_generic_to_shared(hot), a.il_tab, n_hot};
+  } else {
+    for (uint32_t i = threadIdx.x; i < kHotSlots; i += blockDim.x)
+      hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
+    lookup = HotLookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
+  }
   for (;;) {
     if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
     __syncthreads();  // also orders the table fill before the first lookups
@@ -494,28 +524,30 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     const int4 it = a.items[i];
     const qmoe_matrix_desc d = a.descs[it.x];
     const int nrows = it.w & 0x7fff, ntok = it.w >> 16;
+    const int tail = (it.w & 0x8000) ? d.height - (it.y + nrows) : 0;
     // one token: fp32 activations (no conversion per gather); two and four: bf16, so that a gather
     // is one 4- or 8-byte shared load (two 4-byte words per lane cost twice the bank cycles)
     if (ntok <= 1)
-      process_item<1, GENERAL, MatSink<1, true>>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup);
+      process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup,
+                                                     tail);
     else if (ntok == 2)
-      process_item<2, GENERAL, MatSink<2, false>>(a, d, it.y, nrows, it.z, ntok,
-                                                  reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
+      process_item<2, GENERAL, MatSink<2, false>, IL>(a, d, it.y, nrows, it.z, ntok,
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail);
     else
-      process_item<4, GENERAL, MatSink<4, false>>(a, d, it.y, nrows, it.z, ntok,
-                                                  reinterpret_cast<__nv_bfloat16 *>(xs), lookup);
+      process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail);
     __syncthreads();  // xs and s_item are rewritten by the next round
   }
 }
 
-// Work items of a store with paired-lane streams whose rows are shared out one per WARP: the rows
-// that are left when a matrix's height is not a multiple of the 1024 rows a CTA of k_matmul_paired
-// takes, and whole layers when so few experts are active (one token per step while generating) that
-// rows per thread could not fill the GPU.  Several CTAs per SM; the table is read through L1/L2.
+// Work items of an interleaved store whose rows are shared out one per WARP: the rows that are left
+// when a matrix's height is not a multiple of the 1024 rows a CTA of k_matmul_grouped takes, and
+// whole layers when so few experts are active (one token per step while generating) that rows per
+// thread could not fill the GPU.  Several CTAs per SM; the table is read through L1/L2.
 // G: groups of 32 codes per round of a row.  A row of w weights has about w / 23 codes; the host
 // picks nine groups for wide matrices, so that a 6144-wide row (about 265 codes) is one round of
 // dictionary lookups instead of three, and four otherwise (fewer registers, more CTAs per SM).
-template <int G>
+template <bool GENERAL, int G>
 __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
   const int n_items = a.header[0];
@@ -525,11 +557,13 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_grouped_warp(const M
     const qmoe_matrix_desc d = a.descs[it.x];
     const int nrows = it.w & 0xffff, ntok = it.w >> 16;
     if (ntok <= 1)
-      warp_rows_item<1, MatSink<1, true>, G>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(smem_u32));
+      warp_rows_item<1, GENERAL, MatSink<1, true>, G>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(smem_u32));
     else if (ntok == 2)
-      warp_rows_item<2, MatSink<2, false>, G>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<__nv_bfloat16 *>(smem_u32));
+      warp_rows_item<2, GENERAL, MatSink<2, false>, G>(a, d, it.y, nrows, it.z, ntok,
+                                                       reinterpret_cast<__nv_bfloat16 *>(smem_u32));
     else
-      warp_rows_item<4, MatSink<4, false>, G>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<__nv_bfloat16 *>(smem_u32));
+      warp_rows_item<4, GENERAL, MatSink<4, false>, G>(a, d, it.y, nrows, it.z, ntok,
+                                                       reinterpret_cast<__nv_bfloat16 *>(smem_u32));
     __syncthreads();  // xs is rewritten by the next round
   }
 }
@@ -592,7 +626,13 @@ static size_t grouped_x_bytes(int width, int group) {
 static size_t grouped_smem_bytes(int width, int group) {
   return sizeof(uint32_t) * kHotSlots + grouped_x_bytes(width, group);
 }
+// Interleaved stores: whatever the activations leave of the 227 KB goes to the table.
 constexpr size_t kSmemPerCta = 232448 - 1024;  // opt-in limit minus static shared memory and slack
+static int hot_entries_for(int width) {
+  const size_t left = kSmemPerCta - grouped_x_bytes(width, kMaxGroup);
+  size_t n = left / sizeof(uint32_t) / 1024 * 1024;
+  return (int)(n > QMOE_DICT_COUNT ? QMOE_DICT_COUNT : n);
+}
 
 template <bool GENERAL>
 static int set_smem_limits() {
@@ -600,8 +640,14 @@ static int set_smem_limits() {
                                  (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_warp_rows<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
-  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemPerCta));
+  QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped_warp<GENERAL, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
+  QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped_warp<GENERAL, 9>), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   return QMOE_OK;
 }
 
@@ -617,10 +663,6 @@ static int ensure_smem_limits(int device) {
     if (rc) return rc;
     rc = set_smem_limits<true>();
     if (rc) return rc;
-    QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped_warp<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
-    QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped_warp<9>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
     done[device] = true;
   }
   return QMOE_OK;
@@ -691,17 +733,122 @@ int launch_build_table(const int32_t *dec, uint32_t *tab, int *nonconforming, cu
   return QMOE_OK;
 }
 
-// ---- code histogram (which dictionary entries a store uses most) ----------------------------------
+// ---- renumbering of code values --------------------------------------------------------------------
 __global__ void k_code_histogram(const uint16_t *__restrict__ codes, long long n,
                                  unsigned long long *__restrict__ hist) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     atomicAdd(hist + codes[i], 1ull);
 }
 
+// dec_out[2 * remap[c] + i] = dec[2 * c + i]: the reference table in the order of the new code values.
+__global__ void k_permute_dec(const int32_t *__restrict__ dec, const uint32_t *__restrict__ remap,
+                              int32_t *__restrict__ dec_out, int *bad) {
+  const int code = blockIdx.x * blockDim.x + threadIdx.x;
+  if (code >= QMOE_DICT_COUNT) return;
+  const uint32_t to = remap != nullptr ? remap[code] : (uint32_t)code;
+  if (to >= (uint32_t)QMOE_DICT_COUNT) {
+    atomicAdd(bad, 1);
+    return;
+  }
+  dec_out[2 * to] = dec[2 * code];
+  dec_out[2 * to + 1] = dec[2 * code + 1];
+}
+
 int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream) {
   QMOE_LAUNCH(k_code_histogram, 148 * 8, 256, 0, stream, codes, (long long)n,
               reinterpret_cast<unsigned long long *>(hist));
   QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+// Entries of dec_out that no code was mapped to (remap is not a permutation) keep length 0.
+__global__ void k_count_unset(const int32_t *__restrict__ dec_out, const int32_t *__restrict__ dec, int *bad) {
+  const int code = blockIdx.x * blockDim.x + threadIdx.x;
+  if (code >= QMOE_DICT_COUNT) return;
+  if (dec_out[2 * code] == 0 && dec_out[2 * code + 1] == 0) atomicAdd(bad, 1);
+  if (dec[2 * code] == 0 && dec[2 * code + 1] == 0) atomicSub(bad, 1);  // all-zero words of the source itself
+}
+
+// scratch2[0] := number of out-of-range or colliding targets, scratch2[1] := non-conforming entries.
+int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
+                        int *scratch2, cudaStream_t stream) {
+  QMOE_CUDA(cudaMemsetAsync(scratch2, 0, 2 * sizeof(int), stream));
+  QMOE_CUDA(cudaMemsetAsync(dec_out, 0, sizeof(int32_t) * 2 * QMOE_DICT_COUNT, stream));
+  QMOE_LAUNCH(k_permute_dec, QMOE_DICT_COUNT / 256, 256, 0, stream, dec, remap, dec_out, scratch2);
+  QMOE_CUDA(cudaGetLastError());
+  QMOE_LAUNCH(k_count_unset, QMOE_DICT_COUNT / 256, 256, 0, stream, dec_out, dec, scratch2);
+  QMOE_CUDA(cudaGetLastError());
+  QMOE_LAUNCH(k_build_table, QMOE_DICT_COUNT / 256, 256, 0, stream, dec_out, tab_out, scratch2 + 1);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+// ---- lane-interleaved code streams ----------------------------------------------------------------
+// One-time re-layout of a store's code streams for the grouped kernel.  Rows are taken in blocks of
+// 32 (one warp); inside a block, chunk k (codes 8k .. 8k+7) of row l is the uint4 at index
+// k * 32 + l, so the 32 lanes of a warp read 512 contiguous bytes per step instead of 32 separate
+// cache lines.  Every row of a block is padded with zero codes to the block's longest row, rounded
+// up to a whole chunk; the row lengths still come from row_off.  Heights must be multiples of 32.
+__global__ void k_interleave_count(const int32_t *__restrict__ row_off, const qmoe_matrix_desc *__restrict__ descs,
+                                   int32_t *__restrict__ blk_units) {
+  const qmoe_matrix_desc d = descs[blockIdx.x];
+  const int32_t *ro = row_off + d.rowoff_base;
+  for (int blk = threadIdx.x; blk < d.height / 32; blk += blockDim.x) {
+    int longest = 0;
+    for (int l = 0; l < 32; l++) {
+      const int n = ro[blk * 32 + l + 1] - ro[blk * 32 + l];
+      longest = n > longest ? n : longest;
+    }
+    blk_units[d.minmax_base / 32 + blk] = (longest + 7) / 8 * 32;  // uint4 entries of this block
+  }
+}
+
+__global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int32_t *__restrict__ row_off,
+                                  const qmoe_matrix_desc *__restrict__ descs,
+                                  const long long *__restrict__ blk_base, const uint32_t *__restrict__ remap,
+                                  uint4 *__restrict__ il) {
+  const qmoe_matrix_desc d = descs[blockIdx.y];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int32_t *ro = row_off + d.rowoff_base;
+  const uint16_t *src = codes + d.code_base;
+  for (int blk = blockIdx.x * nwarps + warp; blk < d.height / 32; blk += gridDim.x * nwarps) {
+    const long long gblk = d.minmax_base / 32 + blk;
+    const long long first = blk_base[gblk];
+    const int chunks = (int)((blk_base[gblk + 1] - first) >> 5);
+    long long b = ro[blk * 32 + lane], e = ro[blk * 32 + lane + 1];
+    b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
+    e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
+    for (int k = 0; k < chunks; k++) {
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const long long idx = b + 8 * k + j;
+        uint32_t code = idx < e ? src[idx] : 0u;
+        if (remap != nullptr) code = __ldg(remap + code) & 0xffffu;
+        w[j >> 1] |= code << (16 * (j & 1));
+      }
+      il[first + (long long)k * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+                            int32_t *blk_units, cudaStream_t stream) {
+  QMOE_LAUNCH(k_interleave_count, (unsigned)n_matrices, 256, 0, stream, row_off, descs, blk_units);
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
+                           int n_matrices, const int64_t *blk_base, const uint32_t *remap, void *il,
+                           cudaStream_t stream) {
+  const int per_pass = 32768;  // grid.y limit is 65535
+  for (int m0 = 0; m0 < n_matrices; m0 += per_pass) {
+    const int n = n_matrices - m0 < per_pass ? n_matrices - m0 : per_pass;
+    QMOE_LAUNCH(k_interleave_emit, dim3(8, (unsigned)n), 256, 0, stream, codes, row_off, descs + m0,
+                reinterpret_cast<const long long *>(blk_base), remap, reinterpret_cast<uint4 *>(il));
+    QMOE_CUDA(cudaGetLastError());
+  }
   return QMOE_OK;
 }
 
@@ -713,23 +860,19 @@ int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cuda
 // and fetch counters of the warp items of wi and wo.
 //
 // Who takes which rows is decided here, on the device, from the number of (expert, token group)
-// pairs of the step.
-//  * Stores without a paired-lane copy: groups of up to four tokens, every matrix cut into equal
-//    items of at most 1024 rows for k_matmul_grouped (finer when there are few pairs, until there
-//    are about two items per SM).
-//  * Stores with a paired-lane copy: groups of up to four tokens as well.  Rows up to the last
-//    multiple of 1024 go to k_matmul_paired in c equal items per pair, c chosen so that the items
-//    fill whole rounds of the SMs as
-//    well as they can (190 pairs x 2 items over 148 SMs would be 2.6 rounds that cost 3); a remainder
-//    of at most 256 rows (2080 = 2 x 1024 + 32) goes to k_matmul_grouped_warp, one row per warp; and
-//    when so few pairs exist (one token per step while generating) that rows per thread could not
-//    fill the SMs, everything goes to that kernel.
+// pairs.  A full layer (hundreds of pairs) is cut into items of up to 1024 rows for
+// k_matmul_grouped, one row per thread of its persistent CTAs.  With an interleaved store, rows that
+// do not fill such an item (heights like 2080 = 2 x 1024 + 32) are done one per warp by the CTA that
+// takes the matrix's last item, and when so few pairs exist (one token per step while generating)
+// that rows per thread could not fill the SMs, everything goes to k_matmul_grouped_warp in items of
+// 32 rows.  In between, the items are made finer than 1024 rows
+// until there are about two per SM.  Without an interleaved store there is no warp kernel.
 constexpr int kExtraItems = 8192;
+constexpr int kItemOverheadRows = 64;       // fixed cost of a work item, in rows of work (staging the activations)
 constexpr int kWarpItemRows = 8;             // one row per warp of a k_matmul_grouped_warp CTA
 constexpr int kWarpRemainderMax = 256;      // most rows of a matrix that are left to the warp kernel
 constexpr int kSmallRows = 148 * 8 * 32;    // fewer rows in total (less than eight warps of rows per SM):
                                             // the warp kernel takes all of them
-constexpr int kItemOverheadRows = 64;       // fixed cost of a work item, in rows of work (staging the activations)
 
 struct WorkPhase {
   int4 *items;
@@ -741,13 +884,12 @@ struct WorkPhase {
 };
 
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
-                                                     int max_slots, int tile_min, int sms, int paired,
-                                                     int *header, WorkPhase p0, WorkPhase p1) {
+                                                     int max_slots, int tile_min, int sms,
+                                                     int use_warp, int *header, WorkPhase p0, WorkPhase p1) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_total;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int group = kMaxGroup;
   auto group_count = [&](int e, int &first, int &count) {
     first = 0;
     count = 0;
@@ -757,7 +899,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       count = count < 0 ? 0 : count;
       if (tile_min > 0 && count >= tile_min) count = 0;  // handled by the tensor-core tile path
     }
-    return (count + group - 1) / group;
+    return (count + kMaxGroup - 1) / kMaxGroup;
   };
   // pass 1: total number of (expert, token group) pairs
   if (tid == 0) s_total = 0;
@@ -777,34 +919,34 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
     const int H = p.height;
     // rows [0, main_rows) in items of rpc rows for the per-thread kernel, the rest in warp items
     int rpc = rows_per_chunk_dev(H, kGroupedThreads), main_rows = H;
-    if (paired && (long long)total * H <= kSmallRows) {
+    if (use_warp && (long long)total * H <= kSmallRows) {
       main_rows = 0;
-    } else if (paired && total > 0) {
+    } else if (total > 0) {
       const int rest = H % kGroupedThreads;
-      if (H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) main_rows = H - rest;
+      if (use_warp && H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) main_rows = H - rest;
+      // c equal items per pair: the c that fills whole rounds of the SMs best (190 pairs x 2 items
+      // over 148 SMs are 2.6 rounds that cost 3; 3 items of 704 rows are 3.9 rounds that cost 4 x 0.69)
       const int c0 = (main_rows + kGroupedThreads - 1) / kGroupedThreads;
-      int best_c = c0;
+      int best_rows = ((main_rows + c0 - 1) / c0 + 31) / 32 * 32;
       long long best_cost = -1;
-      for (int c = c0; c <= c0 + 6; c++) {
-        if (c > c0 && (long long)total * c > p.capacity) break;
+      for (int c = c0; c <= c0 + 64 && c * 32 <= main_rows; c++) {
         const int rows = ((main_rows + c - 1) / c + 31) / 32 * 32;
         const int per_pair = (main_rows + rows - 1) / rows;
+        if (c > c0 && (long long)total * per_pair > p.capacity) break;
         const long long rounds = ((long long)total * per_pair + sms - 1) / sms;
         const long long cost = rounds * (rows + kItemOverheadRows);
         if (best_cost < 0 || cost < best_cost) {
           best_cost = cost;
-          best_c = c;
+          best_rows = rows;
         }
       }
-      rpc = ((main_rows + best_c - 1) / best_c + 31) / 32 * 32;
-    } else if (total > 0) {
-      const long long want = ((long long)total * H + 2 * sms - 1) / (2 * sms);
-      int fine = (int)((want + 31) / 32 * 32);
-      fine = fine < 32 ? 32 : fine;
-      if (fine < rpc && (long long)total * ((H + fine - 1) / fine) <= p.capacity) rpc = fine;  // few pairs
+      rpc = best_rows;
     }
     const int chunks = (main_rows + rpc - 1) / rpc;
-    const int wchunks = paired ? (H - main_rows + kWarpItemRows - 1) / kWarpItemRows : 0;
+    // what is left after the per-thread items: with none of those, items for the warp kernel;
+    // otherwise the CTA that takes the last per-thread item does them, one row per warp (bit 15)
+    const int wchunks = main_rows == 0 ? (H + kWarpItemRows - 1) / kWarpItemRows : 0;
+    const int tail_flag = main_rows > 0 && main_rows < H ? 0x8000 : 0;
     if (tid == 0) s_base = 0;
     __syncthreads();
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
@@ -831,20 +973,21 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       }
       __syncthreads();
       const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
-      // Items for the per-thread kernels (a few per group): every lane writes those of its expert.
+      // Items for the per-thread kernel (a few per group): every lane writes those of its expert.
       for (int g = 0; g < groups && chunks > 0; g++) {
         const int gi = base + g;
         if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
-        const int tok0 = first + g * group;
-        const int ntok = min(group, count - g * group);
+        const int tok0 = first + g * kMaxGroup;
+        const int ntok = min(kMaxGroup, count - g * kMaxGroup);
         for (int k = 0; k < chunks; k++) {
           const int row0 = k * rpc;
           p.items[(size_t)gi * chunks + k] =
-              make_int4(2 * e + p.which, row0, tok0, min(rpc, main_rows - row0) | (ntok << 16));
+              make_int4(2 * e + p.which, row0, tok0,
+                        min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) | (ntok << 16));
         }
       }
-      // Items for the warp kernel (hundreds per group in steps with a handful of groups, a few per
-      // group for remainder rows): the whole warp writes those of each lane's expert in turn.
+      // Items for the warp kernel (hundreds per group, but only in steps with a handful of groups):
+      // the whole warp writes those of each lane's expert in turn.
       unsigned busy = __ballot_sync(0xffffffffu, groups > 0 && wchunks > 0);
       while (busy) {
         const int src = __ffs(busy) - 1;
@@ -855,10 +998,10 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
         for (int g = 0; g < o_groups; g++) {
           const int gi = o_base + g;
           if (gi >= max_slots || (long long)(gi + 1) * wchunks > p.warp_capacity) break;
-          const int tok0 = o_first + g * group;
-          const int ntok = min(group, o_count - g * group);
+          const int tok0 = o_first + g * kMaxGroup;
+          const int ntok = min(kMaxGroup, o_count - g * kMaxGroup);
           for (int k = lane; k < wchunks; k += 32) {
-            const int row0 = main_rows + k * kWarpItemRows;
+            const int row0 = k * kWarpItemRows;
             p.warp_items[(size_t)gi * wchunks + k] =
                 make_int4(2 * o_e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (ntok << 16));
           }
@@ -875,7 +1018,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       header[10 + 2 * phase] = groups_done * wchunks;
       header[11 + 2 * phase] = 0;
       header[6 + phase] = rpc;  // rows per item of this phase (reports)
-      header[9] = group;
+      header[9] = kMaxGroup;
     }
     __syncthreads();
   }
@@ -919,10 +1062,8 @@ static int64_t item_capacity(int max_slots, int height) {
 }
 
 static int64_t warp_item_capacity(int max_slots) {
-  // steps with at most kSmallRows rows in total, or up to kWarpRemainderMax remainder rows per pair
-  const int64_t small = kSmallRows / kWarpItemRows;
-  const int64_t rest = (int64_t)max_slots * (kWarpRemainderMax / kWarpItemRows);
-  return (small > rest ? small : rest) + kExtraItems;
+  (void)max_slots;  // only steps with at most kSmallRows rows use warp items
+  return kSmallRows / kWarpItemRows + kExtraItems;
 }
 
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
@@ -934,11 +1075,23 @@ int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
 // What the last qmoe_moe_grouped_ffn call with this work buffer planned (a host read-back for tests
 // and reports): out[0] / out[1] = per-thread items of wi / wo, out[2] / out[3] = row-per-warp items
 // of wi / wo, out[4] / out[5] = rows per per-thread item of wi / wo, out[6] / out[7] = tile items of
-// wi / wo, out[8] = tokens decoded together.
-int work_summary(const void *work, int32_t *out, cudaStream_t stream) {
+// wi / wo, out[8] = tokens decoded together, out[9] = wo items whose CTA also does the matrix's
+// remainder rows one per warp.
+int work_summary(const void *work, int max_slots, int d_ff, int32_t *out, cudaStream_t stream) {
   int header[16];
   QMOE_CUDA(cudaMemcpyAsync(header, work, sizeof(header), cudaMemcpyDeviceToHost, stream));
   QMOE_CUDA(cudaStreamSynchronize(stream));
+  const int64_t cap_wi = item_capacity(max_slots, d_ff);
+  int n_wo = header[2];
+  n_wo = n_wo < 0 ? 0 : n_wo;
+  std::vector<int4> items((size_t)n_wo);
+  if (n_wo > 0) {
+    const char *base = reinterpret_cast<const char *>(work) + 64 + cap_wi * sizeof(int4);
+    QMOE_CUDA(cudaMemcpyAsync(items.data(), base, sizeof(int4) * (size_t)n_wo, cudaMemcpyDeviceToHost, stream));
+    QMOE_CUDA(cudaStreamSynchronize(stream));
+  }
+  int flagged = 0;
+  for (const int4 &it : items) flagged += (it.w & 0x8000) ? 1 : 0;
   out[0] = header[0];
   out[1] = header[2];
   out[2] = header[10];
@@ -948,14 +1101,9 @@ int work_summary(const void *work, int32_t *out, cudaStream_t stream) {
   out[6] = header[4];
   out[7] = header[5];
   out[8] = header[9];
+  out[9] = flagged;
   return QMOE_OK;
 }
-
-// The kernel of sub1_paired.cu.
-int launch_paired_phase(const uint32_t *hot_table, const void *il, const int64_t *blk_base, const void *minmax,
-                      const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, int *header, int flags,
-                      int width, int device, cudaStream_t stream);
 
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
@@ -982,15 +1130,15 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   ph[0].warp_capacity = ph[1].warp_capacity = (int)warp_item_capacity(max_slots);
   ph[1].warp_items = ph[0].warp_items + ph[0].warp_capacity;
   const bool il = ils != nullptr;
-  // The tile path decodes the row-by-row streams; a store that kept only its paired-lane copy
-  // (codes == nullptr) sends every expert through the per-row kernels.
+  // The tile path decodes the row-by-row streams; a store that kept only its interleaved copy
+  // (codes == nullptr) sends every expert through the per-row kernel.
   // max_slots bounds the tokens of the step, so launches that cannot get work are left out: the
   // tile path when no expert can reach its threshold, the per-thread kernel when the step is small
   // enough for the warp kernel whatever the routing (see k_build_work).
   int tile_min = tab.conforming && codes != nullptr ? tile_min_tokens() : 0;
   if (tile_min > max_slots) tile_min = 0;
-  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, sms, il ? 1 : 0, header,
-              ph[0], ph[1]);
+  QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, sms, il ? 1 : 0,
+              header, ph[0], ph[1]);
   QMOE_CUDA(cudaGetLastError());
   if (tile_min > 0) {
     rc = launch_build_tile_work(offsets, n_experts, tile_min, d_model, d_ff, max_slots, header, tile_wi, tile_wo, stream);
@@ -1005,39 +1153,50 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   a.minmax = reinterpret_cast<const __nv_bfloat162 *>(minmax);
   a.descs = descs;
   if (il) {
-    a.il = reinterpret_cast<const uint32_t *>(ils->codes);
+    a.il = reinterpret_cast<const uint4 *>(ils->codes);
     a.blk_base = reinterpret_cast<const long long *>(ils->blk_base);
     a.il_tab = ils->table;
+    a.il_dec = ils->dec;
   }
   cudaEvent_t *events = nullptr;
   const bool timed = profile_begin(device, &events);
 
   for (int phase = 0; phase < 2; phase++) {
     const int width = phase == 0 ? d_model : d_ff;
-    const int height = phase == 0 ? d_ff : d_model;
     a.x = reinterpret_cast<const __nv_bfloat16 *>(phase == 0 ? xs : hs);
     a.y = reinterpret_cast<__nv_bfloat16 *>(phase == 0 ? hs : ys);
     a.x_stride = phase == 0 ? xs_stride : width;
-    a.y_stride = phase == 0 ? height : ys_stride;
+    a.y_stride = phase == 0 ? d_ff : ys_stride;
     a.x_rows = phase == 0 ? x_rows : nullptr;   // the hidden activation in between is indexed by slot
     a.y_rows = phase == 0 ? nullptr : y_rows;
     a.items = ph[phase].items;
     a.header = header + 2 * phase;
     a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
+    a.n_hot = hot_entries_for(width);
+    const size_t smem = il ? sizeof(uint32_t) * a.n_hot + grouped_x_bytes(width, kMaxGroup)
+                           : grouped_smem_bytes(width, kMaxGroup);
     if (tile_min > 0) {
-      const int rows_blocks = (height + 127) / 128;
+      const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
       rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
                              a.x_rows, a.y_rows, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
       if (rc) return rc;
     }
+    const unsigned grid = (unsigned)sms;  // the table in shared memory allows one CTA per SM
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
+    const int height = phase == 0 ? d_ff : d_model;
+    if (il && (long long)max_slots * height <= kSmallRows) {
+      // every step this small goes to the warp kernel
+    } else if (tab.conforming && il)
+      QMOE_LAUNCH((k_matmul_grouped<false, true>), grid, kGroupedThreads, smem, stream, a);
+    else if (tab.conforming)
+      QMOE_LAUNCH((k_matmul_grouped<false, false>), grid, kGroupedThreads, smem, stream, a);
+    else if (il)
+      QMOE_LAUNCH((k_matmul_grouped<true, true>), grid, kGroupedThreads, smem, stream, a);
+    else
+      QMOE_LAUNCH((k_matmul_grouped<true, false>), grid, kGroupedThreads, smem, stream, a);
+    QMOE_CUDA(cudaGetLastError());
     if (il) {
-      if ((long long)max_slots * height > kSmallRows) {  // smaller steps go to the warp kernel whole
-        rc = launch_paired_phase(ils->hot_table, ils->codes, ils->blk_base, minmax, descs, a.x, a.y, a.x_stride,
-                               a.y_stride, a.x_rows, a.y_rows, a.items, a.header, a.flags, width, device, stream);
-        if (rc) return rc;
-      }
       MatmulArgs w = a;
       w.items = ph[phase].warp_items;
       w.header = header + 10 + 2 * phase;
@@ -1045,18 +1204,15 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
       int per_sm = (int)(kSmemPerCta / (wsmem + 1024));  // CTAs of 256 threads that fit one SM
       per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
       const unsigned wgrid = (unsigned)(per_sm * sms);
-      if (width > 3072)
-        QMOE_LAUNCH(k_matmul_grouped_warp<9>, wgrid, kWarpRowThreads, wsmem, stream, w);
+      const bool long_rows = width > 3072;
+      if (tab.conforming && long_rows)
+        QMOE_LAUNCH((k_matmul_grouped_warp<false, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
+      else if (tab.conforming)
+        QMOE_LAUNCH((k_matmul_grouped_warp<false, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
+      else if (long_rows)
+        QMOE_LAUNCH((k_matmul_grouped_warp<true, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
       else
-        QMOE_LAUNCH(k_matmul_grouped_warp<4>, wgrid, kWarpRowThreads, wsmem, stream, w);
-      QMOE_CUDA(cudaGetLastError());
-    } else {
-      const unsigned grid = (unsigned)sms;  // the table in shared memory allows one CTA per SM
-      const size_t smem = grouped_smem_bytes(width, kMaxGroup);
-      if (tab.conforming)
-        QMOE_LAUNCH(k_matmul_grouped<false>, grid, kGroupedThreads, smem, stream, a);
-      else
-        QMOE_LAUNCH(k_matmul_grouped<true>, grid, kGroupedThreads, smem, stream, a);
+        QMOE_LAUNCH((k_matmul_grouped_warp<true, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
       QMOE_CUDA(cudaGetLastError());
     }
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));

@@ -57,6 +57,27 @@ struct HotLookup {
     return e;
   }
 };
+// The same for a store whose code values were renumbered by decreasing frequency: the first n_hot
+// entries live in shared memory, the rest in global memory.
+struct HotLookupLow {
+  uint32_t hot_addr;
+  const uint32_t *__restrict__ tab;
+  uint32_t n_hot;
+  __device__ __forceinline__ uint32_t operator()(uint32_t code) const {
+    uint32_t e;
+    const uint32_t saddr = hot_addr + code * 4u;
+    const uint32_t *gaddr = tab + code;
+    asm("{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.lt.u32 p, %1, %4;\n\t"
+        "@p ld.shared.b32 %0, [%2];\n\t"
+        "@!p ld.global.nc.b32 %0, [%3];\n\t"
+        "}"
+        : "=r"(e)
+        : "r"(code), "r"(saddr), "l"(gaddr), "r"(n_hot));
+    return e;
+  }
+};
 static_assert(kHotLow == 24576 && kHotHigh == 49152 && (kHotHigh - kHotLow) * 4 == 98304,
               "HotLookup's inline PTX hard-codes the hot ranges");
 
@@ -87,13 +108,19 @@ __device__ __forceinline__ uint32_t chunk_code(const uint4 &q, int j) {
 // codes, so x must be followed by this many zero entries.
 constexpr int kWalkPad = 4 * 28 + 32;
 
-// Where the eight codes of a chunk come from: the reference's stream (rows back to back), read
-// through a 16-byte aligned pointer.
+// Where the eight codes of a chunk come from.  StreamFetch: the reference's stream (rows back to
+// back), read through a 16-byte aligned pointer.  LaneFetch: the lane-interleaved layout, in which
+// the 32 rows of a row block alternate chunk by chunk (chunk k of row l at uint4 index k * 32 + l),
+// so that the 32 loads of a warp cover 512 contiguous bytes.
 struct StreamFetch {
   const uint16_t *__restrict__ codes_al;
   __device__ __forceinline__ uint4 operator()(int c) const {
     return __ldg(reinterpret_cast<const uint4 *>(codes_al + c));
   }
+};
+struct LaneFetch {
+  const uint4 *__restrict__ p;  // chunk 0 of this lane's row
+  __device__ __forceinline__ uint4 operator()(int c) const { return __ldg(p + (c >> 3) * 32); }
 };
 
 // Walks codes [b_al, e_al) (indices as fetch() takes them; fetch(c) returns codes c .. c + 7 for c a

@@ -153,74 +153,49 @@ class ExpertStore:
         self.dec = dec                                   # decoder table of these streams (None: the standard one)
         if dec is not None and dec.is_cuda:
             sub1_cuda.track_dec(dec)                     # the library's cache follows the tensor's life
-        self.il_codes: Optional[torch.Tensor] = None     # paired-lane copy of the streams (uint32 words)
-        self.blk_base: Optional[torch.Tensor] = None     # int64, first word of every 32-row block
+        self.il_codes: Optional[torch.Tensor] = None     # lane-interleaved copy of the streams
+        self.blk_base: Optional[torch.Tensor] = None     # int64, first 16-byte entry of every 32-row block
         if interleave and codes.is_cuda and d_model % 32 == 0 and d_ff % 32 == 0:
             self.interleave()
 
-    def interleave(self) -> None:
-        """Build the paired-lane copy of the code streams that the grouped kernel reads (layout in
-        include/qmoe_sub1.h): two codes per word, the words of the 32 rows of a block side by side,
-        code values renumbered by decreasing frequency, and every code outside the most frequent
-        ``PAIRED_TABLE - 1`` replaced by frequent codes that spell the same weights, so that the kernel
-        serves every lookup from shared memory.  One-time cost when a store is created.  A decoder
-        table the kernel cannot serve (an entry with more than three non-zeros) leaves the store
-        without a copy; it then runs on its row-by-row streams."""
+    def interleave(self, renumber: bool = True) -> None:
+        """Build the lane-interleaved copy of the code streams that the grouped kernel reads with
+        coalesced loads (layout in include/qmoe_sub1.h), with code values renumbered by decreasing
+        frequency so that the part of the table kept in shared memory serves as many lookups as
+        possible.  One-time cost when a store is created."""
         L = _lib.load()
         dev = self.device
         dec = self.dec if self.dec is not None else DEC(dev)
-        n_mat = len(self.host_descs)
-        hist = torch.zeros(_lib.DICT_COUNT, dtype=torch.int64, device=dev)
-        last = self.host_descs[min(63, n_mat - 1)]                          # 64 matrices are sample enough
-        n = min(last.code_base + last.n_codes, self.codes.numel())
-        _lib.check(L.qmoe_sub1_code_histogram(self.codes.data_ptr(), n, hist.data_ptr(), dev.index, _s(dev)))
-        remap = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
-        hot_table = torch.empty(_lib.PAIRED_TABLE, dtype=torch.int32, device=dev)
-        table = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
-        split_off = torch.empty(_lib.DICT_COUNT + 1, dtype=torch.int32, device=dev)
-        split_cap = 14 * _lib.DICT_COUNT                                    # a code is at most 14 pairs
-        split_codes = torch.empty(split_cap, dtype=torch.int16, device=dev)
-        total = ctypes.c_int64(0)
-        rc = L.qmoe_moe_paired_prepare(dec.data_ptr(), hist.data_ptr(), remap.data_ptr(), hot_table.data_ptr(),
-                                     table.data_ptr(), split_off.data_ptr(), split_codes.data_ptr(), split_cap,
-                                     ctypes.byref(total), dev.index, _s(dev))
-        if rc == _lib.ERR_UNSUPPORTED:
-            return
-        _lib.check(rc)
-        split_codes = split_codes[:int(total.value)].clone()
+        remap_ptr = None
+        if renumber:
+            hist = torch.zeros(_lib.DICT_COUNT, dtype=torch.int64, device=dev)
+            last = self.host_descs[min(63, len(self.host_descs) - 1)]      # 64 matrices are sample enough
+            n = min(last.code_base + last.n_codes, self.codes.numel())
+            _lib.check(L.qmoe_sub1_code_histogram(self.codes.data_ptr(), n, hist.data_ptr(), dev.index, _s(dev)))
+            order = torch.argsort(hist, descending=True, stable=True)
+            remap = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
+            remap[order] = torch.arange(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
+            self.remap = remap
+            remap_ptr = remap.data_ptr()
+        self.il_table = torch.empty(_lib.DICT_COUNT, dtype=torch.int32, device=dev)
+        self.il_dec = torch.empty(2 * _lib.DICT_COUNT, dtype=torch.int32, device=dev)
+        _lib.check(L.qmoe_sub1_remap_tables(dec.data_ptr(), remap_ptr, self.il_table.data_ptr(),
+                                            self.il_dec.data_ptr(), dev.index, _s(dev)))
         rows = sum(d.height for d in self.host_descs)
         units = torch.empty(rows // 32, dtype=torch.int32, device=dev)
-        _lib.check(L.qmoe_moe_paired_count(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
-                                         ctypes.addressof(self._desc_array), n_mat, split_off.data_ptr(),
-                                         units.data_ptr(), dev.index, _s(dev)))
+        _lib.check(L.qmoe_moe_interleave_count(self.row_off.data_ptr(), self.descs.data_ptr(),
+                                               ctypes.addressof(self._desc_array), len(self.host_descs),
+                                               units.data_ptr(), dev.index, _s(dev)))
         base = torch.zeros(rows // 32 + 1, dtype=torch.int64, device=dev)
         base[1:] = torch.cumsum(units, 0, dtype=torch.int64)
-        words = int(base[-1].item())
-        # the kernel reads its stream a few words ahead without a range test: null words at the end
-        null_word = (_lib.PAIRED_TABLE - 1) | ((_lib.PAIRED_TABLE - 1) << 16)
-        il = torch.full((words + _lib.PAIRED_TAIL_WORDS,), null_word - (1 << 32), dtype=torch.int32, device=dev)
-        _lib.check(L.qmoe_moe_paired_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
-                                        n_mat, base.data_ptr(), split_off.data_ptr(), split_codes.data_ptr(),
-                                        il.data_ptr(), dev.index, _s(dev)))
-        self.remap, self.split_off, self.split_codes = remap, split_off, split_codes
-        self.il_table, self.hot_table = table, hot_table
+        total = int(base[-1].item())
+        il = torch.empty((max(total, 1), 4), dtype=torch.int32, device=dev)
+        _lib.check(L.qmoe_moe_interleave_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
+                                              len(self.host_descs), base.data_ptr(), remap_ptr, il.data_ptr(),
+                                              dev.index, _s(dev)))
         self.il_codes, self.blk_base = il, base
-        self.il_words = words
-        self.il_struct = _lib.InterleavedStore(il.data_ptr(), base.data_ptr(), table.data_ptr(),
-                                               hot_table.data_ptr())
-
-    def decode_copy(self, m: int, return_status: bool = False):
-        """Ternary symbols ``uint8[height, width]`` of matrix ``m`` decoded from the paired-lane copy
-        with the table and the walk of the grouped kernel (the parity check of the copy)."""
-        if self.il_codes is None:
-            raise RuntimeError("store has no paired-lane copy")
-        d = self.host_descs[m]
-        dev = self.device
-        sym = torch.empty((d.height, d.width), dtype=torch.uint8, device=dev)
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        _lib.check(_lib.load().qmoe_moe_paired_decode(ctypes.addressof(self.il_struct), ctypes.byref(d), sym.data_ptr(),
-                                                    status.data_ptr(), dev.index, _s(dev)))
-        return (sym, int(status.item())) if return_status else sym
+        self.il_struct = _lib.InterleavedStore(il.data_ptr(), base.data_ptr(), self.il_table.data_ptr(),
+                                               self.il_dec.data_ptr())
 
     @property
     def resident_bytes(self) -> int:
@@ -229,15 +204,15 @@ class ExpertStore:
         if self.codes is not None:
             total += self.codes.numel() * 2
         if self.il_codes is not None:
-            total += self.il_codes.numel() * 4 + self.blk_base.numel() * 8 + 4 * (_lib.DICT_COUNT + _lib.PAIRED_TABLE)
+            total += self.il_codes.numel() * 4 + self.blk_base.numel() * 8 + 3 * 4 * _lib.DICT_COUNT
         return total
 
     def drop_reference_layout(self) -> None:
-        """Free the row-by-row streams and keep only the paired-lane copy (about half the device
+        """Free the row-by-row streams and keep only the interleaved copy (about half the device
         memory).  Afterwards :meth:`matrix` is unavailable and experts with many tokens stay on the
         per-row kernel (the tensor-core tile path reads the row-by-row streams)."""
         if self.il_codes is None:
-            raise RuntimeError("store has no paired-lane copy to fall back on")
+            raise RuntimeError("store has no interleaved copy to fall back on")
         self._code_elems = self.codes.numel()
         self.codes = None
 
@@ -483,16 +458,17 @@ def grouped_ffn(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, max
     return ys
 
 
-def work_plan(work: torch.Tensor) -> Dict[str, int]:
+def work_plan(work: torch.Tensor, max_slots: int, d_ff: int) -> Dict[str, int]:
     """What the last :func:`grouped_ffn` call that used ``work`` planned (synchronises): numbers of
     row-per-thread and row-per-warp work items of wi and wo, rows per row-per-thread item, the tile
-    items and the tokens decoded together."""
-    out = (ctypes.c_int32 * 9)()
+    items, the tokens decoded together, and the wo items that also cover their matrix's remainder
+    rows (a height that is not a multiple of 1024) one row per warp."""
+    out = (ctypes.c_int32 * 10)()
     dev = work.device
-    _lib.check(_lib.load().qmoe_moe_work_summary(work.data_ptr(), out, dev.index, _s(dev)))
+    _lib.check(_lib.load().qmoe_moe_work_summary(work.data_ptr(), int(max_slots), int(d_ff), out, dev.index, _s(dev)))
     return {"wi_items": out[0], "wo_items": out[1], "wi_warp_items": out[2], "wo_warp_items": out[3],
             "wi_rows_per_item": out[4], "wo_rows_per_item": out[5], "tile_wi_items": out[6],
-            "tile_wo_items": out[7], "group_tokens": out[8]}
+            "tile_wo_items": out[7], "group_tokens": out[8], "wo_items_with_remainder": out[9]}
 
 
 def tile_timeouts(device, reset: bool = False) -> int:

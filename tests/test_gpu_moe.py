@@ -124,43 +124,35 @@ def test_tensor_core_tile_path_for_heavily_loaded_experts(dev, small_layer):
 
 
 def _plain_copy(store, **kw):
-    """The same store without / with its own paired-lane copy."""
+    """The same store without / with a differently built interleaved copy."""
     from qmoe_b200.sub1 import ExpertStore
     return ExpertStore(store.codes, store.row_off, store.minmax, store.host_descs, store.d_model, store.d_ff, **kw)
 
 
-def test_paired_lane_copy_decodes_to_the_same_weights(dev, small_layer):
-    """The copy the grouped kernel reads is a re-tokenisation of the reference's streams (rare codes
-    cut into frequent ones, null padding): decoded with the kernel's own table and walk it must give
-    the symbols of the reference streams, bit for bit, for every matrix; and its layout must be what
-    the header says."""
-    from qmoe_b200 import _lib, sub1_cuda
+def test_interleaved_copy_holds_the_same_codes(dev, small_layer):
+    """Undo the lane interleaving and the renumbering on the host: every row's codes come back."""
     _, store = small_layer
     assert store.il_codes is not None
-    dec = sub1.DEC(dev)
-    for m, d in enumerate(store.host_descs):
-        w_comp, row_off, _ = store.matrix(m)
-        want = sub1_cuda.sub1decode(dec, w_comp.contiguous(), row_off.contiguous(), d.width)
-        got, bad = store.decode_copy(m, return_status=True)
-        assert bad == 0 and torch.equal(got, want), f"matrix {m}"
-    # layout: two codes per word, every code below the table size, rows padded with the null code
-    words = store.il_codes[:store.il_words].cpu().numpy().view(np.uint32)
-    lo, hi = words & 0xffff, words >> 16
-    assert int(max(lo.max(), hi.max())) <= _lib.PAIRED_TABLE - 1
+    il = store.il_codes.cpu().numpy().view(np.uint16).reshape(-1, 8)          # [16-byte entry, 8 codes]
     base = store.blk_base.cpu().numpy()
-    assert base[0] == 0 and base[-1] == store.il_words and ((base[1:] - base[:-1]) % 32 == 0).all()
-    # the replacement lists spell every code: frequent codes map to themselves
-    off = store.split_off.cpu().numpy().view(np.uint32)
-    remap = store.remap.cpu().numpy().view(np.uint32)
-    pieces = store.split_codes.cpu().numpy().view(np.uint16)
-    single = (off[1:] - off[:-1]) == 1
-    assert single.sum() == _lib.PAIRED_TABLE - 1 and (pieces[off[:-1][single]] == remap[single]).all()
-    assert ((off[1:] - off[:-1])[~single] >= 2).all()
+    inverse = np.empty(65536, np.int64)
+    inverse[store.remap.cpu().numpy()] = np.arange(65536)
+    codes = store.codes.cpu().numpy().view(np.uint16)
+    row_off = store.row_off.cpu().numpy()
+    for d in store.host_descs:
+        for row in range(d.height):
+            b, e = row_off[d.rowoff_base + row], row_off[d.rowoff_base + row + 1]
+            gblk, lane = (d.minmax_base + row) // 32, row % 32
+            chunks = (base[gblk + 1] - base[gblk]) // 32
+            mine = il[base[gblk] + lane:base[gblk] + 32 * chunks:32].reshape(-1)
+            assert len(mine) >= e - b
+            assert (inverse[mine[:e - b]] == codes[d.code_base + b:d.code_base + e]).all()
+            assert (mine[e - b:] == store.remap.cpu().numpy()[0] % 65536).all()   # padding = code 0, renumbered
 
 
-@pytest.mark.parametrize("variant", ["row_by_row", "copy_only"])
-def test_paired_lane_and_row_by_row_stores_give_identical_results(dev, small_layer, variant):
-    """Same weights, same order of accumulation: the layouts must agree bit for bit."""
+@pytest.mark.parametrize("variant", ["row_by_row", "interleaved_plain_numbers", "interleaved_only"])
+def test_interleaved_and_row_by_row_stores_give_identical_results(dev, small_layer, variant):
+    """Same codes, same order of accumulation: the layouts must agree bit for bit."""
     experts, store = small_layer
     counts = [3, 9, 1, 0, 4, 2, 2, 5]
     n = sum(counts)
@@ -170,6 +162,9 @@ def test_paired_lane_and_row_by_row_stores_give_identical_results(dev, small_lay
     if variant == "row_by_row":
         other = _plain_copy(store, interleave=False)
         assert other.il_codes is None
+    elif variant == "interleaved_plain_numbers":
+        other = _plain_copy(store, interleave=False)
+        other.interleave(renumber=False)
     else:
         other = _plain_copy(store)
         other.drop_reference_layout()
@@ -181,43 +176,23 @@ def test_paired_lane_and_row_by_row_stores_give_identical_results(dev, small_lay
     assert rel_err(got[:counts[0]], experts[0].oracle_ffn(xs[:counts[0]].cpu())) <= TOL
 
 
-def test_paired_lane_kernel_on_a_layer_large_enough_for_it(dev):
-    """Small layers run on the row-per-warp kernel; this one (96 experts of 1056 x 640) has enough
-    rows for the row-per-thread kernel: wi in items of up to 1024 rows plus a 32-row remainder for the
-    warps, wo in items of up to 640 rows, groups of one to four tokens, experts without tokens,
-    against the oracle."""
-    d_model, d_ff, n_exp = 640, 1056, 96
-    experts = [Expert(d_model, d_ff, seed=2, expert_id=e) for e in range(n_exp)]
-    store = store_from_experts(experts, dev)
-    assert store.il_codes is not None
-    counts = [(e * 7) % 5 for e in range(n_exp)]
-    n = sum(counts)
-    xs = synth.tokens(n, d_model, seed=6)
-    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+def test_remap_tables_reject_a_non_permutation(dev):
     from qmoe_b200 import _lib
-    nbytes = int(_lib.load().qmoe_moe_work_bytes(n_exp, n, d_model, d_ff))
-    work = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
-    ys = sub1.grouped_ffn(store, offsets, xs.to(dev), n, work=work)
-    plan = sub1.work_plan(work)
-    groups = sum((c + 3) // 4 for c in counts)
-    assert plan["group_tokens"] == 4 and plan["wi_items"] >= groups and plan["wi_warp_items"] == groups * 4
-    assert plan["wo_items"] >= groups and plan["wo_warp_items"] == 0
-    plain = _plain_copy(store, interleave=False)
-    ys_plain = sub1.grouped_ffn(plain, offsets, xs.to(dev), n)
-    assert torch.equal(ys[:n], ys_plain[:n]) or rel_err(ys[:n], ys_plain[:n]) <= 2e-3
-    pos = 0
-    for e, c in enumerate(counts):
-        if c and e % 9 == 0:
-            assert rel_err(ys[pos:pos + c], experts[e].oracle_ffn(xs[pos:pos + c])) <= TOL, (e, c)
-        pos += c
+    remap = torch.arange(65536, dtype=torch.int32, device=dev)
+    remap[7] = 8                                                  # two codes onto one number
+    tab = torch.empty(65536, dtype=torch.int32, device=dev)
+    dec_out = torch.empty(131072, dtype=torch.int32, device=dev)
+    rc = _lib.load().qmoe_sub1_remap_tables(sub1.DEC(dev).data_ptr(), remap.data_ptr(), tab.data_ptr(),
+                                            dec_out.data_ptr(), dev.index, None)
+    assert rc == _lib.ERR_INVALID_ARG
+    assert b"permutation" in _lib.load().qmoe_last_error()
 
 
 @pytest.mark.parametrize("interleave", [True, False])
 def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
     """A decoder table with an entry of four non-zeros (not expressible in the sparse form): the
-    grouped kernel must fall back to digit-by-digit decoding of that entry, for groups of one, two
-    and three tokens.  Such a table cannot be served by the paired-lane copy: asking for one leaves
-    the store on its row-by-row streams."""
+    grouped kernels must fall back to digit-by-digit decoding of that entry, in the row-by-row and in
+    the interleaved, renumbered layout, for groups of one, two and three tokens."""
     from oracle import oracle as O
     from qmoe_b200 import _lib
     from qmoe_b200.sub1 import ExpertStore
@@ -243,7 +218,8 @@ def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
         assert left == 0
         return codes[::-1] if r % 3 == 0 else codes
 
-    # wi: two items of 528 rows per group; wo: 64 rows
+    # wi: 1024 rows one per thread plus 32 one per warp in k_matmul_grouped; wo (64 rows, few in
+    # total): k_matmul_grouped_warp
     d_model, d_ff, n_exp = 64, 1056, 40
     parts, dense = [], []
     for h, w in ((d_ff, d_model), (d_model, d_ff)):
@@ -259,7 +235,7 @@ def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
     base = ExpertStore.from_matrices(parts * n_exp, d_model, d_ff)    # experts with the same two matrices
     store = ExpertStore(base.codes, base.row_off, base.minmax, base.host_descs, d_model, d_ff,
                         interleave=interleave, dec=dec2)
-    assert store.il_codes is None
+    assert (store.il_codes is not None) == interleave
     counts = [1 + e % 3 for e in range(n_exp)]
     n = sum(counts)
     xs = synth.tokens(n, d_model, seed=9)
@@ -269,6 +245,43 @@ def test_grouped_ffn_with_a_table_that_needs_the_digit_path(dev, interleave):
     want = (hidden.float() @ dense[1].t()).bfloat16()
     assert rel_err(ys, want) <= TOL
     _lib.check(_lib.load().qmoe_sub1_release(0))
+
+
+def test_tile_path_reports_a_wait_that_ran_out(dev, small_layer):
+    """Every wait of the tile kernel on an MMA-completion barrier is bounded.  With the bound lowered
+    to a single poll the first such wait gives up although nothing hangs: the CTA stops, writes
+    zeros for the rows it did not finish, and the library's sticky status word reports it until it
+    is read with reset.  (The clean-up waits before tensor memory is released keep the full bound.)"""
+    from qmoe_b200 import _lib
+    experts, store = small_layer
+    L = _lib.load()
+    counts = [0, 70, 0, 0, 0, 0, 0, 0]
+    n = sum(counts)
+    xs = synth.tokens(n, store.d_model, seed=12).to(dev)
+    offsets = torch.tensor([0] + np.cumsum(counts).tolist(), dtype=torch.int32, device=dev)
+    assert sub1.tile_timeouts(dev, reset=True) == 0
+    before = L.qmoe_moe_set_tile_min_tokens(16)
+    L.qmoe_moe_set_tile_wait_limit(1)
+    try:
+        ys = sub1.grouped_ffn(store, offsets, xs, n)
+        torch.cuda.synchronize()
+    finally:
+        L.qmoe_moe_set_tile_wait_limit(0)
+        L.qmoe_moe_set_tile_min_tokens(before)
+    assert torch.isfinite(ys.float()).all()
+    assert sub1.tile_timeouts(dev) > 0                     # sticky: still there on a second read
+    with pytest.raises(_lib.QmoeError):
+        sub1.check_tile_status(dev)                        # raises and clears
+    assert sub1.tile_timeouts(dev) == 0
+    # the same step with the default bound completes and matches the oracle
+    before = L.qmoe_moe_set_tile_min_tokens(16)
+    try:
+        ys = sub1.grouped_ffn(store, offsets, xs, n)
+        torch.cuda.synchronize()
+    finally:
+        L.qmoe_moe_set_tile_min_tokens(before)
+    assert sub1.tile_timeouts(dev) == 0
+    assert rel_err(ys, experts[1].oracle_ffn(xs.cpu())) <= TOL
 
 
 def test_tile_path_reports_a_wait_that_ran_out(dev, small_layer):

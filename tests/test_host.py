@@ -63,21 +63,19 @@ def test_argument_validation_without_gpu():
         _lib.check(lib.qmoe_sub1_pack_prepare(None, None, None, 1, 2, 0, None))
 
 
-def test_paired_lane_store_arguments_are_validated_without_gpu():
+def test_interleaved_store_arguments_are_validated_without_gpu():
     lib = _lib.load()
     fake = ctypes.c_void_p(256)
     # heights must be multiples of 32 and rows consecutive: checked on the host copy of the descriptors
     descs = (_lib.MatrixDesc * 2)(_lib.MatrixDesc(0, 10, 0, 0, 64, 32), _lib.MatrixDesc(16, 10, 65, 64, 33, 64))
-    rc = lib.qmoe_moe_paired_count(fake, fake, fake, ctypes.addressof(descs), 2, fake, fake, 0, None)
+    rc = lib.qmoe_moe_interleave_count(fake, fake, ctypes.addressof(descs), 2, fake, 0, None)
     assert rc == _lib.ERR_UNSUPPORTED and b"multiples of 32" in lib.qmoe_last_error()
     descs = (_lib.MatrixDesc * 2)(_lib.MatrixDesc(0, 10, 0, 0, 64, 32), _lib.MatrixDesc(16, 10, 65, 96, 32, 64))
-    assert lib.qmoe_moe_paired_count(fake, fake, fake, ctypes.addressof(descs), 2, fake, fake, 0, None) \
-        == _lib.ERR_UNSUPPORTED
-    assert lib.qmoe_moe_paired_count(None, fake, fake, ctypes.addressof(descs), 2, fake, fake, 0, None) \
-        == _lib.ERR_INVALID_ARG
-    assert lib.qmoe_moe_paired_emit(fake, fake, fake, 2, fake, fake, fake, ctypes.c_void_p(8), 0, None) \
+    assert lib.qmoe_moe_interleave_count(fake, fake, ctypes.addressof(descs), 2, fake, 0, None) == _lib.ERR_UNSUPPORTED
+    assert lib.qmoe_moe_interleave_count(None, fake, ctypes.addressof(descs), 2, fake, 0, None) == _lib.ERR_INVALID_ARG
+    assert lib.qmoe_moe_interleave_emit(fake, fake, fake, 2, fake, None, ctypes.c_void_p(8), 0, None) \
         == _lib.ERR_INVALID_ARG                                   # copy not 16-byte aligned
-    # grouped FFN over a paired-lane store: null store, null member, widths that are not multiples of 32
+    # grouped FFN over an interleaved store: null store, null member, widths that are not multiples of 32
     args = (fake, None, fake, fake, fake)
     tail = (fake, fake, fake, fake, fake, 4, 8)
     assert lib.qmoe_moe_grouped_ffn_interleaved(*args, None, *tail, 64, 96, 0, None) == _lib.ERR_INVALID_ARG
@@ -89,91 +87,7 @@ def test_paired_lane_store_arguments_are_validated_without_gpu():
         == _lib.ERR_UNSUPPORTED
     assert lib.qmoe_decode_attention(fake, fake, fake, fake, fake, 4, 512, 64, 0, None) == _lib.ERR_UNSUPPORTED
     assert lib.qmoe_rms_norm(None, fake, fake, 1, 8, 1e-6, 0, None) == _lib.ERR_INVALID_ARG
-    assert lib.qmoe_moe_paired_prepare(None, fake, fake, fake, fake, fake, fake, 1 << 20, fake, 0, None) \
-        == _lib.ERR_INVALID_ARG
-
-
-def _paired_plan(dec, hist):
-    lib = _lib.load()
-    n = _lib.DICT_COUNT
-    remap = np.zeros(n, np.uint32)
-    ring = np.zeros(_lib.PAIRED_TABLE, np.uint32)
-    table = np.zeros(n, np.uint32)
-    off = np.zeros(n + 1, np.uint32)
-    pieces = np.zeros(14 * n, np.uint16)
-    total = ctypes.c_int64(0)
-    rc = lib.qmoe_moe_paired_plan_host(dec.ctypes.data, hist.ctypes.data, remap.ctypes.data, ring.ctypes.data,
-                                     table.ctypes.data, off.ctypes.data, pieces.ctypes.data, pieces.size,
-                                     ctypes.byref(total))
-    return rc, remap, ring, table, off, pieces[:total.value]
-
-
-def test_paired_plan_replaces_rare_codes_by_frequent_ones_that_decode_to_the_same_digits():
-    """The re-tokenisation behind the paired-lane copy, against the oracle's view of the dictionary:
-    every code's replacement list, decoded with the kernel's table, gives the code's own digits."""
-    from oracle import oracle as O
-    dec, trie = O.build_dictionary()
-    digits, nweights = O.numpy_entry_digits(dec)                  # [65536, 28], weights per code
-    sym = O.synth_ternary(256 * 6144, 0, 7 << 32, 0.9).reshape(256, 6144)
-    codes, _ = O.encode_matrix(trie, sym)
-    hist = np.bincount(codes, minlength=_lib.DICT_COUNT).astype(np.uint64)
-    rc, remap, ring, table, off, pieces = _paired_plan(np.ascontiguousarray(dec), hist)
-    assert rc == _lib.OK
-    assert sorted(remap.tolist()) == list(range(_lib.DICT_COUNT))          # a permutation
-    null = _lib.PAIRED_TABLE - 1
-    assert ring[null] == (2 | 2 << 7 | 2 << 9) and table[null] == 0x80808000
-    assert int(pieces.max()) < null
-    # frequent codes: one piece, their own number; the most frequent code of the sample is number <= 9
-    # (only the nine one-pair codes are put in front of it)
-    assert remap[int(hist.argmax())] <= 9
-    lens = off[1:] - off[:-1]
-    assert (lens[remap < null] == 1).all() and (lens[remap >= null] >= 2).all()
-
-    def paired_digits(e):                                 # the entry layout of csrc/sub1_paired.cu
-        e = int(e)
-        out = np.zeros(28, np.int64)
-        for k, (dshift, pshift) in enumerate(((0, 2), (7, 11), (9, 16))):
-            d = (e >> dshift) & 3                             # 0 = row min, 1 = row max, 2 = none
-            if d != 2:
-                out[(e >> pshift) & 31] = d + 1
-        return out, (e >> 21) & 31
-
-    inverse = np.empty(_lib.DICT_COUNT, np.int64)
-    inverse[remap] = np.arange(_lib.DICT_COUNT)
-    rng = np.random.default_rng(0)
-    rare = np.nonzero(remap >= null)[0]
-    sample = np.concatenate([rng.choice(rare, 3000, replace=False), rng.choice(_lib.DICT_COUNT, 3000, replace=False)])
-    for c in sample:
-        got = []
-        for piece in pieces[off[c]:off[c + 1]]:
-            d, n = paired_digits(ring[piece])
-            assert n == nweights[inverse[piece]] and (d == digits[inverse[piece]]).all()
-            got.append(d[:n])
-        got = np.concatenate(got)
-        assert len(got) == nweights[c] and (got == digits[c][:nweights[c]]).all(), int(c)
-    # the row-per-warp kernel's table holds the same entries in the 4-byte form of the other kernels
-    for c in sample[:500]:
-        e = int(table[remap[c]])
-        if remap[c] == null:
-            continue
-        assert (e & 15) * 2 == nweights[c]
-        d = np.zeros(28, np.int64)
-        for k in range(3):
-            b = (e >> (8 + 8 * k)) & 0xff
-            if b < 0x80:
-                d[b] = 2 if e & (0x10 << k) else 1
-        assert (d == digits[c]).all()
-
-
-def test_paired_plan_refuses_a_table_with_a_dense_entry():
-    from oracle import oracle as O
-    dec = np.ascontiguousarray(O.build_dictionary()[0]).copy()
-    digits, nweights = O.numpy_entry_digits(dec)
-    bad = int(np.where((nweights >= 8) & ((digits != 0).sum(1) == 3))[0][0])
-    free = int(np.where(digits[bad][:nweights[bad]] == 0)[0][0])
-    dec[2 * bad + free // 14] = np.int32(np.uint32(dec[2 * bad + free // 14]) | np.uint32(2 << (4 + 2 * (free % 14))))
-    rc = _paired_plan(dec, np.ones(_lib.DICT_COUNT, np.uint64))[0]
-    assert rc == _lib.ERR_UNSUPPORTED
+    assert lib.qmoe_sub1_remap_tables(None, None, fake, fake, 0, None) == _lib.ERR_INVALID_ARG
 
 
 def test_cpu_tensors_are_rejected():
