@@ -64,8 +64,8 @@ def parse_args():
     p.add_argument("--min-seconds", type=float, default=1.0,
                    help="the timed loop of --steps steps is repeated until this much time has been timed")
     p.add_argument("--kernel-times", action="store_true",
-                   help="generate mode: also time the kernels of a decode step (torch profiler, eager launches) "
-                        "and add their average durations to the JSON line")
+                   help="also time the kernels of a step (torch profiler, eager launches) and add their average "
+                        "durations to the JSON line")
     p.add_argument("--mode", default="moe", choices=["moe", "layers", "generate", "smem-ceiling"],
                    help="moe: the MoE-layer benchmark (default); layers: the reference's per-layer matvec "
                         "benchmark (test.py --benchmark) on its six shapes; generate: end-to-end decoding; "
@@ -573,6 +573,25 @@ def run_ours(args):
         parity = parity_leg(world, rank, dev, out_chk, index_chk.reshape(-1).to(torch.int32), prob_chk, hidden_all,
                             d_model, d_ff, e_local)
 
+    kernel_times = None
+    if args.kernel_times:
+        # five eager steps under the torch profiler (CUPTI) on every rank; rank 0 reports its own
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(5):
+                step(hidden_dev)
+            torch.cuda.synchronize()
+        barrier()
+        rows = [e for e in prof.key_averages() if e.device_type == torch.autograd.DeviceType.CUDA]
+        total = sum(e.device_time_total for e in rows)
+        kernel_times = {
+            "per_step_us": round(total / 5, 1), "launches_per_step": sum(e.count for e in rows) / 5,
+            "kernels": [{"name": e.key[:70], "calls_per_step": e.count / 5,
+                         "avg_us": round(e.device_time_total / max(e.count, 1), 2),
+                         "share": round(e.device_time_total / max(total, 1e-9), 4)}
+                        for e in sorted(rows, key=lambda e: -e.device_time_total)[:24]]}
+
     # algorithmic bytes of the grouped kernels on rank 0: matrices of experts that received tokens
     idx_all = index_chk.reshape(-1).to(torch.int64)
     if world > 1:
@@ -637,6 +656,8 @@ def run_ours(args):
             "parity_check": parity,
             "clocks": clocks,
         }
+        if kernel_times is not None:
+            line["step_kernels"] = kernel_times
         if world == 1 and args.tokens_per_expert == 0 and args.experts == 0 and args.workload == "switch-c-2048":
             # the batch-1 figure: the same layer with exactly one token per expert (every one of the
             # 2048 experts active, each matrix applied to one vector), eager, event-timed launches
