@@ -63,6 +63,9 @@ def parse_args():
     p.add_argument("--no-gpu-reference", action="store_true", help="skip the timing of the reference's own kernel")
     p.add_argument("--min-seconds", type=float, default=1.0,
                    help="the timed loop of --steps steps is repeated until this much time has been timed")
+    p.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                   help="N > 1: how rows travel between ranks (peer: stored straight into the peers' memory over "
+                        "NVLink; nccl: two all-to-all collectives; auto: peer where it can be set up)")
     p.add_argument("--kernel-times", action="store_true",
                    help="also time the kernels of a step (torch profiler, eager launches) and add their average "
                         "durations to the JSON line")
@@ -435,7 +438,7 @@ def run_ours(args):
         router = "uniform top-1"
     given = None if given_all is None else given_all[rank * t_local:(rank + 1) * t_local].contiguous().to(dev)
     if world > 1:
-        layer = ExpertParallelMLP(router_weight, store, n_experts, expert_capacity=1024)
+        layer = ExpertParallelMLP(router_weight, store, n_experts, expert_capacity=1024, exchange=args.exchange)
         full = lambda h, lg: layer(h, router_logits=lg, seq_len=t_local)  # noqa: E731
     else:
         layer = sub1.FasterMLP(router_weight, store, expert_capacity=1024)
@@ -560,10 +563,11 @@ def run_ours(args):
     # status words of the timed steps: tile kernels that gave up, tokens that did not fit the exchange
     tile_timeouts = sub1.tile_timeouts(dev, reset=True)
     overflow = layer.overflow_count(reset=True) if world > 1 else 0
-    status = torch.tensor([tile_timeouts, overflow], dtype=torch.int64, device=dev)
+    peer_timeouts = layer.peer_timeouts() if world > 1 else 0
+    status = torch.tensor([tile_timeouts, overflow, peer_timeouts], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(status, op=dist.ReduceOp.SUM)
-    tile_timeouts, overflow = (int(v) for v in status.tolist())
+    tile_timeouts, overflow, peer_timeouts = (int(v) for v in status.tolist())
 
     # one more eager step whose output is checked: expert choice, router probability, layer output
     out_chk, (rl_chk, index_chk) = full(hidden_dev, given)
@@ -638,6 +642,7 @@ def run_ours(args):
                 "execution": "cuda-graph replay of the step" if gstep is not None else "eager launches",
                 "eager_ms_per_step": ms_eager / args.steps,
                 "pair_capacity": default_pair_capacity(t_local, world) if world > 1 else None,
+                "exchange": layer.exchange if world > 1 else None,
             },
             "e2e": {"value": n_tokens * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": n_tokens * d_model * 2, "d2h_bytes_per_step": n_tokens * d_model * 2},
@@ -652,7 +657,8 @@ def run_ours(args):
                 "timed_in": "the eager pass before the graph capture (CUDA events around the launches on their "
                             "stream); value and e2e come from the graph replay of the same kernels",
             },
-            "status": {"tile_timeouts": tile_timeouts, "exchange_overflow_tokens": overflow},
+            "status": {"tile_timeouts": tile_timeouts, "exchange_overflow_tokens": overflow,
+                       "peer_barrier_timeouts": peer_timeouts},
             "parity_check": parity,
             "clocks": clocks,
         }

@@ -287,6 +287,52 @@ int qmoe_moe_plan(const void *rows_dev, int64_t row_stride, int d_model, const i
                   int n_buckets, int32_t *offsets_dev, int32_t *slot_of_row_dev, int32_t *row_of_slot_dev,
                   int device, void *stream);
 
+/* The same exchange over peer memory (NVLink / NVSwitch), without a collective library in the data
+ * path.  The reference has nothing to compare: its GPUs only ever pass whole activations on
+ * (sub1.py:307-309,320).  Every rank owns a receive buffer of n_ranks * pair_capacity rows of
+ * d_model + 8 bf16 and a return buffer of n_ranks * pair_capacity rows of d_model bf16 that its peers
+ * have mapped (CUDA IPC, the driver's virtual memory API, or torch's symmetric memory); block r of
+ * either belongs to rank r.  All pointers below are addresses valid on THIS GPU.
+ *
+ * qmoe_moe_ep_dispatch_peer: qmoe_moe_ep_dispatch that stores every kept row straight into its
+ * destination's receive buffer.  dest_blocks_dev[d] (device array of n_ranks pointers) = first row
+ * of this rank's block in rank d's receive buffer.  slot_dev as above (dest * pair_capacity + rank).
+ *
+ * qmoe_moe_plan_peer: qmoe_moe_plan over the trailers of the received rows that also emits, for
+ * every slot s, the address of its result row: out_ptr_of_slot_dev[s] = out_blocks_dev[i /
+ * rows_per_block] + (i % rows_per_block) * out_row_bytes for the received row i = row_of_slot[s];
+ * out_blocks_dev[q] (device array of n_ranks addresses) = first row of this rank's block in rank
+ * q's return buffer, rows_per_block = pair_capacity.
+ *
+ * qmoe_moe_grouped_ffn_scatter: qmoe_moe_grouped_ffn_rows whose result rows are stored to the
+ * addresses y_row_ptrs_dev[s] (2-byte aligned, d_model bf16 each; may lie in a peer's memory).
+ *
+ * qmoe_moe_peer_barrier, one launch of one CTA: makes this GPU's earlier stores visible to its
+ * peers, raises flag [channel][rank] in every peer's flag block and waits for flag [channel][p] of
+ * every peer p in its own (flag_blocks_dev: device array of n_ranks pointers to the ranks' blocks of
+ * at least (channel + 1) * n_ranks int32, zeroed before first use; a flag is cleared by the rank that
+ * waited for it, so the blocks need no reset between steps).  Ranks must launch matching barriers in
+ * the same order, each on its own GPU (never two ranks on one GPU: they would wait for each other's
+ * kernels).  The waits end after limit_ms milliseconds; *status_dev is then incremented and the
+ * kernel returns: from then on the buffers' contents are undefined and the flag blocks must be
+ * zeroed again by all ranks before reuse.  Use one channel per barrier of a step. */
+int qmoe_moe_ep_dispatch_peer(const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
+                              int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *const *dest_blocks_dev,
+                              int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks, int seq_len,
+                              int expert_capacity, int pair_capacity, int d_model, int device, void *stream);
+int qmoe_moe_plan_peer(const void *rows_dev, int64_t row_stride, int d_model, int n_rows, int n_buckets,
+                       int32_t *offsets_dev, int32_t *slot_of_row_dev, int32_t *row_of_slot_dev,
+                       const uint64_t *out_blocks_dev, int rows_per_block, int64_t out_row_bytes,
+                       uint64_t *out_ptr_of_slot_dev, int device, void *stream);
+int qmoe_moe_grouped_ffn_scatter(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                                 const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
+                                 const qmoe_interleaved_store *store, const int32_t *offsets_dev, const void *xs_dev,
+                                 int64_t xs_stride, const int32_t *x_rows_dev, void *hs_dev,
+                                 const uint64_t *y_row_ptrs_dev, void *work_dev, int n_experts, int max_slots,
+                                 int d_model, int d_ff, int device, void *stream);
+int qmoe_moe_peer_barrier(int32_t *const *flag_blocks_dev, int rank, int n_ranks, int channel, int64_t limit_ms,
+                          int32_t *status_dev, int device, void *stream);
+
 /* out[token] = bf16(prob[token] * (slot >= 0 ? ys[slot] : hidden[token])): the scatter back to
  * token order, the pass-through of dropped tokens and the router-probability scaling of
  * sub1.py:312,318. */

@@ -88,6 +88,10 @@ SIGNATURES = {
     "qmoe_moe_grouped_ffn_rows": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _L, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_ep_dispatch": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_plan": (_I, [_P, _L, _I, _P, _I, _I, _P, _P, _P, _I, _P]),
+    "qmoe_moe_ep_dispatch_peer": (_I, [_P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_plan_peer": (_I, [_P, _L, _I, _I, _I, _P, _P, _P, _P, _I, _L, _P, _I, _P]),
+    "qmoe_moe_grouped_ffn_scatter": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "qmoe_moe_peer_barrier": (_I, [_P, _I, _I, _I, _L, _P, _I, _P]),
     "qmoe_moe_interleave_count": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "qmoe_moe_interleave_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine_add": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),

@@ -107,16 +107,19 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
                        int64_t xs_stride, const int32_t *x_rows, void *hs, void *ys, int64_t ys_stride,
-                       const int32_t *y_rows, void *work, int n_experts, int max_slots, int d_model, int d_ff,
-                       int device, cudaStream_t stream);
+                       const int32_t *y_rows, const unsigned long long *y_ptrs, void *work, int n_experts,
+                       int max_slots, int d_model, int d_ff, int device, cudaStream_t stream);
 int launch_keep(const int32_t *choice, int32_t *expert, int n_tokens, int n_experts, int seq_len, int capacity,
                 cudaStream_t stream);
 int launch_ep_dispatch(const int32_t *choice, const void *hidden, int64_t hidden_stride, int32_t *expert,
-                       int32_t *dest, int32_t *slot, void *send, int *overflow, int n_tokens, int n_experts,
-                       int local_experts, int seq_len, int capacity, int n_ranks, int cap, int d_model,
+                       int32_t *dest, int32_t *slot, void *send, void *const *blocks, int *overflow, int n_tokens,
+                       int n_experts, int local_experts, int seq_len, int capacity, int n_ranks, int cap, int d_model,
                        cudaStream_t stream);
 int launch_ep_plan(const void *rows, int64_t row_stride, int d_model, const int32_t *meta, int n_rows, int n_buckets,
-                   int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, cudaStream_t stream);
+                   int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, const uint64_t *out_blocks,
+                   int rows_per_block, int64_t out_row_bytes, uint64_t *out_ptr_of_slot, cudaStream_t stream);
+int launch_peer_barrier(int32_t *const *flag_blocks, int rank, int n_ranks, int channel, uint64_t limit_ns,
+                        int *status, cudaStream_t stream);
 int launch_combine_add(const void *ys, const void *hidden, const int32_t *slot, const void *prob,
                        const void *residual, void *out, int n_tokens, int d_model, cudaStream_t stream);
 int launch_route_small(const float *logits, const void *hidden, int n_tokens, int n_experts, int d_model,
@@ -502,8 +505,9 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
                              const int32_t *row_off_dev, const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
                              const qmoe_interleaved_store *ils, const int32_t *offsets_dev,
                              const void *xs_dev, int64_t xs_stride, const int32_t *x_rows_dev, void *hs_dev,
-                             void *ys_dev, int64_t ys_stride, const int32_t *y_rows_dev, void *work_dev,
-                             int n_experts, int max_slots, int d_model, int d_ff, int device, void *stream) {
+                             void *ys_dev, int64_t ys_stride, const int32_t *y_rows_dev, const uint64_t *y_ptrs_dev,
+                             void *work_dev, int n_experts, int max_slots, int d_model, int d_ff, int device,
+                             void *stream) {
   if (!(dec_dev && (codes_dev || ils) && row_off_dev && minmax_dev && descs_dev && offsets_dev && work_dev)) {
     set_error("%s: null device pointer", fn);
     return QMOE_ERR_INVALID_ARG;
@@ -525,11 +529,11 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
     return QMOE_ERR_UNSUPPORTED;
   }
   if (max_slots == 0) return QMOE_OK;
-  if (!(xs_dev && hs_dev && ys_dev)) {
+  if (!(xs_dev && hs_dev && (ys_dev || y_ptrs_dev))) {
     set_error("%s: null activation pointer", fn);
     return QMOE_ERR_INVALID_ARG;
   }
-  if (xs_stride < d_model || ys_stride < d_model) {
+  if (xs_stride < d_model || (!y_ptrs_dev && ys_stride < d_model)) {
     set_error("%s: row stride smaller than d_model", fn);
     return QMOE_ERR_INVALID_ARG;
   }
@@ -545,7 +549,8 @@ static int grouped_ffn_entry(const char *fn, const int32_t *dec_dev, const uint1
   if (rc) return rc;
   return launch_grouped_ffn(tab, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, ils,
                             offsets_dev, xs_dev, xs_stride, x_rows_dev, hs_dev, ys_dev, ys_stride, y_rows_dev,
-                            work_dev, n_experts, max_slots, d_model, d_ff, device, as_stream(stream));
+                            reinterpret_cast<const unsigned long long *>(y_ptrs_dev), work_dev, n_experts, max_slots,
+                            d_model, d_ff, device, as_stream(stream));
 }
 
 int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
@@ -553,7 +558,7 @@ int qmoe_moe_grouped_ffn(const int32_t *dec_dev, const uint16_t *codes_dev, cons
                          const void *xs_dev, void *hs_dev, void *ys_dev, void *work_dev, int n_experts,
                          int max_slots, int d_model, int d_ff, int device, void *stream) {
   return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, nullptr,
-                           offsets_dev, xs_dev, d_model, nullptr, hs_dev, ys_dev, d_model, nullptr, work_dev,
+                           offsets_dev, xs_dev, d_model, nullptr, hs_dev, ys_dev, d_model, nullptr, nullptr, work_dev,
                            n_experts, max_slots, d_model, d_ff, device, stream);
 }
 
@@ -565,7 +570,7 @@ int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *cod
                                      int device, void *stream) {
   QMOE_REQUIRE(store != nullptr, "null interleaved store");
   return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, store, offsets_dev,
-                           xs_dev, d_model, nullptr, hs_dev, ys_dev, d_model, nullptr, work_dev, n_experts,
+                           xs_dev, d_model, nullptr, hs_dev, ys_dev, d_model, nullptr, nullptr, work_dev, n_experts,
                            max_slots, d_model, d_ff, device, stream);
 }
 
@@ -576,49 +581,127 @@ int qmoe_moe_grouped_ffn_rows(const int32_t *dec_dev, const uint16_t *codes_dev,
                               int64_t ys_stride, const int32_t *y_rows_dev, void *work_dev, int n_experts,
                               int max_slots, int d_model, int d_ff, int device, void *stream) {
   return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, store, offsets_dev,
-                           xs_dev, xs_stride, x_rows_dev, hs_dev, ys_dev, ys_stride, y_rows_dev, work_dev, n_experts,
-                           max_slots, d_model, d_ff, device, stream);
+                           xs_dev, xs_stride, x_rows_dev, hs_dev, ys_dev, ys_stride, y_rows_dev, nullptr, work_dev,
+                           n_experts, max_slots, d_model, d_ff, device, stream);
+}
+
+int qmoe_moe_grouped_ffn_scatter(const int32_t *dec_dev, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                                 const void *minmax_dev, const qmoe_matrix_desc *descs_dev,
+                                 const qmoe_interleaved_store *store, const int32_t *offsets_dev, const void *xs_dev,
+                                 int64_t xs_stride, const int32_t *x_rows_dev, void *hs_dev,
+                                 const uint64_t *y_row_ptrs_dev, void *work_dev, int n_experts, int max_slots,
+                                 int d_model, int d_ff, int device, void *stream) {
+  QMOE_REQUIRE(y_row_ptrs_dev != nullptr || max_slots == 0, "null pointer list");
+  return grouped_ffn_entry(__func__, dec_dev, codes_dev, row_off_dev, minmax_dev, descs_dev, store, offsets_dev,
+                           xs_dev, xs_stride, x_rows_dev, hs_dev, nullptr, 0, nullptr, y_row_ptrs_dev, work_dev,
+                           n_experts, max_slots, d_model, d_ff, device, stream);
+}
+
+static int ep_dispatch_entry(const char *fn, const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
+                             int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *send_dev,
+                             void *const *blocks_dev, int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks,
+                             int seq_len, int expert_capacity, int pair_capacity, int d_model, int device,
+                             void *stream) {
+  const bool ok_shape = n_tokens >= 0 && n_experts >= 1 && n_ranks >= 1 && d_model >= 2 && d_model % 2 == 0 &&
+                        pair_capacity >= 0 && n_experts % n_ranks == 0 && seq_len >= 1 && n_tokens % seq_len == 0 &&
+                        expert_capacity >= 0;
+  if (!ok_shape) {
+    set_error("%s: bad shape (even d_model, experts a multiple of the ranks, tokens a multiple of seq_len)", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (n_tokens == 0 && pair_capacity == 0) return QMOE_OK;
+  if (!((send_dev || blocks_dev) && overflow_dev &&
+        (n_tokens == 0 || (choice_dev && hidden_dev && expert_dev && dest_dev && slot_dev)))) {
+    set_error("%s: null device pointer", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (hidden_stride < d_model || (reinterpret_cast<uintptr_t>(send_dev) & 3u) != 0) {
+    set_error("%s: row stride smaller than the row, or a send buffer that is not 4-byte aligned", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_ep_dispatch(choice_dev, hidden_dev, hidden_stride, expert_dev, dest_dev, slot_dev, send_dev, blocks_dev,
+                            overflow_dev, n_tokens, n_experts, n_experts / n_ranks, seq_len, expert_capacity,
+                            n_ranks, pair_capacity, d_model, as_stream(stream));
 }
 
 int qmoe_moe_ep_dispatch(const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
                          int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *send_dev,
                          int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks, int seq_len,
                          int expert_capacity, int pair_capacity, int d_model, int device, void *stream) {
-  QMOE_REQUIRE(n_tokens >= 0 && n_experts >= 1 && n_ranks >= 1 && d_model >= 2 && pair_capacity >= 0, "bad shape");
-  QMOE_REQUIRE(n_experts % n_ranks == 0, "the number of experts must be a multiple of the number of ranks");
-  QMOE_REQUIRE(d_model % 2 == 0, "d_model must be even (the trailer is a 4-byte word)");
-  QMOE_REQUIRE(seq_len >= 1 && (n_tokens % seq_len == 0), "n_tokens must be a multiple of seq_len");
-  QMOE_REQUIRE(expert_capacity >= 0, "negative capacity");
-  if (n_tokens == 0 && pair_capacity == 0) return QMOE_OK;
-  QMOE_REQUIRE(send_dev && overflow_dev && (n_tokens == 0 || (choice_dev && hidden_dev && expert_dev && dest_dev && slot_dev)),
-               "null device pointer");
-  QMOE_REQUIRE(hidden_stride >= d_model, "row stride smaller than the row");
-  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(send_dev) & 3u) == 0, "send buffer must be 4-byte aligned");
+  QMOE_REQUIRE(send_dev != nullptr || (n_tokens == 0 && pair_capacity == 0), "null send buffer");
+  return ep_dispatch_entry(__func__, choice_dev, hidden_dev, hidden_stride, expert_dev, dest_dev, slot_dev, send_dev,
+                           nullptr, overflow_dev, n_tokens, n_experts, n_ranks, seq_len, expert_capacity,
+                           pair_capacity, d_model, device, stream);
+}
+
+int qmoe_moe_ep_dispatch_peer(const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
+                              int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *const *dest_blocks_dev,
+                              int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks, int seq_len,
+                              int expert_capacity, int pair_capacity, int d_model, int device, void *stream) {
+  QMOE_REQUIRE(dest_blocks_dev != nullptr, "null block list");
+  return ep_dispatch_entry(__func__, choice_dev, hidden_dev, hidden_stride, expert_dev, dest_dev, slot_dev, nullptr,
+                           dest_blocks_dev, overflow_dev, n_tokens, n_experts, n_ranks, seq_len, expert_capacity,
+                           pair_capacity, d_model, device, stream);
+}
+
+static int plan_entry(const char *fn, const void *rows_dev, int64_t row_stride, int d_model, const int32_t *bucket_dev,
+                      int n_rows, int n_buckets, int32_t *offsets_dev, int32_t *slot_of_row_dev,
+                      int32_t *row_of_slot_dev, const uint64_t *out_blocks_dev, int rows_per_block,
+                      int64_t out_row_bytes, uint64_t *out_ptr_of_slot_dev, int device, void *stream) {
+  if (!(n_rows >= 0 && n_buckets >= 1)) {
+    set_error("%s: bad shape", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (n_buckets > 8192) {
+    set_error("%s: at most 8192 buckets (their running sizes are kept in shared memory)", fn);
+    return QMOE_ERR_UNSUPPORTED;
+  }
+  if (!(offsets_dev && (n_rows == 0 || ((rows_dev || bucket_dev) && slot_of_row_dev && row_of_slot_dev)))) {
+    set_error("%s: null device pointer", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if (rows_dev && !(d_model >= 2 && d_model % 2 == 0 && row_stride >= d_model + 2 &&
+                    (reinterpret_cast<uintptr_t>(rows_dev) & 3u) == 0 && row_stride % 2 == 0)) {
+    set_error("%s: rows with a trailer need an even d_model, a stride that holds the trailer and 4-byte alignment", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_ep_dispatch(choice_dev, hidden_dev, hidden_stride, expert_dev, dest_dev, slot_dev, send_dev,
-                            overflow_dev, n_tokens, n_experts, n_experts / n_ranks, seq_len, expert_capacity,
-                            n_ranks, pair_capacity, d_model, as_stream(stream));
+  return launch_ep_plan(rows_dev, row_stride, d_model, bucket_dev, n_rows, n_buckets, offsets_dev, slot_of_row_dev,
+                        row_of_slot_dev, out_blocks_dev, rows_per_block, out_row_bytes, out_ptr_of_slot_dev,
+                        as_stream(stream));
 }
 
 int qmoe_moe_plan(const void *rows_dev, int64_t row_stride, int d_model, const int32_t *bucket_dev, int n_rows,
                   int n_buckets, int32_t *offsets_dev, int32_t *slot_of_row_dev, int32_t *row_of_slot_dev,
                   int device, void *stream) {
-  QMOE_REQUIRE(n_rows >= 0 && n_buckets >= 1, "bad shape");
-  if (n_buckets > 8192) {
-    set_error("%s: at most 8192 buckets (their running sizes are kept in shared memory)", __func__);
-    return QMOE_ERR_UNSUPPORTED;
-  }
-  QMOE_REQUIRE(offsets_dev != nullptr, "null offsets pointer");
-  QMOE_REQUIRE(n_rows == 0 || ((rows_dev || bucket_dev) && slot_of_row_dev && row_of_slot_dev),
-               "null device pointer");
-  QMOE_REQUIRE(!rows_dev || (d_model >= 2 && d_model % 2 == 0 && row_stride >= d_model + 2 &&
-                             (reinterpret_cast<uintptr_t>(rows_dev) & 3u) == 0 && row_stride % 2 == 0),
-               "rows with a trailer need an even d_model, a stride that holds the trailer and 4-byte alignment");
+  return plan_entry(__func__, rows_dev, row_stride, d_model, bucket_dev, n_rows, n_buckets, offsets_dev,
+                    slot_of_row_dev, row_of_slot_dev, nullptr, 0, 0, nullptr, device, stream);
+}
+
+int qmoe_moe_plan_peer(const void *rows_dev, int64_t row_stride, int d_model, int n_rows, int n_buckets,
+                       int32_t *offsets_dev, int32_t *slot_of_row_dev, int32_t *row_of_slot_dev,
+                       const uint64_t *out_blocks_dev, int rows_per_block, int64_t out_row_bytes,
+                       uint64_t *out_ptr_of_slot_dev, int device, void *stream) {
+  QMOE_REQUIRE(rows_dev != nullptr || n_rows == 0, "null rows pointer");
+  QMOE_REQUIRE(out_blocks_dev && out_ptr_of_slot_dev && rows_per_block >= 1 && out_row_bytes >= 2 &&
+                   out_row_bytes % 2 == 0,
+               "bad output block list");
+  return plan_entry(__func__, rows_dev, row_stride, d_model, nullptr, n_rows, n_buckets, offsets_dev, slot_of_row_dev,
+                    row_of_slot_dev, out_blocks_dev, rows_per_block, out_row_bytes, out_ptr_of_slot_dev, device, stream);
+}
+
+int qmoe_moe_peer_barrier(int32_t *const *flag_blocks_dev, int rank, int n_ranks, int channel, int64_t limit_ms,
+                          int32_t *status_dev, int device, void *stream) {
+  QMOE_REQUIRE(flag_blocks_dev && status_dev, "null device pointer");
+  QMOE_REQUIRE(n_ranks >= 1 && n_ranks <= 1024 && rank >= 0 && rank < n_ranks && channel >= 0, "bad rank or channel");
+  QMOE_REQUIRE(limit_ms >= 1, "the wait needs a limit of at least a millisecond");
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_ep_plan(rows_dev, row_stride, d_model, bucket_dev, n_rows, n_buckets, offsets_dev,
-                        slot_of_row_dev, row_of_slot_dev, as_stream(stream));
+  return launch_peer_barrier(flag_blocks_dev, rank, n_ranks, channel, (uint64_t)limit_ms * 1000000ull, status_dev,
+                             as_stream(stream));
 }
 
 int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev, int device,

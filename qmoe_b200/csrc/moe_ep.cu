@@ -7,6 +7,13 @@
 //
 // Nothing here copies a row twice: the grouped FFN reads its input rows through the plan's row list
 // and writes its output rows back to the same places, so there is no permute / un-permute pass.
+//
+// Exchange over peer memory: with `blocks` (one pointer per destination rank, each the part of that
+// rank's receive buffer reserved for rows from this rank, as mapped into this GPU's address space)
+// k_ep_keep and k_ep_pack store rows straight into the destinations' memory, and k_ep_plan can emit
+// for every slot the address of its output row in the source rank's return buffer, which the
+// grouped FFN then stores to.  k_peer_barrier orders the two sides: every rank raises one flag per
+// peer in the peer's memory and waits for the peers' flags in its own, with a time limit.
 #include "common.cuh"
 
 namespace qmoe {
@@ -29,10 +36,15 @@ __device__ __forceinline__ int block_sum(int v, int *s_warp) {
 // reset to "empty" (-1).
 __global__ void k_ep_keep(const int32_t *__restrict__ choice, int32_t *__restrict__ expert,
                           int32_t *__restrict__ dest, int n_tokens, int n_experts, int local_experts,
-                          int seq_len, int capacity, __nv_bfloat16 *__restrict__ send, int n_slots,
+                          int seq_len, int capacity, __nv_bfloat16 *__restrict__ send,
+                          __nv_bfloat16 *const *__restrict__ blocks, int cap, int n_slots,
                           long long row_stride, int d_model) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n_slots) *reinterpret_cast<int32_t *>(send + (long long)i * row_stride + d_model) = -1;
+  if (i < n_slots) {
+    __nv_bfloat16 *row = blocks != nullptr ? blocks[i / cap] + (long long)(i % cap) * row_stride
+                                           : send + (long long)i * row_stride;
+    *reinterpret_cast<int32_t *>(row + d_model) = -1;
+  }
   if (i >= n_tokens) return;
   const int c = choice[i];
   int keep = c >= 0 && c < n_experts;
@@ -52,7 +64,8 @@ __global__ void k_ep_keep(const int32_t *__restrict__ choice, int32_t *__restric
 // layer like a token dropped by the capacity rule) and *overflow is incremented (never cleared here).
 __global__ void __launch_bounds__(128) k_ep_pack(const int32_t *__restrict__ expert, const int32_t *__restrict__ dest,
                                                  const __nv_bfloat16 *__restrict__ hidden, long long hidden_stride,
-                                                 __nv_bfloat16 *__restrict__ send, long long row_stride,
+                                                 __nv_bfloat16 *__restrict__ send,
+                                                 __nv_bfloat16 *const *__restrict__ blocks, long long row_stride,
                                                  int32_t *__restrict__ slot, int *overflow, int d_model,
                                                  int local_experts, int cap) {
   __shared__ int s_warp[4];
@@ -73,7 +86,7 @@ __global__ void __launch_bounds__(128) k_ep_pack(const int32_t *__restrict__ exp
     return;
   }
   const int s = dst * cap + rank;
-  __nv_bfloat16 *row = send + (long long)s * row_stride;
+  __nv_bfloat16 *row = blocks != nullptr ? blocks[dst] + (long long)rank * row_stride : send + (long long)s * row_stride;
   const __nv_bfloat16 *src = hidden + (long long)t * hidden_stride;
   if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(row)) & 15u) == 0 && (d_model & 7) == 0) {
     for (int i = threadIdx.x; i < d_model / 8; i += blockDim.x)
@@ -96,7 +109,9 @@ __global__ void __launch_bounds__(128) k_ep_pack(const int32_t *__restrict__ exp
 __global__ void __launch_bounds__(1024) k_ep_plan(const __nv_bfloat16 *__restrict__ rows, long long row_stride,
                                                   int d_model, const int32_t *__restrict__ meta_in, int n_rows,
                                                   int n_buckets, int32_t *__restrict__ offsets,
-                                                  int32_t *__restrict__ slot_of_row, int32_t *__restrict__ row_of_slot) {
+                                                  int32_t *__restrict__ slot_of_row, int32_t *__restrict__ row_of_slot,
+                                                  const unsigned long long *__restrict__ out_blocks, int rows_per_block,
+                                                  long long out_row_bytes, unsigned long long *__restrict__ out_ptr_of_slot) {
   extern __shared__ int s_count[];  // running size of every bucket
   __shared__ int s_warp[32];
   __shared__ int s_carry;
@@ -168,34 +183,89 @@ __global__ void __launch_bounds__(1024) k_ep_plan(const __nv_bfloat16 *__restric
     const int s = s_count[b] + rank;
     slot_of_row[i] = s;
     row_of_slot[s] = i;
+    // row i came from rank i / rows_per_block; its result goes to the same place of that rank's block
+    if (out_ptr_of_slot != nullptr)
+      out_ptr_of_slot[s] = out_blocks[i / rows_per_block] + (unsigned long long)(i % rows_per_block) * out_row_bytes;
   }
 }
 
+// One CTA, one thread per rank.  Thread p raises flag [channel][rank] in rank p's flag block (waiting
+// first, if need be, until the flag of the previous round was taken) and then takes flag [channel][p]
+// from this rank's own block.  Before the flags all earlier stores of this GPU (rows written into
+// peers' memory by the kernels launched before) are made visible system-wide.  Both waits end after
+// `limit_ns`: the kernel then adds 1 to *status and returns, and the exchange buffers must not be
+// trusted any more.
+__global__ void k_peer_barrier(int32_t *const *__restrict__ flag_blocks, int rank, int n_ranks, int channel,
+                               unsigned long long limit_ns, int *status) {
+  const int p = threadIdx.x;
+  __threadfence_system();
+  if (p < n_ranks && p != rank) {
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    auto expired = [&]() {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      return t - t0 > limit_ns;
+    };
+    int32_t *theirs = flag_blocks[p] + channel * n_ranks + rank;
+    int32_t *mine = flag_blocks[rank] + channel * n_ranks + p;
+    bool ok = true;
+    while (atomicCAS_system(theirs, 0, 1) != 0) {
+      if (expired()) {
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+    while (ok && atomicCAS_system(mine, 1, 0) != 1) {
+      if (expired()) {
+        ok = false;
+        break;
+      }
+      __nanosleep(100);
+    }
+    if (!ok) atomicAdd(status, 1);
+  }
+  __threadfence_system();
+}
+
 int launch_ep_dispatch(const int32_t *choice, const void *hidden, int64_t hidden_stride, int32_t *expert,
-                       int32_t *dest, int32_t *slot, void *send, int *overflow, int n_tokens, int n_experts,
-                       int local_experts, int seq_len, int capacity, int n_ranks, int cap, int d_model,
+                       int32_t *dest, int32_t *slot, void *send, void *const *blocks, int *overflow, int n_tokens,
+                       int n_experts, int local_experts, int seq_len, int capacity, int n_ranks, int cap, int d_model,
                        cudaStream_t stream) {
   const int n_slots = n_ranks * cap;
   const long long row_stride = d_model + 8;
   const int threads = 256;
   const int n = n_tokens > n_slots ? n_tokens : n_slots;
   QMOE_LAUNCH(k_ep_keep, (n + threads - 1) / threads, threads, 0, stream, choice, expert, dest, n_tokens, n_experts,
-              local_experts, seq_len, capacity, reinterpret_cast<__nv_bfloat16 *>(send), n_slots, row_stride, d_model);
+              local_experts, seq_len, capacity, reinterpret_cast<__nv_bfloat16 *>(send),
+              reinterpret_cast<__nv_bfloat16 *const *>(blocks), cap > 0 ? cap : 1, n_slots, row_stride, d_model);
   QMOE_CUDA(cudaGetLastError());
   if (n_tokens > 0) {
     QMOE_LAUNCH(k_ep_pack, n_tokens, 128, 0, stream, expert, dest, reinterpret_cast<const __nv_bfloat16 *>(hidden),
-                (long long)hidden_stride, reinterpret_cast<__nv_bfloat16 *>(send), row_stride, slot, overflow, d_model,
-                local_experts, cap);
+                (long long)hidden_stride, reinterpret_cast<__nv_bfloat16 *>(send),
+                reinterpret_cast<__nv_bfloat16 *const *>(blocks), row_stride, slot, overflow, d_model, local_experts, cap);
     QMOE_CUDA(cudaGetLastError());
   }
   return QMOE_OK;
 }
 
 int launch_ep_plan(const void *rows, int64_t row_stride, int d_model, const int32_t *meta, int n_rows, int n_buckets,
-                   int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, cudaStream_t stream) {
+                   int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, const uint64_t *out_blocks,
+                   int rows_per_block, int64_t out_row_bytes, uint64_t *out_ptr_of_slot, cudaStream_t stream) {
   QMOE_LAUNCH(k_ep_plan, 1, 1024, sizeof(int) * (size_t)n_buckets, stream,
               reinterpret_cast<const __nv_bfloat16 *>(rows), (long long)row_stride, d_model, meta, n_rows, n_buckets,
-              offsets, slot_of_row, row_of_slot);
+              offsets, slot_of_row, row_of_slot, reinterpret_cast<const unsigned long long *>(out_blocks),
+              rows_per_block > 0 ? rows_per_block : 1, (long long)out_row_bytes,
+              reinterpret_cast<unsigned long long *>(out_ptr_of_slot));
+  QMOE_CUDA(cudaGetLastError());
+  return QMOE_OK;
+}
+
+int launch_peer_barrier(int32_t *const *flag_blocks, int rank, int n_ranks, int channel, uint64_t limit_ns,
+                        int *status, cudaStream_t stream) {
+  QMOE_LAUNCH(k_peer_barrier, 1, (unsigned)((n_ranks + 31) / 32 * 32), 0, stream, flag_blocks, rank, n_ranks, channel,
+              (unsigned long long)limit_ns, status);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

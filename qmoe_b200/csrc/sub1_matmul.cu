@@ -185,6 +185,8 @@ struct MatmulArgs {
   __nv_bfloat16 *y;
   long long x_stride, y_stride;
   const int32_t *x_rows, *y_rows;  // grouped mode: token t reads row x_rows[t] / writes row y_rows[t] (null: t)
+  const unsigned long long *y_ptrs;  // grouped mode, optional: address of token t's output row (then y, y_stride
+                                     // and y_rows are not used); the row may lie in another GPU's memory
   const int4 *items;  // grouped mode: {matrix, first row, first token, rows | tokens << 16}
   int *header;        // grouped mode: header[0] = item count, header[1] = fetch counter
   int chunks, rpc, tokens;  // uniform mode
@@ -202,8 +204,13 @@ __device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink
     if (t < ntok) {
       // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
       float v = bf16_round(sink.acc[t]);
-      const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + t] : tok0 + t;
-      __nv_bfloat16 *yp = a.y + out_row * a.y_stride + row;
+      __nv_bfloat16 *yp;
+      if (a.y_ptrs != nullptr) {
+        yp = reinterpret_cast<__nv_bfloat16 *>(a.y_ptrs[tok0 + t]) + row;
+      } else {
+        const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + t] : tok0 + t;
+        yp = a.y + out_row * a.y_stride + row;
+      }
       if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
       if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
       *yp = __float2bfloat16_rn(v);
@@ -889,6 +896,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_total;
+  __shared__ unsigned long long s_best;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto group_count = [&](int e, int &first, int &count) {
     first = 0;
@@ -926,20 +934,24 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       if (use_warp && H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) main_rows = H - rest;
       // c equal items per pair: the c that fills whole rounds of the SMs best (190 pairs x 2 items
       // over 148 SMs are 2.6 rounds that cost 3; 3 items of 704 rows are 3.9 rounds that cost 4 x 0.69)
+      // Candidate c0 + tid is priced by thread tid; the cheapest (the smallest c among equals) wins.
       const int c0 = (main_rows + kGroupedThreads - 1) / kGroupedThreads;
-      int best_rows = ((main_rows + c0 - 1) / c0 + 31) / 32 * 32;
-      long long best_cost = -1;
-      for (int c = c0; c <= c0 + 64 && c * 32 <= main_rows; c++) {
-        const int rows = ((main_rows + c - 1) / c + 31) / 32 * 32;
-        const int per_pair = (main_rows + rows - 1) / rows;
-        if (c > c0 && (long long)total * per_pair > p.capacity) break;
-        const long long rounds = ((long long)total * per_pair + sms - 1) / sms;
-        const long long cost = rounds * (rows + kItemOverheadRows);
-        if (best_cost < 0 || cost < best_cost) {
-          best_cost = cost;
-          best_rows = rows;
+      if (tid == 0) s_best = ~0ull;
+      __syncthreads();
+      if (tid <= 64) {
+        const int c = c0 + tid;
+        if (c * 32 <= main_rows || tid == 0) {
+          const int rows = ((main_rows + c - 1) / c + 31) / 32 * 32;
+          const int per_pair = (main_rows + rows - 1) / rows;
+          if (tid == 0 || (long long)total * per_pair <= p.capacity) {
+            const unsigned long long rounds = ((unsigned long long)total * per_pair + sms - 1) / sms;
+            const unsigned long long cost = rounds * (unsigned long long)(rows + kItemOverheadRows);
+            atomicMin(&s_best, (cost << 24) | ((unsigned long long)tid << 16) | (unsigned long long)rows);
+          }
         }
       }
+      __syncthreads();
+      const int best_rows = (int)(s_best & 0xffffull);
       rpc = best_rows;
     }
     const int chunks = (main_rows + rpc - 1) / rpc;
@@ -1031,8 +1043,8 @@ int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, 
                            int max_slots, int *header, int4 *items_wi, int4 *items_wo, cudaStream_t stream);
 int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, const int *n_items, int flags,
-                      int max_items, int device, cudaStream_t stream);
+                      const int32_t *x_rows, const int32_t *y_rows, const unsigned long long *y_ptrs, const int4 *items,
+                      const int *n_items, int flags, int max_items, int device, cudaStream_t stream);
 
 // Experts with at least this many tokens take the tile path (0 disables it).  The default is the
 // measured break-even on a switch-large-128 layer with a skewed router (eight hot experts share half
@@ -1109,8 +1121,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                        const int32_t *row_off, const void *minmax, const qmoe_matrix_desc *descs,
                        const qmoe_interleaved_store *ils, const int32_t *offsets, const void *xs,
                        int64_t xs_stride, const int32_t *x_rows, void *hs, void *ys, int64_t ys_stride,
-                       const int32_t *y_rows, void *work, int n_experts, int max_slots, int d_model, int d_ff,
-                       int device, cudaStream_t stream) {
+                       const int32_t *y_rows, const unsigned long long *y_ptrs, void *work, int n_experts,
+                       int max_slots, int d_model, int d_ff, int device, cudaStream_t stream) {
   int rc = ensure_smem_limits(device);
   if (rc) return rc;
   const int sms = sm_count(device);
@@ -1169,6 +1181,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     a.y_stride = phase == 0 ? d_ff : ys_stride;
     a.x_rows = phase == 0 ? x_rows : nullptr;   // the hidden activation in between is indexed by slot
     a.y_rows = phase == 0 ? nullptr : y_rows;
+    a.y_ptrs = phase == 0 ? nullptr : y_ptrs;
     a.items = ph[phase].items;
     a.header = header + 2 * phase;
     a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
@@ -1178,7 +1191,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     if (tile_min > 0) {
       const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
       rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
-                             a.x_rows, a.y_rows, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
+                             a.x_rows, a.y_rows, a.y_ptrs, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
       if (rc) return rc;
     }

@@ -47,6 +47,7 @@ struct TileArgs {
   __nv_bfloat16 *y;
   long long x_stride, y_stride;
   const int32_t *x_rows, *y_rows;  // token t reads row x_rows[t] / writes row y_rows[t] (null: t)
+  const unsigned long long *y_ptrs;  // optional: address of token t's output row (replaces y, y_stride, y_rows)
   const int4 *items;   // {matrix, first row, first token, tokens}
   const int *n_items;  // device scalar
   int *status;         // device word: incremented when a bounded wait gives up (sticky)
@@ -144,6 +145,12 @@ __device__ __forceinline__ void named_arrive(int id, int count) {
 //            the A tile, synchronise among themselves, and one thread issues the eight K=16 MMAs and
 //            commits them to the stage's mbarrier.
 // The stagers run up to one window ahead of the decoders, and the tensor core runs behind both.
+__device__ __forceinline__ __nv_bfloat16 *out_row_ptr(const TileArgs &a, int tok) {
+  if (a.y_ptrs != nullptr) return reinterpret_cast<__nv_bfloat16 *>(a.y_ptrs[tok]);
+  const long long out_row = a.y_rows != nullptr ? a.y_rows[tok] : tok;
+  return a.y + out_row * a.y_stride;
+}
+
 __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs a) {
   constexpr int kABytes = kTileChunks * kTileM * 16;  // [column chunk][row][8 bf16]
   constexpr int kBBytes = kTileChunks * kTileN * 16;  // [column chunk][token][8 bf16]
@@ -156,6 +163,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
   const bool decoder = tid < kTileM;
   const int t = decoder ? tid : tid - kTileM;  // index inside the warpgroup
   const uint32_t mbar0 = smem_u32(&s_mbar[0]), mbar1 = smem_u32(&s_mbar[1]);
+  if (*a.n_items <= 0) return;  // nothing routed to the tile path this step (uniform over the grid)
 
   if (tid == 0) {
     mbar_init(mbar0, 1);
@@ -340,8 +348,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
         const qmoe_matrix_desc rd = a.descs[ri.x];
         for (int i = tid; i < kTileM * ri.w; i += kTileThreads) {
           const int r = ri.y + (i % kTileM), n = i / kTileM;
-          const long long out_row = a.y_rows != nullptr ? a.y_rows[ri.z + n] : ri.z + n;
-          if (r < rd.height) a.y[out_row * a.y_stride + r] = __float2bfloat16_rn(0.f);
+          if (r < rd.height) out_row_ptr(a, ri.z + n)[r] = __float2bfloat16_rn(0.f);
         }
       }
       break;
@@ -361,8 +368,7 @@ __global__ void __launch_bounds__(kTileThreads, 1) k_tile_matmul(const TileArgs 
           if (valid_row && n < ntok) {
             float r = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
             if (a.flags & QMOE_FLAG_RELU) r = fmaxf(r, 0.f);
-            const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + n] : tok0 + n;
-            a.y[out_row * a.y_stride + row] = __float2bfloat16_rn(r);
+            out_row_ptr(a, tok0 + n)[row] = __float2bfloat16_rn(r);
           }
         }
       }
@@ -437,8 +443,8 @@ int launch_build_tile_work(const int32_t *offsets, int n_experts, int tile_min, 
 // One linear (wi or wo) of every expert on the tile path.
 int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t *row_off, const void *minmax,
                       const qmoe_matrix_desc *descs, const void *x, void *y, long long x_stride, long long y_stride,
-                      const int32_t *x_rows, const int32_t *y_rows, const int4 *items, const int *n_items, int flags,
-                      int max_items, int device, cudaStream_t stream) {
+                      const int32_t *x_rows, const int32_t *y_rows, const unsigned long long *y_ptrs, const int4 *items,
+                      const int *n_items, int flags, int max_items, int device, cudaStream_t stream) {
   TileArgs a{};
   a.tab = tab;
   a.codes = codes;
@@ -451,6 +457,7 @@ int launch_tile_phase(const uint32_t *tab, const uint16_t *codes, const int32_t 
   a.y_stride = y_stride;
   a.x_rows = x_rows;
   a.y_rows = y_rows;
+  a.y_ptrs = y_ptrs;
   a.items = items;
   a.n_items = n_items;
   a.status = tile_status_word(device);

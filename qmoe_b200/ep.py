@@ -20,12 +20,22 @@ router probability, exactly like a token dropped by the router's own capacity ru
 in ``overflow_count()``.  ``pair_capacity=n_local`` (or ``exact=True``, which re-runs an overflowing
 step at the worst case after a host check) never drops one.
 
+Two ways to move the rows (``exchange``): ``"nccl"``, two ``all_to_all_single`` calls, and
+``"peer"``, where the packing kernel stores every row straight into its destination's receive
+buffer and the grouped FFN stores every result row straight into the source's return buffer, both
+in peer-mapped memory over NVLink (:mod:`qmoe_b200.peer`), with one small barrier kernel after each
+side.  ``"auto"`` (the default; environment variable ``QMOE_EP_EXCHANGE`` overrides it) takes
+``"peer"`` on GPUs when every rank has its own GPU and symmetric memory can be set up, else NCCL.
+Both give the same bits.
+
 The device work goes through an ``ops`` namespace, by default the CUDA entry points of
 :mod:`qmoe_b200.sub1`; the CPU test-suite substitutes a torch re-statement to check the index
 arithmetic and the exchanges among gloo ranks.
 """
 from __future__ import annotations
 
+import os
+import warnings
 from typing import Optional
 
 import torch
@@ -52,7 +62,7 @@ class ExpertParallelMLP:
 
     def __init__(self, router_weight: Optional[torch.Tensor], store, n_experts: int,
                  group: Optional[dist.ProcessGroup] = None, expert_capacity: int = 1024,
-                 pair_capacity: Optional[int] = None, ops=None, exact: bool = False):
+                 pair_capacity: Optional[int] = None, ops=None, exact: bool = False, exchange: str = "auto"):
         self.ops = ops if ops is not None else _default_ops()
         self.store = store
         self.group = group
@@ -68,6 +78,13 @@ class ExpertParallelMLP:
         self.pair_capacity = pair_capacity
         self.exact = bool(exact)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=store.device)
+        exchange = os.environ.get("QMOE_EP_EXCHANGE", exchange)
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'nccl'")
+        if self.world <= 1 or (exchange == "auto" and (ops is not None or store.device.type != "cuda")):
+            exchange = "nccl"
+        self.exchange = exchange
+        self._peer = {}  # (pair capacity, d_model) -> PeerBuffers
         self.router = None
         if router_weight is not None:
             from .sub1 import RouterClassifier
@@ -84,6 +101,26 @@ class ExpertParallelMLP:
             self.overflow.zero_()
         return n
 
+    def _peer_buffers(self, cap: int, d: int):
+        """Peer-mapped exchange buffers for this capacity (a collective call on first use), or None
+        after falling back to NCCL."""
+        key = (cap, d)
+        if key not in self._peer:
+            from .peer import PeerBuffers
+            try:
+                self._peer[key] = PeerBuffers.create(self.group, self.store.device, cap, d)
+            except Exception as exc:  # no symmetric memory in this build, ranks sharing a GPU, ...
+                if self.exchange == "peer":
+                    raise
+                warnings.warn(f"expert-parallel exchange falls back to NCCL: {exc}")
+                self.exchange = "nccl"
+                return None
+        return self._peer[key]
+
+    def peer_timeouts(self) -> int:
+        """Barrier waits of the peer exchange that ran out of time (device-to-host reads)."""
+        return sum(p.timeouts() for p in self._peer.values())
+
     def forward(self, hidden: torch.Tensor, router_logits: Optional[torch.Tensor] = None, seq_len: int = 0,
                 pair_capacity: Optional[int] = None):
         """``hidden`` bf16 [n_local, d_model] (every rank passes the same n_local)."""
@@ -96,9 +133,14 @@ class ExpertParallelMLP:
         choice, prob = ops.route_top1(router_logits.reshape(n, self.n_experts).float().contiguous())
         if self.exact and cap < n:
             before = self.overflow_count()
+        peer = self._peer_buffers(cap, d) if self.exchange != "nccl" else None
         # capacity rule on the global expert id, destination rank, rows packed into exchange slots
-        expert, slot, send = ops.ep_dispatch(choice, hidden, self.n_experts, G, seq_len, self.expert_capacity, cap,
-                                             self.overflow)
+        if peer is not None:
+            expert, slot = ops.ep_dispatch_peer(choice, hidden, self.n_experts, G, seq_len, self.expert_capacity,
+                                                cap, self.overflow, peer.dest_blocks)
+        else:
+            expert, slot, send = ops.ep_dispatch(choice, hidden, self.n_experts, G, seq_len, self.expert_capacity,
+                                                 cap, self.overflow)
         if self.exact and cap < n:
             # every rank must take the same branch: the largest overflow decides
             over = torch.tensor([self.overflow_count() - before], dtype=torch.int32, device=hidden.device)
@@ -108,6 +150,16 @@ class ExpertParallelMLP:
                 self.overflow.fill_(before)
                 return self.forward(hidden, router_logits, seq_len, pair_capacity=n)
 
+        if peer is not None:
+            # the rows are in the peers' memory already: wait until everybody's are in ours, group them by
+            # local expert and let the FFN store every result where its source rank will read it
+            peer.barrier(0)
+            offsets_r, _, row_of_slot, out_ptrs = ops.plan_rows_peer(self.local_experts, peer.recv, d,
+                                                                     peer.out_blocks, cap, 2 * d)
+            ops.grouped_ffn_scatter(self.store, offsets_r, peer.recv, row_of_slot, out_ptrs, G * cap)
+            peer.barrier(1)
+            out = ops.combine(peer.ret, hidden, slot, prob)
+            return out, (router_logits, torch.clamp(expert, min=0).to(torch.int64))
         if G > 1:
             recv = torch.empty_like(send)
             dist.all_to_all_single(recv, send, group=self.group)

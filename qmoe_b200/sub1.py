@@ -402,6 +402,67 @@ def ep_dispatch(choice: torch.Tensor, hidden: torch.Tensor, n_experts: int, n_ra
     return expert, slot, send
 
 
+def ep_dispatch_peer(choice: torch.Tensor, hidden: torch.Tensor, n_experts: int, n_ranks: int, seq_len: int,
+                     expert_capacity: int, pair_capacity: int, overflow: torch.Tensor, dest_blocks: torch.Tensor):
+    """:func:`ep_dispatch` that stores the kept rows straight into the destinations' receive buffers
+    (``dest_blocks`` int64[n_ranks]: where this rank's block starts in every rank's buffer, as
+    addresses valid on this GPU).  Returns (expert, slot)."""
+    n, d = hidden.shape
+    dev = hidden.device
+    expert = torch.empty(n, dtype=torch.int32, device=dev)
+    dest = torch.empty(n, dtype=torch.int32, device=dev)
+    slot = torch.empty(n, dtype=torch.int32, device=dev)
+    assert hidden.dtype == torch.bfloat16 and hidden.stride(1) == 1 and choice.dtype == torch.int32
+    assert dest_blocks.dtype == torch.int64 and dest_blocks.numel() == n_ranks and dest_blocks.is_cuda
+    _lib.check(_lib.load().qmoe_moe_ep_dispatch_peer(
+        choice.data_ptr(), hidden.data_ptr(), hidden.stride(0), expert.data_ptr(), dest.data_ptr(), slot.data_ptr(),
+        dest_blocks.data_ptr(), overflow.data_ptr(), n, int(n_experts), int(n_ranks), max(int(seq_len), 1),
+        int(expert_capacity), int(pair_capacity), d, dev.index, _s(dev)))
+    return expert, slot
+
+
+def plan_rows_peer(n_buckets: int, rows: torch.Tensor, d_model: int, out_blocks: torch.Tensor, rows_per_block: int,
+                   out_row_bytes: int):
+    """:func:`plan_rows` over received rows that also returns, per slot, the address of its result
+    row in the source rank's return buffer (int64[m])."""
+    m = rows.shape[0]
+    dev = rows.device
+    offsets = torch.empty(n_buckets + 1, dtype=torch.int32, device=dev)
+    slot_of_row = torch.empty(m, dtype=torch.int32, device=dev)
+    row_of_slot = torch.zeros(m, dtype=torch.int32, device=dev)
+    out_ptrs = torch.zeros(m, dtype=torch.int64, device=dev)
+    assert rows.dtype == torch.bfloat16 and rows.stride(1) == 1 and rows.shape[1] >= d_model + 2
+    assert out_blocks.dtype == torch.int64 and out_blocks.is_cuda
+    _lib.check(_lib.load().qmoe_moe_plan_peer(
+        rows.data_ptr(), rows.stride(0), int(d_model), m, int(n_buckets), offsets.data_ptr(), slot_of_row.data_ptr(),
+        row_of_slot.data_ptr(), out_blocks.data_ptr(), int(rows_per_block), int(out_row_bytes), out_ptrs.data_ptr(),
+        dev.index, _s(dev)))
+    return offsets, slot_of_row, row_of_slot, out_ptrs
+
+
+def grouped_ffn_scatter(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, x_rows: Optional[torch.Tensor],
+                        y_row_ptrs: torch.Tensor, max_slots: int, work: Optional[torch.Tensor] = None) -> None:
+    """:func:`grouped_ffn_rows` whose result of slot ``s`` is stored at the address ``y_row_ptrs[s]``
+    (``d_model`` bf16; the row may lie in a peer GPU's memory)."""
+    dev = store.device
+    L = _lib.load()
+    if max_slots == 0:
+        return
+    hs = torch.empty((max_slots, store.d_ff), dtype=torch.bfloat16, device=dev)
+    nbytes = int(L.qmoe_moe_work_bytes(store.n_experts, max_slots, store.d_model, store.d_ff))
+    if work is None or work.numel() < nbytes:
+        work = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    assert xs.dtype == torch.bfloat16 and xs.stride(1) == 1 and y_row_ptrs.dtype == torch.int64
+    dec = store.dec if store.dec is not None else DEC(dev)
+    _lib.check(L.qmoe_moe_grouped_ffn_scatter(
+        dec.data_ptr(), None if store.codes is None else store.codes.data_ptr(), store.row_off.data_ptr(),
+        store.minmax.data_ptr(), store.descs.data_ptr(),
+        ctypes.addressof(store.il_struct) if store.il_codes is not None else None, offsets.data_ptr(),
+        xs.data_ptr(), xs.stride(0), None if x_rows is None else x_rows.data_ptr(), hs.data_ptr(),
+        y_row_ptrs.data_ptr(), work.data_ptr(), store.n_experts, max_slots, store.d_model, store.d_ff, dev.index,
+        _s(dev)))
+
+
 def grouped_ffn_rows(store: ExpertStore, offsets: torch.Tensor, xs: torch.Tensor, x_rows: Optional[torch.Tensor],
                      ys: torch.Tensor, y_rows: Optional[torch.Tensor], max_slots: int,
                      work: Optional[torch.Tensor] = None) -> torch.Tensor:
