@@ -187,6 +187,13 @@ int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff)
  * the reference, which runs one matvec per token (sub1.py:139-142). */
 int qmoe_moe_set_tile_min_tokens(int tokens);
 
+/* For measurements: the per-row kernel of qmoe_moe_grouped_ffn normally cuts every matrix into the
+ * number of equal work items that fills whole rounds of the SMs best (decided on the device from
+ * the step's routing).  A value > 0 forces that many items per wi / wo matrix instead (ignored
+ * where it would not fit the work buffer or give items of fewer than 32 rows); 0 restores the
+ * choice.  Process-wide. */
+int qmoe_moe_set_items_per_matrix(int wi, int wo);
+
 /* Host read-back (synchronises `stream`) of what the last qmoe_moe_grouped_ffn call that used
  * work_dev planned, for tests and reports; max_slots / d_ff as in that call.  out_host int32[10]:
  * [0] / [1] row-per-thread work items of wi / wo, [2] / [3] row-per-warp work items of wi / wo,

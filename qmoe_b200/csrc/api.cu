@@ -101,6 +101,7 @@ int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *co
                   uint8_t *sym, int32_t *status, int height, int width, int64_t n_codes, cudaStream_t stream);
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
 int set_tile_min_tokens(int tokens);
+void set_items_per_matrix(int wi, int wo);
 int set_tile_wait_limit(uint32_t spins);
 int work_summary(const void *work, int max_slots, int d_ff, int32_t *out, cudaStream_t stream);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
@@ -485,6 +486,11 @@ int qmoe_moe_unpermute(const void *ys_dev, const int32_t *slot_dev, void *out_de
 }
 
 int qmoe_moe_set_tile_min_tokens(int tokens) { return set_tile_min_tokens(tokens); }
+
+int qmoe_moe_set_items_per_matrix(int wi, int wo) {
+  set_items_per_matrix(wi, wo);
+  return QMOE_OK;
+}
 
 int64_t qmoe_moe_work_bytes(int n_experts, int max_slots, int d_model, int d_ff) {
   (void)n_experts;

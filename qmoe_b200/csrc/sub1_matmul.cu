@@ -892,7 +892,8 @@ struct WorkPhase {
 
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
                                                      int max_slots, int tile_min, int sms,
-                                                     int use_warp, int *header, WorkPhase p0, WorkPhase p1) {
+                                                     int use_warp, int *header, WorkPhase p0, WorkPhase p1,
+                                                     int forced_wi, int forced_wo) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_total;
@@ -951,7 +952,10 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
         }
       }
       __syncthreads();
-      const int best_rows = (int)(s_best & 0xffffull);
+      int best_rows = (int)(s_best & 0xffffull);
+      const int forced = phase == 0 ? forced_wi : forced_wo;  // measurements: a given number of items per matrix
+      if (forced > 0 && forced * 32 <= main_rows && (long long)total * forced <= p.capacity)
+        best_rows = ((main_rows + forced - 1) / forced + 31) / 32 * 32;
       rpc = best_rows;
     }
     const int chunks = (main_rows + rpc - 1) / rpc;
@@ -1063,6 +1067,13 @@ static int tile_min_tokens() {
   }
   return v;
 }
+// Items per matrix forced by qmoe_moe_set_items_per_matrix (0: chosen on the device).
+static std::atomic<int> g_forced_items[2] = {{0}, {0}};
+void set_items_per_matrix(int wi, int wo) {
+  g_forced_items[0].store(wi > 0 ? wi : 0, std::memory_order_relaxed);
+  g_forced_items[1].store(wo > 0 ? wo : 0, std::memory_order_relaxed);
+}
+
 int set_tile_min_tokens(int tokens) {
   const int before = tile_min_tokens();
   g_tile_min.store(clamp_tile_min(tokens), std::memory_order_relaxed);
@@ -1150,7 +1161,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   int tile_min = tab.conforming && codes != nullptr ? tile_min_tokens() : 0;
   if (tile_min > max_slots) tile_min = 0;
   QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, sms, il ? 1 : 0,
-              header, ph[0], ph[1]);
+              header, ph[0], ph[1], g_forced_items[0].load(std::memory_order_relaxed),
+              g_forced_items[1].load(std::memory_order_relaxed));
   QMOE_CUDA(cudaGetLastError());
   if (tile_min > 0) {
     rc = launch_build_tile_work(offsets, n_experts, tile_min, d_model, d_ff, max_slots, header, tile_wi, tile_wo, stream);
