@@ -194,6 +194,14 @@ int qmoe_moe_set_tile_min_tokens(int tokens);
  * choice.  Process-wide. */
 int qmoe_moe_set_items_per_matrix(int wi, int wo);
 
+/* With lane-interleaved streams, qmoe_moe_grouped_ffn runs the per-thread work items of wi and of wo
+ * in ONE persistent launch: an item of wo starts as soon as the items of wi for the same (expert,
+ * token group) have stored their rows (a completion count per pair, waited for at most two seconds;
+ * a wait that runs out is counted in the word qmoe_moe_tile_timeouts reads), so no SM idles
+ * between the two linears.  on = 0 goes back to one launch per linear (measurements); returns the
+ * previous setting.  Process-wide, default 1. */
+int qmoe_moe_set_fused_phases(int on);
+
 /* Host read-back (synchronises `stream`) of what the last qmoe_moe_grouped_ffn call that used
  * work_dev planned, for tests and reports; max_slots / d_ff as in that call.  out_host int32[10]:
  * [0] / [1] row-per-thread work items of wi / wo, [2] / [3] row-per-warp work items of wi / wo,

@@ -83,6 +83,7 @@ SIGNATURES = {
     "qmoe_moe_work_bytes": (_L, [_I, _I, _I, _I]),
     "qmoe_moe_set_tile_min_tokens": (_I, [_I]),
     "qmoe_moe_set_items_per_matrix": (_I, [_I, _I]),
+    "qmoe_moe_set_fused_phases": (_I, [_I]),
     "qmoe_moe_work_summary": (_I, [_P, _I, _I, _P, _I, _P]),
     "qmoe_moe_grouped_ffn": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "qmoe_moe_grouped_ffn_interleaved": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),

@@ -102,6 +102,7 @@ int launch_decode(const SparseTable &tab, const int32_t *dec, const uint16_t *co
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff);
 int set_tile_min_tokens(int tokens);
 void set_items_per_matrix(int wi, int wo);
+int set_fused_phases(int on);
 int set_tile_wait_limit(uint32_t spins);
 int work_summary(const void *work, int max_slots, int d_ff, int32_t *out, cudaStream_t stream);
 int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_t *codes,
@@ -486,6 +487,8 @@ int qmoe_moe_unpermute(const void *ys_dev, const int32_t *slot_dev, void *out_de
 }
 
 int qmoe_moe_set_tile_min_tokens(int tokens) { return set_tile_min_tokens(tokens); }
+
+int qmoe_moe_set_fused_phases(int on) { return set_fused_phases(on); }
 
 int qmoe_moe_set_items_per_matrix(int wi, int wo) {
   set_items_per_matrix(wi, wo);

@@ -189,6 +189,23 @@ struct MatmulArgs {
                                      // and y_rows are not used); the row may lie in another GPU's memory
   const int4 *items;  // grouped mode: {matrix, first row, first token, rows | tokens << 16}
   int *header;        // grouped mode: header[0] = item count, header[1] = fetch counter
+  // Fused launch of both linears of the expert FFN (grouped mode, `fused` != 0): the items of the
+  // second linear follow those of the first in one fetch order; `second` says where they read and
+  // write; items2 / header2 are their list and count; done[pair] counts the finished items of the
+  // first linear per (expert, token group), which an item of the second waits for.
+  struct SecondIO {
+    const __nv_bfloat16 *x;
+    __nv_bfloat16 *y;
+    long long x_stride, y_stride;
+    const int32_t *y_rows;
+    const unsigned long long *y_ptrs;
+    int flags;
+  } second;
+  const int4 *items2;
+  const int *header2;
+  int *done;
+  int *wait_status;
+  int fused;
   int chunks, rpc, tokens;  // uniform mode
   int flags;
 };
@@ -197,22 +214,27 @@ __device__ __forceinline__ float bf16_round(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
 }
 
+// `second`: an item of the second linear of a fused launch (reads and writes through a.second).
 template <int T, class SinkT>
-__device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink, int row, int tok0, int ntok) {
+__device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink, int row, int tok0, int ntok,
+                                          bool second = false) {
+  const unsigned long long *y_ptrs = second ? a.second.y_ptrs : a.y_ptrs;
+  const int32_t *y_rows = second ? a.second.y_rows : a.y_rows;
+  const int flags = second ? a.second.flags : a.flags;
 #pragma unroll
   for (int t = 0; t < T; t++) {
     if (t < ntok) {
       // fp32 accumulate, round to bf16, then add in bf16 (sub1_cuda_kernel.cu:197-200).
       float v = bf16_round(sink.acc[t]);
       __nv_bfloat16 *yp;
-      if (a.y_ptrs != nullptr) {
-        yp = reinterpret_cast<__nv_bfloat16 *>(a.y_ptrs[tok0 + t]) + row;
+      if (y_ptrs != nullptr) {
+        yp = reinterpret_cast<__nv_bfloat16 *>(y_ptrs[tok0 + t]) + row;
       } else {
-        const long long out_row = a.y_rows != nullptr ? a.y_rows[tok0 + t] : tok0 + t;
-        yp = a.y + out_row * a.y_stride + row;
+        const long long out_row = y_rows != nullptr ? y_rows[tok0 + t] : tok0 + t;
+        yp = (second ? a.second.y : a.y) + out_row * (second ? a.second.y_stride : a.y_stride) + row;
       }
-      if (a.flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
-      if (a.flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
+      if (flags & QMOE_FLAG_ACCUMULATE) v = bf16_round(__bfloat162float(*yp) + v);
+      if (flags & QMOE_FLAG_RELU) v = fmaxf(v, 0.f);
       *yp = __float2bfloat16_rn(v);
     }
   }
@@ -220,19 +242,24 @@ __device__ __forceinline__ void store_row(const MatmulArgs &a, const SinkT &sink
 
 template <int T, class SinkT>
 __device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wlim, int tok0, int ntok,
-                                             typename SinkT::elem *xs) {
+                                             typename SinkT::elem *xs, bool second = false) {
   // xs[c][t] = x[row of token tok0 + t][c], zero beyond the width / token count.
   const __nv_bfloat16 *xp[T];
 #pragma unroll
   for (int t = 0; t < T; t++) {
     const int tok = tok0 + (t < ntok ? t : 0);
-    xp[t] = a.x + (a.x_rows != nullptr ? (long long)a.x_rows[tok] : (long long)tok) * a.x_stride;
+    if (second) xp[t] = a.second.x + (long long)tok * a.second.x_stride;  // indexed by slot
+    else xp[t] = a.x + (a.x_rows != nullptr ? (long long)a.x_rows[tok] : (long long)tok) * a.x_stride;
   }
   for (int c = threadIdx.x; c < wlim + kPad; c += blockDim.x) {
 #pragma unroll
     for (int t = 0; t < T; t++) {
       __nv_bfloat16 v = __float2bfloat16_rn(0.f);
-      if (c < W && t < ntok) v = xp[t][c];
+      if (c < W && t < ntok) {
+        // rows written by other CTAs of the same launch are read from L2, never from this SM's L1
+        if (second) v = __ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short *>(xp[t] + c)));
+        else v = xp[t][c];
+      }
       xs[c * T + t] = SinkT::stage(v);
     }
   }
@@ -241,19 +268,19 @@ __device__ __forceinline__ void stage_tokens(const MatmulArgs &a, int W, int wli
 template <int T, bool GENERAL, class SinkT, int G = 2, class Lookup>
 __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                                  int nrows, int tok0, int ntok, typename SinkT::elem *xs,
-                                                 const Lookup &lookup);
+                                                 const Lookup &lookup, bool second = false);
 
 // Rows [row0, row0 + nrows) one per thread; with an interleaved store, `tail_rows` further rows
 // (what a height like 2080 leaves after blocks of 1024) one per warp, against the same staged x.
 template <int T, bool GENERAL, class SinkT, bool IL = false, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                              int nrows, int tok0, int ntok, typename SinkT::elem *xs,
-                                             const Lookup &lookup, int tail_rows = 0) {
+                                             const Lookup &lookup, int tail_rows = 0, bool second = false) {
   const int tid = threadIdx.x;
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
 
-  stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs);
+  stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs, second);
   __syncthreads();
 
   if (tid < nrows) {
@@ -279,10 +306,11 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
       walk_row<GENERAL>(StreamFetch{codes_m - mis}, (int)b + mis, (int)e + mis, lookup, a.dec, wlim, sink);
     }
 
-    store_row<T>(a, sink, row, tok0, ntok);
+    store_row<T>(a, sink, row, tok0, ntok, second);
   }
   if constexpr (IL) {
-    if (tail_rows > 0) warp_rows_staged<T, GENERAL, SinkT>(a, d, row0 + nrows, tail_rows, tok0, ntok, xs, lookup);
+    if (tail_rows > 0)
+      warp_rows_staged<T, GENERAL, SinkT>(a, d, row0 + nrows, tail_rows, tok0, ntok, xs, lookup, second);
   }
 }
 
@@ -454,7 +482,7 @@ __device__ __forceinline__ void warp_rows(const MatmulArgs &a, int row0, int nro
 template <int T, bool GENERAL, class SinkT, int G, class Lookup>
 __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                                  int nrows, int tok0, int ntok, typename SinkT::elem *xs,
-                                                 const Lookup &lookup) {
+                                                 const Lookup &lookup, bool second) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int wlim = (d.width + 1) & ~1;
   const int32_t *ro = a.row_off + d.rowoff_base;
@@ -474,7 +502,7 @@ __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe
     const auto code_at = [&](int i) { return (uint32_t)__ldg(src + (i >> 3) * 256 + (i & 7)); };
     if constexpr (G == 2) warp_row_sum<GENERAL>(code_at, n, lookup, a.il_dec, (uint32_t)wlim, sink, lane);
     else warp_row_sum_groups<GENERAL, G>(code_at, n, lookup, a.il_dec, (uint32_t)wlim, sink, lane);
-    if (lane == 0) store_row<T>(a, sink, row, tok0, ntok);
+    if (lane == 0) store_row<T>(a, sink, row, tok0, ntok, second);
   }
 }
 
@@ -499,6 +527,8 @@ __global__ void __launch_bounds__(kWarpRowThreads) k_matmul_warp_rows(const Matm
   else warp_rows<4, GENERAL>(a, row0, nrows, tok0, ntok, xs_f32);
 }
 
+constexpr unsigned long long kFusedWaitNs = 2000000000ull;  // an item of the second linear waits this long at most
+
 // Persistent CTAs (one per SM) pulling items of a device-built work list.  Shared memory holds the
 // hot part of the sparse table (loaded once per CTA) followed by the bf16 activations of the
 // current item.
@@ -509,8 +539,11 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
   uint32_t *hot = smem_u32;
   const uint32_t n_hot = IL ? (uint32_t)a.n_hot : kHotSlots;
   void *xs = smem_u32 + n_hot;
-  const int n_items = a.header[0];
+  const int n_first = a.header[0];
+  const int n_items = n_first + (a.fused ? a.header2[0] : 0);
   if (n_items <= 0) return;
+  // items per (expert, token group) of either linear, written by k_build_work behind the counts
+  const int per_pair_first = a.fused ? a.header[14] : 0, per_pair_second = a.fused ? a.header[15] : 1;
   using Lookup = typename std::conditional<IL, HotLookupLow, HotLookup>::type;
   Lookup lookup;
   if constexpr (IL) {
@@ -528,22 +561,52 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     __syncthreads();  // also orders the table fill before the first lookups
     const int i = s_item;
     if (i >= n_items) break;
-    const int4 it = a.items[i];
+    const bool second = i >= n_first;
+    const int j = second ? i - n_first : i;
+    const int4 it = second ? a.items2[j] : a.items[j];
     const qmoe_matrix_desc d = a.descs[it.x];
     const int nrows = it.w & 0x7fff, ntok = it.w >> 16;
     const int tail = (it.w & 0x8000) ? d.height - (it.y + nrows) : 0;
+    if (second && per_pair_first > 0) {
+      // The hidden activations of this (expert, token group) come from the items of the first linear,
+      // all of which were fetched before this one (one fetch order) by CTAs that are running: wait
+      // until they have stored their rows.  The wait is bounded in time all the same; when it runs out
+      // the status word is raised and the item goes ahead on whatever is there.
+      if (threadIdx.x == 0) {
+        const int *flag = a.done + j / per_pair_second;
+        unsigned long long t0 = 0;
+        for (unsigned spins = 0;; spins++) {
+          int v;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (v >= per_pair_first) break;
+          unsigned long long t;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+          if (spins == 0) t0 = t;
+          if (t - t0 > kFusedWaitNs) {
+            atomicAdd(a.wait_status, 1);
+            break;
+          }
+          __nanosleep(100);
+        }
+      }
+      __syncthreads();
+    }
     // one token: fp32 activations (no conversion per gather); two and four: bf16, so that a gather
     // is one 4- or 8-byte shared load (two 4-byte words per lane cost twice the bank cycles)
     if (ntok <= 1)
       process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup,
-                                                     tail);
+                                                     tail, second);
     else if (ntok == 2)
       process_item<2, GENERAL, MatSink<2, false>, IL>(a, d, it.y, nrows, it.z, ntok,
-                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail);
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second);
     else
       process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
-                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail);
-    __syncthreads();  // xs and s_item are rewritten by the next round
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second);
+    __syncthreads();  // xs and s_item are rewritten by the next round; every row of the item is stored
+    if (a.fused && !second && threadIdx.x == 0) {
+      __threadfence();  // the rows stored by the whole CTA (ordered by the barrier) before the count
+      atomicAdd(a.done + j / per_pair_first, 1);
+    }
   }
 }
 
@@ -893,7 +956,7 @@ struct WorkPhase {
 __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__ offsets, int n_experts,
                                                      int max_slots, int tile_min, int sms,
                                                      int use_warp, int *header, WorkPhase p0, WorkPhase p1,
-                                                     int forced_wi, int forced_wo) {
+                                                     int forced_wi, int forced_wo, int *done) {
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_total;
@@ -922,6 +985,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
   }
   __syncthreads();
   const int total = min(s_total, max_slots);
+  for (int g = tid; g < total; g += blockDim.x) done[g] = 0;  // finished first-linear items per pair
 
   for (int phase = 0; phase < 2; phase++) {
     const WorkPhase p = phase == 0 ? p0 : p1;
@@ -1035,6 +1099,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       header[11 + 2 * phase] = 0;
       header[6 + phase] = rpc;  // rows per item of this phase (reports)
       header[9] = kMaxGroup;
+      header[14 + phase] = chunks;  // per-thread items per (expert, token group) of this phase
     }
     __syncthreads();
   }
@@ -1067,6 +1132,10 @@ static int tile_min_tokens() {
   }
   return v;
 }
+// Both linears' per-thread items in one launch (qmoe_moe_set_fused_phases; default on).
+static std::atomic<int> g_fused_phases{1};
+int set_fused_phases(int on) { return g_fused_phases.exchange(on != 0 ? 1 : 0, std::memory_order_relaxed); }
+
 // Items per matrix forced by qmoe_moe_set_items_per_matrix (0: chosen on the device).
 static std::atomic<int> g_forced_items[2] = {{0}, {0}};
 void set_items_per_matrix(int wi, int wo) {
@@ -1092,7 +1161,7 @@ static int64_t warp_item_capacity(int max_slots) {
 int64_t moe_work_bytes(int max_slots, int d_model, int d_ff) {
   return 64 + (item_capacity(max_slots, d_ff) + item_capacity(max_slots, d_model) +
                2 * warp_item_capacity(max_slots)) * (int64_t)sizeof(int4) +
-         tile_work_bytes(max_slots, d_model, d_ff);
+         tile_work_bytes(max_slots, d_model, d_ff) + ((int64_t)max_slots * 4 + 15) / 16 * 16;
 }
 
 // What the last qmoe_moe_grouped_ffn call with this work buffer planned (a host read-back for tests
@@ -1152,6 +1221,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   ph[0].warp_items = tile_wo + (size_t)tile_cap_blocks(max_slots) * ((d_model + 127) / 128);
   ph[0].warp_capacity = ph[1].warp_capacity = (int)warp_item_capacity(max_slots);
   ph[1].warp_items = ph[0].warp_items + ph[0].warp_capacity;
+  int *done = reinterpret_cast<int *>(ph[1].warp_items + ph[1].warp_capacity);  // int[max_slots]
   const bool il = ils != nullptr;
   // The tile path decodes the row-by-row streams; a store that kept only its interleaved copy
   // (codes == nullptr) sends every expert through the per-row kernel.
@@ -1162,7 +1232,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   if (tile_min > max_slots) tile_min = 0;
   QMOE_LAUNCH(k_build_work, 1, 1024, 0, stream, offsets, n_experts, max_slots, tile_min, sms, il ? 1 : 0,
               header, ph[0], ph[1], g_forced_items[0].load(std::memory_order_relaxed),
-              g_forced_items[1].load(std::memory_order_relaxed));
+              g_forced_items[1].load(std::memory_order_relaxed), done);
   QMOE_CUDA(cudaGetLastError());
   if (tile_min > 0) {
     rc = launch_build_tile_work(offsets, n_experts, tile_min, d_model, d_ff, max_slots, header, tile_wi, tile_wo, stream);
@@ -1185,61 +1255,115 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   cudaEvent_t *events = nullptr;
   const bool timed = profile_begin(device, &events);
 
+  // what either linear reads, writes and works through
+  MatmulArgs pa[2];
+  size_t smem_of[2];
   for (int phase = 0; phase < 2; phase++) {
     const int width = phase == 0 ? d_model : d_ff;
-    a.x = reinterpret_cast<const __nv_bfloat16 *>(phase == 0 ? xs : hs);
-    a.y = reinterpret_cast<__nv_bfloat16 *>(phase == 0 ? hs : ys);
-    a.x_stride = phase == 0 ? xs_stride : width;
-    a.y_stride = phase == 0 ? d_ff : ys_stride;
-    a.x_rows = phase == 0 ? x_rows : nullptr;   // the hidden activation in between is indexed by slot
-    a.y_rows = phase == 0 ? nullptr : y_rows;
-    a.y_ptrs = phase == 0 ? nullptr : y_ptrs;
-    a.items = ph[phase].items;
-    a.header = header + 2 * phase;
-    a.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
-    a.n_hot = hot_entries_for(width);
-    const size_t smem = il ? sizeof(uint32_t) * a.n_hot + grouped_x_bytes(width, kMaxGroup)
-                           : grouped_smem_bytes(width, kMaxGroup);
-    if (tile_min > 0) {
-      const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
-      rc = launch_tile_phase(tab.entries, codes, row_off, minmax, descs, a.x, a.y, a.x_stride, a.y_stride,
-                             a.x_rows, a.y_rows, a.y_ptrs, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, a.flags,
+    MatmulArgs &p = pa[phase];
+    p = a;
+    p.x = reinterpret_cast<const __nv_bfloat16 *>(phase == 0 ? xs : hs);
+    p.y = reinterpret_cast<__nv_bfloat16 *>(phase == 0 ? hs : ys);
+    p.x_stride = phase == 0 ? xs_stride : width;
+    p.y_stride = phase == 0 ? d_ff : ys_stride;
+    p.x_rows = phase == 0 ? x_rows : nullptr;   // the hidden activation in between is indexed by slot
+    p.y_rows = phase == 0 ? nullptr : y_rows;
+    p.y_ptrs = phase == 0 ? nullptr : y_ptrs;
+    p.items = ph[phase].items;
+    p.header = header + 2 * phase;
+    p.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
+    p.n_hot = hot_entries_for(width);
+    smem_of[phase] = il ? sizeof(uint32_t) * p.n_hot + grouped_x_bytes(width, kMaxGroup)
+                        : grouped_smem_bytes(width, kMaxGroup);
+  }
+  const unsigned grid = (unsigned)sms;  // the table in shared memory allows one CTA per SM
+  auto launch_tiles = [&](int phase) -> int {
+    if (tile_min <= 0) return QMOE_OK;
+    const MatmulArgs &p = pa[phase];
+    const int rows_blocks = ((phase == 0 ? d_ff : d_model) + 127) / 128;
+    return launch_tile_phase(tab.entries, codes, row_off, minmax, descs, p.x, p.y, p.x_stride, p.y_stride, p.x_rows,
+                             p.y_rows, p.y_ptrs, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, p.flags,
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
-      if (rc) return rc;
-    }
-    const unsigned grid = (unsigned)sms;  // the table in shared memory allows one CTA per SM
-    if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
-    const int height = phase == 0 ? d_ff : d_model;
-    if (il && (long long)max_slots * height <= kSmallRows) {
-      // every step this small goes to the warp kernel
-    } else if (tab.conforming && il)
-      QMOE_LAUNCH((k_matmul_grouped<false, true>), grid, kGroupedThreads, smem, stream, a);
+  };
+  auto launch_threads = [&](const MatmulArgs &p, size_t smem) -> int {
+    if (tab.conforming && il)
+      QMOE_LAUNCH((k_matmul_grouped<false, true>), grid, kGroupedThreads, smem, stream, p);
     else if (tab.conforming)
-      QMOE_LAUNCH((k_matmul_grouped<false, false>), grid, kGroupedThreads, smem, stream, a);
+      QMOE_LAUNCH((k_matmul_grouped<false, false>), grid, kGroupedThreads, smem, stream, p);
     else if (il)
-      QMOE_LAUNCH((k_matmul_grouped<true, true>), grid, kGroupedThreads, smem, stream, a);
+      QMOE_LAUNCH((k_matmul_grouped<true, true>), grid, kGroupedThreads, smem, stream, p);
     else
-      QMOE_LAUNCH((k_matmul_grouped<true, false>), grid, kGroupedThreads, smem, stream, a);
+      QMOE_LAUNCH((k_matmul_grouped<true, false>), grid, kGroupedThreads, smem, stream, p);
     QMOE_CUDA(cudaGetLastError());
-    if (il) {
-      MatmulArgs w = a;
-      w.items = ph[phase].warp_items;
-      w.header = header + 10 + 2 * phase;
-      const size_t wsmem = grouped_x_bytes(width, kMaxGroup);
-      int per_sm = (int)(kSmemPerCta / (wsmem + 1024));  // CTAs of 256 threads that fit one SM
-      per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
-      const unsigned wgrid = (unsigned)(per_sm * sms);
-      const bool long_rows = width > 3072;
-      if (tab.conforming && long_rows)
-        QMOE_LAUNCH((k_matmul_grouped_warp<false, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
-      else if (tab.conforming)
-        QMOE_LAUNCH((k_matmul_grouped_warp<false, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
-      else if (long_rows)
-        QMOE_LAUNCH((k_matmul_grouped_warp<true, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
-      else
-        QMOE_LAUNCH((k_matmul_grouped_warp<true, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
-      QMOE_CUDA(cudaGetLastError());
+    return QMOE_OK;
+  };
+  auto launch_warps = [&](int phase) -> int {
+    if (!il) return QMOE_OK;
+    const int width = phase == 0 ? d_model : d_ff;
+    MatmulArgs w = pa[phase];
+    w.items = ph[phase].warp_items;
+    w.header = header + 10 + 2 * phase;
+    const size_t wsmem = grouped_x_bytes(width, kMaxGroup);
+    int per_sm = (int)(kSmemPerCta / (wsmem + 1024));  // CTAs of 256 threads that fit one SM
+    per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
+    const unsigned wgrid = (unsigned)(per_sm * sms);
+    const bool long_rows = width > 3072;
+    if (tab.conforming && long_rows)
+      QMOE_LAUNCH((k_matmul_grouped_warp<false, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
+    else if (tab.conforming)
+      QMOE_LAUNCH((k_matmul_grouped_warp<false, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
+    else if (long_rows)
+      QMOE_LAUNCH((k_matmul_grouped_warp<true, 9>), wgrid, kWarpRowThreads, wsmem, stream, w);
+    else
+      QMOE_LAUNCH((k_matmul_grouped_warp<true, 4>), wgrid, kWarpRowThreads, wsmem, stream, w);
+    QMOE_CUDA(cudaGetLastError());
+    return QMOE_OK;
+  };
+  // every step this small goes to the warp kernel whatever the routing
+  auto all_small = [&](int phase) { return il && (long long)max_slots * (phase == 0 ? d_ff : d_model) <= kSmallRows; };
+
+  if (il && g_fused_phases.load(std::memory_order_relaxed) != 0) {
+    // One launch for the per-thread items of both linears: the CTAs go from the last items of wi
+    // straight to the first of wo instead of idling until the slowest has finished (with a few
+    // hundred items on 148 SMs, as on one rank of eight, that idle part is a fifth of the time).
+    // Tile and warp items keep their own launches: wi's before, wo's after.
+    if ((rc = launch_tiles(0)) != QMOE_OK || (rc = launch_tiles(1)) != QMOE_OK) return rc;
+    if (timed) QMOE_CUDA(cudaEventRecord(events[0], stream));
+    if ((rc = launch_warps(0)) != QMOE_OK) return rc;
+    if (!(all_small(0) && all_small(1))) {
+      const int wide = d_model > d_ff ? d_model : d_ff;
+      MatmulArgs f = pa[0];
+      f.second.x = pa[1].x;
+      f.second.y = pa[1].y;
+      f.second.x_stride = pa[1].x_stride;
+      f.second.y_stride = pa[1].y_stride;
+      f.second.y_rows = pa[1].y_rows;
+      f.second.y_ptrs = pa[1].y_ptrs;
+      f.second.flags = pa[1].flags;
+      f.items2 = pa[1].items;
+      f.header2 = pa[1].header;
+      f.done = done;
+      f.wait_status = tile_status_word(device);
+      if (f.wait_status == nullptr) return cuda_fail(cudaGetLastError(), "status word");
+      f.fused = 1;
+      f.n_hot = hot_entries_for(wide);
+      if ((rc = launch_threads(f, sizeof(uint32_t) * f.n_hot + grouped_x_bytes(wide, kMaxGroup))) != QMOE_OK) return rc;
     }
+    if ((rc = launch_warps(1)) != QMOE_OK) return rc;
+    if (timed) {
+      // one duration for both linears: reported as the first, the second reads as zero
+      QMOE_CUDA(cudaEventRecord(events[1], stream));
+      QMOE_CUDA(cudaEventRecord(events[2], stream));
+      QMOE_CUDA(cudaEventRecord(events[3], stream));
+    }
+    return QMOE_OK;
+  }
+
+  for (int phase = 0; phase < 2; phase++) {
+    if ((rc = launch_tiles(phase)) != QMOE_OK) return rc;
+    if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
+    if (!all_small(phase) && (rc = launch_threads(pa[phase], smem_of[phase])) != QMOE_OK) return rc;
+    if ((rc = launch_warps(phase)) != QMOE_OK) return rc;
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }
   return QMOE_OK;
