@@ -198,8 +198,10 @@ int qmoe_moe_set_items_per_matrix(int wi, int wo);
  * in ONE persistent launch: an item of wo starts as soon as the items of wi for the same (expert,
  * token group) have stored their rows (a completion count per pair, waited for at most two seconds;
  * a wait that runs out is counted in the word qmoe_moe_tile_timeouts reads), so no SM idles
- * between the two linears.  on = 0 goes back to one launch per linear (measurements); returns the
- * previous setting.  Process-wide, default 1. */
+ * between the two linears.  Taken for steps of at most eight token slots per SM (max_slots <= 8 *
+ * SMs), where a step has only a handful of items per SM; larger steps keep one launch per linear,
+ * whose hot dictionary part is sized for each width.  on = 0 always uses one launch per linear
+ * (measurements); returns the previous setting.  Process-wide, default 1. */
 int qmoe_moe_set_fused_phases(int on);
 
 /* Host read-back (synchronises `stream`) of what the last qmoe_moe_grouped_ffn call that used

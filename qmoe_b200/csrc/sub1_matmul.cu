@@ -938,7 +938,11 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 // 32 rows.  In between, the items are made finer than 1024 rows
 // until there are about two per SM.  Without an interleaved store there is no warp kernel.
 constexpr int kExtraItems = 8192;
-constexpr int kItemOverheadRows = 64;       // fixed cost of a work item, in rows of work (staging the activations)
+// Fixed cost of a work item in rows of work.  A thread walks its row at the latency of the dependent
+// lookups and gathers, so an item of 128 rows takes more than half the time of one of 1024 (measured
+// on 160 pairs of c-2048: 43 us against 74 us for wo, 18 us against 31 us for wi): finer items only
+// pay when they save a whole round of the SMs.
+constexpr int kItemOverheadRows = 1024;
 constexpr int kWarpItemRows = 8;             // one row per warp of a k_matmul_grouped_warp CTA
 constexpr int kWarpRemainderMax = 256;      // most rows of a matrix that are left to the warp kernel
 constexpr int kSmallRows = 148 * 8 * 32;    // fewer rows in total (less than eight warps of rows per SM):
@@ -1029,10 +1033,17 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
     const int tail_flag = main_rows > 0 && main_rows < H ? 0x8000 : 0;
     if (tid == 0) s_base = 0;
     __syncthreads();
+    // Longest items first: the groups of four tokens of all experts, then those of three, two and
+    // one (an item's time grows with its tokens, and with a handful of items per SM the order in
+    // which the CTAs fetch them decides how uneven the last round is).
+    for (int cls = kMaxGroup; cls >= 1; cls--)
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
       const int e = e0 + tid;
       int first, count;
-      const int groups = group_count(e, first, count);
+      group_count(e, first, count);
+      const int full = count / kMaxGroup, rem = count % kMaxGroup;
+      const int groups = cls == kMaxGroup ? full : (rem == cls ? 1 : 0);
+      const int first_tok = cls == kMaxGroup ? first : first + full * kMaxGroup;
       // exclusive scan of `groups` over the block
       int incl = groups;
 #pragma unroll
@@ -1057,8 +1068,8 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       for (int g = 0; g < groups && chunks > 0; g++) {
         const int gi = base + g;
         if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
-        const int tok0 = first + g * kMaxGroup;
-        const int ntok = min(kMaxGroup, count - g * kMaxGroup);
+        const int tok0 = first_tok + g * kMaxGroup;
+        const int ntok = cls;
         for (int k = 0; k < chunks; k++) {
           const int row0 = k * rpc;
           p.items[(size_t)gi * chunks + k] =
@@ -1072,14 +1083,14 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       while (busy) {
         const int src = __ffs(busy) - 1;
         busy &= busy - 1;
-        const int o_e = __shfl_sync(0xffffffffu, e, src), o_first = __shfl_sync(0xffffffffu, first, src);
-        const int o_count = __shfl_sync(0xffffffffu, count, src), o_groups = __shfl_sync(0xffffffffu, groups, src);
+        const int o_e = __shfl_sync(0xffffffffu, e, src), o_first = __shfl_sync(0xffffffffu, first_tok, src);
+        const int o_groups = __shfl_sync(0xffffffffu, groups, src);
         const int o_base = __shfl_sync(0xffffffffu, base, src);
         for (int g = 0; g < o_groups; g++) {
           const int gi = o_base + g;
           if (gi >= max_slots || (long long)(gi + 1) * wchunks > p.warp_capacity) break;
           const int tok0 = o_first + g * kMaxGroup;
-          const int ntok = min(kMaxGroup, o_count - g * kMaxGroup);
+          const int ntok = cls;
           for (int k = lane; k < wchunks; k += 32) {
             const int row0 = k * kWarpItemRows;
             p.warp_items[(size_t)gi * wchunks + k] =
@@ -1322,7 +1333,11 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   // every step this small goes to the warp kernel whatever the routing
   auto all_small = [&](int phase) { return il && (long long)max_slots * (phase == 0 ? d_ff : d_model) <= kSmallRows; };
 
-  if (il && g_fused_phases.load(std::memory_order_relaxed) != 0) {
+  // The fused launch keeps the smaller of the two hot tables for both linears, which costs wi about
+  // 1 % on a full layer (3.04 against 3.01 ms for 2048 tokens on 2048 experts) and saves 3 % when a
+  // step has only a few items per SM (one rank of eight: 456 against 469 us): taken for steps of at
+  // most eight token slots per SM.
+  if (il && g_fused_phases.load(std::memory_order_relaxed) != 0 && max_slots <= 8 * sms) {
     // One launch for the per-thread items of both linears: the CTAs go from the last items of wi
     // straight to the first of wo instead of idling until the slowest has finished (with a few
     // hundred items on 148 SMs, as on one rank of eight, that idle part is a fifth of the time).

@@ -87,6 +87,16 @@ def test_switch_c_2048_slice_grouped_path_against_the_oracle():
     assert plan["wi_warp_items"] == 0 and plan["wo_warp_items"] == 0
     assert plan["wo_items_with_remainder"] == groups, "rows 2048..2079 of wo are not covered"
 
+    # this step is small enough for the single launch that runs the items of wi and wo together; the
+    # benchmark's full layer takes one launch per linear: same bits
+    was = L.qmoe_moe_set_fused_phases(0)
+    try:
+        ys_two = sub1.grouped_ffn(store, offsets, xs, N_TOKENS)
+        torch.cuda.synchronize()
+    finally:
+        L.qmoe_moe_set_fused_phases(was)
+    assert was == 1 and torch.equal(ys, ys_two), "one launch for both linears differs from one launch per linear"
+
     # the same step on a store without the interleaved copy (row-by-row streams, one thread per row)
     plain = sub1.ExpertStore(store.codes, store.row_off, store.minmax, store.host_descs, d_model, d_ff,
                              interleave=False)
