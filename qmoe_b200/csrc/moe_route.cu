@@ -298,6 +298,16 @@ __global__ void k_combine(const __nv_bfloat16 *__restrict__ ys, const __nv_bfloa
   const float p = __bfloat162float(prob[t]);
   const __nv_bfloat16 *src = s >= 0 ? ys + (size_t)s * d_model : hidden + (size_t)t * d_model;
   __nv_bfloat16 *dst = out + (size_t)t * d_model;
+  if ((d_model & 7) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+    for (int i = threadIdx.x; i < d_model / 8; i += blockDim.x) {
+      uint4 v = reinterpret_cast<const uint4 *>(src)[i];
+      __nv_bfloat16 *h = reinterpret_cast<__nv_bfloat16 *>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; k++) h[k] = __float2bfloat16_rn(p * __bfloat162float(h[k]));
+      reinterpret_cast<uint4 *>(dst)[i] = v;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < d_model; i += blockDim.x)
     dst[i] = __float2bfloat16_rn(p * __bfloat162float(src[i]));
 }
@@ -322,7 +332,10 @@ __global__ void k_combine_add(const __nv_bfloat16 *__restrict__ ys, const __nv_b
 int launch_route(const float *logits, int32_t *choice, void *prob, int n_tokens, int n_experts,
                  cudaStream_t stream) {
   if (n_tokens == 0) return QMOE_OK;
-  if (n_tokens <= 16 && n_experts >= 512) {
+  // A CTA per token for wide routers (a warp walking 2048 logits three times is latency: 9.7 us
+  // for 256 tokens); the choice of kernel depends on the router's width only, so that a token gets
+  // the same probability bits whatever batch it arrives in.
+  if (n_experts >= 512) {
     QMOE_LAUNCH(k_route_choose_block, (unsigned)n_tokens, 256, 0, stream, logits, choice,
                 reinterpret_cast<__nv_bfloat16 *>(prob), n_experts);
     QMOE_CUDA(cudaGetLastError());
