@@ -295,7 +295,7 @@ int qmoe_moe_grouped_ffn_rows(const int32_t *dec_dev, const uint16_t *codes_dev,
  * the trailer above) or, with rows_dev NULL, bucket_dev[i]; values outside [0, n_buckets) mean
  * "no row".  offsets_dev int32[n_buckets + 1]: exclusive prefix sums of the bucket sizes;
  * slot_of_row_dev[i] = offsets[bucket] + rank (or -1); row_of_slot_dev[slot] = i (entries at and
- * beyond offsets[n_buckets] are left untouched).  At most 8192 buckets. */
+ * beyond offsets[n_buckets] are left untouched).  At most 4096 buckets. */
 int qmoe_moe_ep_dispatch(const int32_t *choice_dev, const void *hidden_dev, int64_t hidden_stride,
                          int32_t *expert_dev, int32_t *dest_dev, int32_t *slot_dev, void *send_dev,
                          int32_t *overflow_dev, int n_tokens, int n_experts, int n_ranks, int seq_len,

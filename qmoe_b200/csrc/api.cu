@@ -663,8 +663,8 @@ static int plan_entry(const char *fn, const void *rows_dev, int64_t row_stride, 
     set_error("%s: bad shape", fn);
     return QMOE_ERR_INVALID_ARG;
   }
-  if (n_buckets > 8192) {
-    set_error("%s: at most 8192 buckets (their running sizes are kept in shared memory)", fn);
+  if (n_buckets > 4096) {
+    set_error("%s: at most 4096 buckets (their sizes and first slots are kept in shared memory)", fn);
     return QMOE_ERR_UNSUPPORTED;
   }
   if (!(offsets_dev && (n_rows == 0 || ((rows_dev || bucket_dev) && slot_of_row_dev && row_of_slot_dev)))) {

@@ -30,32 +30,37 @@ __device__ __forceinline__ int block_sum(int v, int *s_warp) {
   return total;
 }
 
-// Thread t < n_tokens: the router's capacity rule (kept iff fewer than `capacity` earlier tokens of the
-// same sequence chose the same expert: cumsum(one_hot) <= expert_capacity).  expert[t] = choice or -1,
-// dest[t] = the rank that owns the expert or -1.  Thread i < n_slots: the trailer of exchange slot i is
-// reset to "empty" (-1).
+// Warp t < n_tokens: the router's capacity rule (kept iff fewer than `capacity` earlier tokens of the
+// same sequence chose the same expert: cumsum(one_hot) <= expert_capacity; the lanes share out the
+// earlier tokens).  expert[t] = choice or -1, dest[t] = the rank that owns the expert or -1.
+// Thread i < n_slots: the trailer of exchange slot i is reset to "empty" (-1).
 __global__ void k_ep_keep(const int32_t *__restrict__ choice, int32_t *__restrict__ expert,
                           int32_t *__restrict__ dest, int n_tokens, int n_experts, int local_experts,
                           int seq_len, int capacity, __nv_bfloat16 *__restrict__ send,
                           __nv_bfloat16 *const *__restrict__ blocks, int cap, int n_slots,
                           long long row_stride, int d_model) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n_slots) {
     __nv_bfloat16 *row = blocks != nullptr ? blocks[i / cap] + (long long)(i % cap) * row_stride
                                            : send + (long long)i * row_stride;
     *reinterpret_cast<int32_t *>(row + d_model) = -1;
   }
-  if (i >= n_tokens) return;
-  const int c = choice[i];
+  const int t = (int)(i >> 5), lane = threadIdx.x & 31;
+  if (t >= n_tokens) return;
+  const int c = choice[t];
   int keep = c >= 0 && c < n_experts;
   if (keep && capacity < seq_len) {
-    const int s0 = (i / seq_len) * seq_len;
+    const int s0 = (t / seq_len) * seq_len;
     int before = 0;
-    for (int u = s0; u < i; u++) before += (choice[u] == c);
+    for (int u = s0 + lane; u < t; u += 32) before += (choice[u] == c);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
     keep = before < capacity;
   }
-  expert[i] = keep ? c : -1;
-  dest[i] = keep ? c / local_experts : -1;
+  if (lane == 0) {
+    expert[t] = keep ? c : -1;
+    dest[t] = keep ? c / local_experts : -1;
+  }
 }
 
 // One CTA per token: rank of the token among the earlier kept tokens with the same destination
@@ -103,44 +108,33 @@ __global__ void __launch_bounds__(128) k_ep_pack(const int32_t *__restrict__ exp
 // One CTA.  The bucket of row i (-1 = no row) is read from the trailers of received rows (rows !=
 // nullptr) or from an int32 array.  Produces offsets[n_buckets + 1] (exclusive prefix sums of the
 // bucket sizes), slot_of_row[i] = offsets[bucket] + stable rank (or -1) and row_of_slot[slot] = i.
-// Stable ranks without comparing every pair of rows: rows are taken 1024 at a time in row order;
-// inside a warp __match_any_sync groups the lanes of one bucket, and the 32 warps add their groups to
-// the running bucket counts (dynamic shared memory, n_buckets ints) one after the other.
+// Every pass is parallel over the rows: (1) bucket sizes by shared-memory atomics, each row keeping
+// the position it arrived at; (2) offsets by a block scan; (3) the members of every bucket written
+// to the bucket's slots in arrival order; (4) the stable rank of a row = the members of its bucket
+// with a smaller row index (buckets hold a handful of rows under a balanced router; a bucket of m
+// rows costs m * m compares); (5) the final lists.
 __global__ void __launch_bounds__(1024) k_ep_plan(const __nv_bfloat16 *__restrict__ rows, long long row_stride,
                                                   int d_model, const int32_t *__restrict__ meta_in, int n_rows,
                                                   int n_buckets, int32_t *__restrict__ offsets,
                                                   int32_t *__restrict__ slot_of_row, int32_t *__restrict__ row_of_slot,
                                                   const unsigned long long *__restrict__ out_blocks, int rows_per_block,
                                                   long long out_row_bytes, unsigned long long *__restrict__ out_ptr_of_slot) {
-  extern __shared__ int s_count[];  // running size of every bucket
+  extern __shared__ int s_count[];  // size of every bucket, later its first slot; then the sizes again
   __shared__ int s_warp[32];
   __shared__ int s_carry;
+  int *s_size = s_count + n_buckets;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  auto bucket_of = [&](int i) {
+    const int b = rows != nullptr ? *reinterpret_cast<const int32_t *>(rows + (long long)i * row_stride + d_model)
+                                  : meta_in[i];
+    return (b >= 0 && b < n_buckets) ? b : -1;
+  };
   for (int b = tid; b < n_buckets; b += blockDim.x) s_count[b] = 0;
   __syncthreads();
-  for (int i0 = 0; i0 < n_rows; i0 += blockDim.x) {
-    const int i = i0 + tid;
-    int b = -1;
-    if (i < n_rows) {
-      b = rows != nullptr ? *reinterpret_cast<const int32_t *>(rows + (long long)i * row_stride + d_model) : meta_in[i];
-      b = (b >= 0 && b < n_buckets) ? b : -1;
-    }
-    // lanes without a row get distinct negative keys so that they group with nobody
-    const unsigned same = __match_any_sync(0xffffffffu, b >= 0 ? b : -1 - lane);
-    const int before_in_warp = __popc(same & ((1u << lane) - 1u));
-    const bool leader = before_in_warp == 0;
-    int rank = -1;
-    for (int w = 0; w < 32; w++) {
-      if (warp == w && b >= 0) {
-        rank = s_count[b] + before_in_warp;
-        __syncwarp(same);
-        if (leader) s_count[b] += __popc(same);
-      }
-      __syncthreads();
-    }
-    if (i < n_rows) slot_of_row[i] = rank;  // the offset of the bucket is added below
+  for (int i = tid; i < n_rows; i += blockDim.x) {
+    const int b = bucket_of(i);
+    slot_of_row[i] = b >= 0 ? atomicAdd(&s_count[b], 1) : -1;  // arrival position, replaced in pass 4
   }
-  // offsets = exclusive scan of the bucket sizes
   if (tid == 0) {
     s_carry = 0;
     offsets[0] = 0;
@@ -171,17 +165,29 @@ __global__ void __launch_bounds__(1024) k_ep_plan(const __nv_bfloat16 *__restric
     if (b < n_buckets) {
       offsets[1 + b] = incl_all;
       s_count[b] = incl_all - v;  // now the bucket's first slot
+      s_size[b] = v;
     }
     __syncthreads();
     if (tid == 0) s_carry += s_warp[31];
     __syncthreads();
   }
   for (int i = tid; i < n_rows; i += blockDim.x) {
-    const int rank = slot_of_row[i];
-    if (rank < 0) continue;
-    int b = rows != nullptr ? *reinterpret_cast<const int32_t *>(rows + (long long)i * row_stride + d_model) : meta_in[i];
-    const int s = s_count[b] + rank;
-    slot_of_row[i] = s;
+    const int pos = slot_of_row[i];
+    if (pos >= 0) row_of_slot[s_count[bucket_of(i)] + pos] = i;
+  }
+  __syncthreads();
+  for (int i = tid; i < n_rows; i += blockDim.x) {
+    if (slot_of_row[i] < 0) continue;
+    const int b = bucket_of(i);
+    const int first = s_count[b], size = s_size[b];
+    int rank = 0;
+    for (int k = 0; k < size; k++) rank += (row_of_slot[first + k] < i);
+    slot_of_row[i] = first + rank;
+  }
+  __syncthreads();
+  for (int i = tid; i < n_rows; i += blockDim.x) {
+    const int s = slot_of_row[i];
+    if (s < 0) continue;
     row_of_slot[s] = i;
     // row i came from rank i / rows_per_block; its result goes to the same place of that rank's block
     if (out_ptr_of_slot != nullptr)
@@ -236,8 +242,8 @@ int launch_ep_dispatch(const int32_t *choice, const void *hidden, int64_t hidden
   const int n_slots = n_ranks * cap;
   const long long row_stride = d_model + 8;
   const int threads = 256;
-  const int n = n_tokens > n_slots ? n_tokens : n_slots;
-  QMOE_LAUNCH(k_ep_keep, (n + threads - 1) / threads, threads, 0, stream, choice, expert, dest, n_tokens, n_experts,
+  const long long n = (long long)n_tokens * 32 > n_slots ? (long long)n_tokens * 32 : n_slots;
+  QMOE_LAUNCH(k_ep_keep, (unsigned)((n + threads - 1) / threads), threads, 0, stream, choice, expert, dest, n_tokens, n_experts,
               local_experts, seq_len, capacity, reinterpret_cast<__nv_bfloat16 *>(send),
               reinterpret_cast<__nv_bfloat16 *const *>(blocks), cap > 0 ? cap : 1, n_slots, row_stride, d_model);
   QMOE_CUDA(cudaGetLastError());
@@ -253,7 +259,7 @@ int launch_ep_dispatch(const int32_t *choice, const void *hidden, int64_t hidden
 int launch_ep_plan(const void *rows, int64_t row_stride, int d_model, const int32_t *meta, int n_rows, int n_buckets,
                    int32_t *offsets, int32_t *slot_of_row, int32_t *row_of_slot, const uint64_t *out_blocks,
                    int rows_per_block, int64_t out_row_bytes, uint64_t *out_ptr_of_slot, cudaStream_t stream) {
-  QMOE_LAUNCH(k_ep_plan, 1, 1024, sizeof(int) * (size_t)n_buckets, stream,
+  QMOE_LAUNCH(k_ep_plan, 1, 1024, 2 * sizeof(int) * (size_t)n_buckets, stream,
               reinterpret_cast<const __nv_bfloat16 *>(rows), (long long)row_stride, d_model, meta, n_rows, n_buckets,
               offsets, slot_of_row, row_of_slot, reinterpret_cast<const unsigned long long *>(out_blocks),
               rows_per_block > 0 ? rows_per_block : 1, (long long)out_row_bytes,

@@ -171,23 +171,23 @@ __global__ void __launch_bounds__(256) k_route_small(const float *__restrict__ l
 
 // Capacity rule: kept iff fewer than `capacity` earlier tokens of the same sequence chose the same
 // expert (cumsum(one_hot, dim=-2) <= expert_capacity in the router).
+// One warp per token: the lanes share out the earlier tokens of the sequence.
 __global__ void k_capacity(const int32_t *__restrict__ choice, int32_t *__restrict__ bucket, int n_tokens,
                            int n_buckets, int seq_len, int capacity) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+  const int lane = threadIdx.x & 31;
   if (t >= n_tokens) return;
   const int c = choice[t];
-  if (c < 0 || c >= n_buckets) {
-    bucket[t] = -1;
-    return;
-  }
-  int keep = 1;
-  if (capacity < seq_len) {
+  int keep = c >= 0 && c < n_buckets;
+  if (keep && capacity < seq_len) {
     const int s0 = (t / seq_len) * seq_len;
     int before = 0;
-    for (int u = s0; u < t; u++) before += (choice[u] == c);
+    for (int u = s0 + lane; u < t; u += 32) before += (choice[u] == c);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) before += __shfl_xor_sync(0xffffffffu, before, o);
     keep = before < capacity;
   }
-  bucket[t] = keep ? c : -1;
+  if (lane == 0) bucket[t] = keep ? c : -1;
 }
 
 // rank[t] = number of earlier tokens in the same bucket; counts[b] = bucket sizes.  O(n^2) compares,
@@ -354,7 +354,8 @@ int launch_rank(const int32_t *choice, int32_t *bucket, int32_t *rank, int32_t *
   if (n_tokens == 0) return QMOE_OK;
   const int threads = 256;
   const int blocks = (n_tokens + threads - 1) / threads;
-  QMOE_LAUNCH(k_capacity, blocks, threads, 0, stream, choice, bucket, n_tokens, n_buckets, seq_len, capacity);
+  QMOE_LAUNCH(k_capacity, (unsigned)(((long long)n_tokens * 32 + threads - 1) / threads), threads, 0, stream, choice,
+              bucket, n_tokens, n_buckets, seq_len, capacity);
   QMOE_CUDA(cudaGetLastError());
   QMOE_LAUNCH(k_rank, blocks, threads, 0, stream, bucket, rank, counts, n_tokens);
   QMOE_CUDA(cudaGetLastError());
@@ -364,8 +365,8 @@ int launch_rank(const int32_t *choice, int32_t *bucket, int32_t *rank, int32_t *
 int launch_keep(const int32_t *choice, int32_t *expert, int n_tokens, int n_experts, int seq_len, int capacity,
                 cudaStream_t stream) {
   const int threads = 256;
-  QMOE_LAUNCH(k_capacity, (n_tokens + threads - 1) / threads, threads, 0, stream, choice, expert, n_tokens, n_experts,
-              seq_len, capacity);
+  QMOE_LAUNCH(k_capacity, (unsigned)(((long long)n_tokens * 32 + threads - 1) / threads), threads, 0, stream, choice,
+              expert, n_tokens, n_experts, seq_len, capacity);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }

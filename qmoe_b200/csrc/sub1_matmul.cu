@@ -991,8 +991,10 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
   const int total = min(s_total, max_slots);
   for (int g = tid; g < total; g += blockDim.x) done[g] = 0;  // finished first-linear items per pair
 
+  // ---- how either linear is cut ----------------------------------------------------------------
+  int rpc_of[2], main_of[2], chunks_of[2], wchunks_of[2], tail_of[2];
   for (int phase = 0; phase < 2; phase++) {
-    const WorkPhase p = phase == 0 ? p0 : p1;
+    const WorkPhase &p = phase == 0 ? p0 : p1;
     const int H = p.height;
     // rows [0, main_rows) in items of rpc rows for the per-thread kernel, the rest in warp items
     int rpc = rows_per_chunk_dev(H, kGroupedThreads), main_rows = H;
@@ -1001,9 +1003,8 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
     } else if (total > 0) {
       const int rest = H % kGroupedThreads;
       if (use_warp && H >= kGroupedThreads && rest != 0 && rest <= kWarpRemainderMax) main_rows = H - rest;
-      // c equal items per pair: the c that fills whole rounds of the SMs best (190 pairs x 2 items
-      // over 148 SMs are 2.6 rounds that cost 3; 3 items of 704 rows are 3.9 rounds that cost 4 x 0.69)
-      // Candidate c0 + tid is priced by thread tid; the cheapest (the smallest c among equals) wins.
+      // c equal items per pair: the c whose whole rounds of the SMs cost least.  Candidate c0 + tid is
+      // priced by thread tid; the cheapest (the smallest c among equals) wins.
       const int c0 = (main_rows + kGroupedThreads - 1) / kGroupedThreads;
       if (tid == 0) s_best = ~0ull;
       __syncthreads();
@@ -1025,18 +1026,25 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       if (forced > 0 && forced * 32 <= main_rows && (long long)total * forced <= p.capacity)
         best_rows = ((main_rows + forced - 1) / forced + 31) / 32 * 32;
       rpc = best_rows;
+      __syncthreads();  // s_best is reset for the other linear
     }
-    const int chunks = (main_rows + rpc - 1) / rpc;
+    rpc_of[phase] = rpc;
+    main_of[phase] = main_rows;
+    chunks_of[phase] = (main_rows + rpc - 1) / rpc;
     // what is left after the per-thread items: with none of those, items for the warp kernel;
     // otherwise the CTA that takes the last per-thread item does them, one row per warp (bit 15)
-    const int wchunks = main_rows == 0 ? (H + kWarpItemRows - 1) / kWarpItemRows : 0;
-    const int tail_flag = main_rows > 0 && main_rows < H ? 0x8000 : 0;
-    if (tid == 0) s_base = 0;
-    __syncthreads();
-    // Longest items first: the groups of four tokens of all experts, then those of three, two and
-    // one (an item's time grows with its tokens, and with a handful of items per SM the order in
-    // which the CTAs fetch them decides how uneven the last round is).
-    for (int cls = kMaxGroup; cls >= 1; cls--)
+    wchunks_of[phase] = main_rows == 0 ? (H + kWarpItemRows - 1) / kWarpItemRows : 0;
+    tail_of[phase] = main_rows > 0 && main_rows < H ? 0x8000 : 0;
+  }
+
+  // ---- the items ---------------------------------------------------------------------------------
+  // Longest items first: the groups of four tokens of all experts, then those of three, two and one
+  // (an item's time grows with its tokens, and with a handful of items per SM the order in which the
+  // CTAs fetch them decides how uneven the last round is).  The pairs get the same index in both
+  // linears.
+  if (tid == 0) s_base = 0;
+  __syncthreads();
+  for (int cls = kMaxGroup; cls >= 1; cls--)
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
       const int e = e0 + tid;
       int first, count;
@@ -1064,37 +1072,40 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       }
       __syncthreads();
       const int base = s_base + (warp ? s_warp[warp - 1] : 0) + incl - groups;
-      // Items for the per-thread kernel (a few per group): every lane writes those of its expert.
-      for (int g = 0; g < groups && chunks > 0; g++) {
-        const int gi = base + g;
-        if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
-        const int tok0 = first_tok + g * kMaxGroup;
-        const int ntok = cls;
-        for (int k = 0; k < chunks; k++) {
-          const int row0 = k * rpc;
-          p.items[(size_t)gi * chunks + k] =
-              make_int4(2 * e + p.which, row0, tok0,
-                        min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) | (ntok << 16));
+      for (int phase = 0; phase < 2; phase++) {
+        const WorkPhase &p = phase == 0 ? p0 : p1;
+        const int H = p.height, rpc = rpc_of[phase], main_rows = main_of[phase], chunks = chunks_of[phase];
+        const int wchunks = wchunks_of[phase], tail_flag = tail_of[phase];
+        // Items for the per-thread kernel (a few per group): every lane writes those of its expert.
+        for (int g = 0; g < groups && chunks > 0; g++) {
+          const int gi = base + g;
+          if (gi >= max_slots || (long long)(gi + 1) * chunks > p.capacity) break;  // cannot happen for valid offsets
+          const int tok0 = first_tok + g * kMaxGroup;
+          for (int k = 0; k < chunks; k++) {
+            const int row0 = k * rpc;
+            p.items[(size_t)gi * chunks + k] =
+                make_int4(2 * e + p.which, row0, tok0,
+                          min(rpc, main_rows - row0) | (k == chunks - 1 ? tail_flag : 0) | (cls << 16));
+          }
         }
-      }
-      // Items for the warp kernel (hundreds per group, but only in steps with a handful of groups):
-      // the whole warp writes those of each lane's expert in turn.
-      unsigned busy = __ballot_sync(0xffffffffu, groups > 0 && wchunks > 0);
-      while (busy) {
-        const int src = __ffs(busy) - 1;
-        busy &= busy - 1;
-        const int o_e = __shfl_sync(0xffffffffu, e, src), o_first = __shfl_sync(0xffffffffu, first_tok, src);
-        const int o_groups = __shfl_sync(0xffffffffu, groups, src);
-        const int o_base = __shfl_sync(0xffffffffu, base, src);
-        for (int g = 0; g < o_groups; g++) {
-          const int gi = o_base + g;
-          if (gi >= max_slots || (long long)(gi + 1) * wchunks > p.warp_capacity) break;
-          const int tok0 = o_first + g * kMaxGroup;
-          const int ntok = cls;
-          for (int k = lane; k < wchunks; k += 32) {
-            const int row0 = k * kWarpItemRows;
-            p.warp_items[(size_t)gi * wchunks + k] =
-                make_int4(2 * o_e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (ntok << 16));
+        // Items for the warp kernel (hundreds per group, but only in steps with a handful of groups):
+        // the whole warp writes those of each lane's expert in turn.
+        unsigned busy = __ballot_sync(0xffffffffu, groups > 0 && wchunks > 0);
+        while (busy) {
+          const int src = __ffs(busy) - 1;
+          busy &= busy - 1;
+          const int o_e = __shfl_sync(0xffffffffu, e, src), o_first = __shfl_sync(0xffffffffu, first_tok, src);
+          const int o_groups = __shfl_sync(0xffffffffu, groups, src);
+          const int o_base = __shfl_sync(0xffffffffu, base, src);
+          for (int g = 0; g < o_groups; g++) {
+            const int gi = o_base + g;
+            if (gi >= max_slots || (long long)(gi + 1) * wchunks > p.warp_capacity) break;
+            const int tok0 = o_first + g * kMaxGroup;
+            for (int k = lane; k < wchunks; k += 32) {
+              const int row0 = k * kWarpItemRows;
+              p.warp_items[(size_t)gi * wchunks + k] =
+                  make_int4(2 * o_e + p.which, row0, tok0, min(kWarpItemRows, H - row0) | (cls << 16));
+            }
           }
         }
       }
@@ -1102,17 +1113,17 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       if (tid == 0) s_base += s_warp[31];
       __syncthreads();
     }
-    if (tid == 0) {
-      const int groups_done = min(s_base, max_slots);
-      header[2 * phase] = groups_done * chunks;
+  if (tid == 0) {
+    const int groups_done = min(s_base, max_slots);
+    for (int phase = 0; phase < 2; phase++) {
+      header[2 * phase] = groups_done * chunks_of[phase];
       header[2 * phase + 1] = 0;
-      header[10 + 2 * phase] = groups_done * wchunks;
+      header[10 + 2 * phase] = groups_done * wchunks_of[phase];
       header[11 + 2 * phase] = 0;
-      header[6 + phase] = rpc;  // rows per item of this phase (reports)
-      header[9] = kMaxGroup;
-      header[14 + phase] = chunks;  // per-thread items per (expert, token group) of this phase
+      header[6 + phase] = rpc_of[phase];      // rows per item of this phase (reports)
+      header[14 + phase] = chunks_of[phase];  // per-thread items per (expert, token group) of this phase
     }
-    __syncthreads();
+    header[9] = kMaxGroup;
   }
 }
 
