@@ -63,6 +63,9 @@ def parse_args():
     p.add_argument("--no-gpu-reference", action="store_true", help="skip the timing of the reference's own kernel")
     p.add_argument("--min-seconds", type=float, default=1.0,
                    help="the timed loop of --steps steps is repeated until this much time has been timed")
+    p.add_argument("--decode-input", default="forced", choices=["forced", "greedy"],
+                   help="generate mode: what a decode step is fed (forced: seeded random ids, so that steps visit "
+                        "different experts; greedy: the previous step's argmax)")
     p.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                    help="N > 1: how rows travel between ranks (peer: stored straight into the peers' memory over "
                         "NVLink; nccl: two all-to-all collectives; auto: peer where it can be set up)")
@@ -364,30 +367,29 @@ def gpu_reference_leg(store, dev, d_model, d_ff, counts, hidden_dev, ours_tokens
             "ours_over_reference": ours_tokens_per_s / value if value > 0 else None}
 
 
-def l2_resident_rate(dev, d_model, d_ff, lib):
-    """The grouped kernel on a layer small enough to stay in L2 (37 experts, 84 MB of a 126 MB L2),
-    one token per expert, the step repeated back to back: after the first pass no launch reads HBM, so
-    the rate shows what the SMs sustain when the memory system is out of the picture (the kernel's
-    on-chip ceiling for the batch-1 case).  Returns (GB/s of algorithmic bytes, codes/s, experts)."""
+def l2_resident_rate(dev, d_model, d_ff, n_experts, hidden, logits, lib):
+    """The benchmark's own step -- same tokens, same routing, same work list -- over weights that stay
+    in L2: a layer whose `n_experts` experts alias the matrices of EIGHT real experts (19 MB of code
+    streams in a 126 MB L2).  After the first pass no grouped launch reads codes from HBM, so the rate
+    is what the SMs' issue and shared-memory pipes sustain for this decoder on this workload with the
+    memory system out of the picture.  Returns the milliseconds of the grouped launches per step."""
     import ctypes
     import torch
     from qmoe_b200 import _lib, sub1, synth
-    n = 37                                              # 37 x 8 wi items = two full rounds of 148 SMs
-    store = synth.build_store(d_model, d_ff, list(range(n)), SEED, dev)
-    xs = synth.tokens(n, d_model, SEED + 3).to(dev)
-    offsets = torch.arange(n + 1, dtype=torch.int32, device=dev)
-    for _ in range(5):
-        sub1.grouped_ffn(store, offsets, xs, n)
+    real = 8
+    base = synth.build_store(d_model, d_ff, list(range(real)), SEED, dev)
+    layer = sub1.FasterMLP(None, base.aliased(n_experts), expert_capacity=1024)
+    h, lg = hidden.unsqueeze(0), logits.unsqueeze(0)
+    for _ in range(3):
+        layer(h, router_logits=lg)
     lib.qmoe_profile_enable(1)
-    for _ in range(20):
-        sub1.grouped_ffn(store, offsets, xs, n)
+    for _ in range(10):
+        layer(h, router_logits=lg)
+    torch.cuda.synchronize()
     lib.qmoe_profile_enable(0)
     wi_ms, wo_ms, calls = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
     _lib.check(lib.qmoe_profile_read(ctypes.byref(wi_ms), ctypes.byref(wo_ms), ctypes.byref(calls)))
-    alg = sum(store.matrix_bytes(m) for m in range(2 * n)) + 2 * 2 * n * (d_model + d_ff)
-    ms = (wi_ms.value + wo_ms.value) / max(calls.value, 1)
-    codes = sum(d.n_codes for d in store.host_descs)
-    return alg / (ms * 1e-3) / 1e9, codes / (ms * 1e-3), n
+    return (wi_ms.value + wo_ms.value) / max(calls.value, 1), real
 
 
 def run_ours(args):
@@ -691,14 +693,20 @@ def run_ours(args):
                 "bound": "hbm", "achieved": b1 / (ms1 * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                 "frac": b1 / (ms1 * 1e-3) / 1e9 / peak, "algorithmic_bytes_per_launch": b1, "ms_per_launch": ms1}
         if world == 1:
-            gbs, codes_s, n_l2 = l2_resident_rate(dev, d_model, d_ff, lib)
-            sm_hz = (clocks or {}).get("sm_mhz") or 1965.0
+            lg_l2 = given if given is not None else rl_chk.reshape(t_local, n_experts).float()
+            ms_l2, n_l2 = l2_resident_rate(dev, d_model, d_ff, n_experts, hidden_dev, lg_l2, lib)
+            gbs = (bytes_wi + bytes_wo) / (ms_l2 * 1e-3) / 1e9 if ms_l2 > 0 else None
+            sm_hz = ((clocks or {}).get("sm_mhz") or 1965.0) * 1e6
+            codes_step = sum(store.host_descs[2 * e].n_codes + store.host_descs[2 * e + 1].n_codes
+                             for e, c in enumerate(counts) if c > 0)
             line["roofline_smem"] = {
-                "bound": "smem", "achieved": achieved, "peak": gbs, "unit": "GB/s", "frac": achieved / gbs if gbs else None,
-                "what": f"peak = the same kernels on a {n_l2}-expert layer (one token each) that stays in L2 and is "
-                        "run back to back: no HBM traffic, so this is what the SMs' shared-memory and issue pipes "
-                        "sustain for this decoder; achieved = the HBM-resident layer of this benchmark",
-                "codes_per_sm_per_clock_at_peak": codes_s / (148 * sm_hz * 1e6)}
+                "bound": "smem", "achieved": achieved, "peak": gbs, "unit": "GB/s",
+                "frac": achieved / gbs if gbs else None, "ms_per_step_l2_resident": ms_l2,
+                "what": f"peak = this benchmark's own step (same tokens, routing and work list) on a layer whose "
+                        f"{n_experts} experts alias the matrices of {n_l2} real experts, so that every code stream "
+                        "stays in L2: no HBM traffic for codes, i.e. what the SMs' issue and shared-memory pipes "
+                        "sustain for this decoder on this workload; achieved = the HBM-resident layer",
+                "codes_per_sm_per_clock_at_peak": codes_step / (ms_l2 * 1e-3) / (148 * sm_hz) if ms_l2 > 0 else None}
         if world == 1 and not args.no_gpu_reference:
             line["gpu_reference"] = gpu_reference_leg(store, dev, d_model, d_ff, counts, hidden_dev, value)
         if world == 1 and not args.no_cpu_baseline:
@@ -830,17 +838,40 @@ def run_generate(args):
     torch.cuda.synchronize()
     setup_s = time.perf_counter() - t0
     prompt = torch.randint(0, 32128, (prompt_len,), generator=torch.Generator().manual_seed(SEED))
+    # Teacher-forced decode input: seeded random ids, so that consecutive steps route to different
+    # experts (greedy output of random weights repeats one token and would keep re-reading one expert
+    # per block from L2).  --decode-input greedy feeds the argmax back instead.
+    forced = None
+    if args.decode_input == "forced":
+        forced = torch.randint(0, 32128, (new_tokens,), generator=torch.Generator().manual_seed(SEED + 1))
     times = []
     for it in range(max(args.steps, 1) + 1):                 # first sample is warm-up (sub1.py:382)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        out = model.generate(prompt, new_tokens, use_graph=not args.no_graph)
+        out = model.generate(prompt, new_tokens, use_graph=not args.no_graph, forced=forced)
         torch.cuda.synchronize()
         if it > 0:
             times.append(time.perf_counter() - t0)
     secs = sum(times) / len(times)
+    timing = dict(getattr(model, "last_timing", None) or {})
+    # one more sample, untimed and eager, that counts which experts the decode steps visit
+    model.trace_experts(True)
+    model.generate(prompt, new_tokens, use_graph=False, forced=forced)
+    torch.cuda.synchronize()
+    trace = model.expert_trace()                               # [layers, experts]
+    model.trace_experts(False)
+    steps_traced = new_tokens - 1
+    distinct = (trace > 0).sum(1)
+    store0 = model.blocks[0]["moe"].store
+    expert_bytes = sum(store0.matrix_bytes(m) for m in range(2 * store0.n_experts)) / store0.n_experts
+    experts_visited = {
+        "decode_steps": steps_traced, "distinct_experts_per_block_mean": float(distinct.float().mean()),
+        "distinct_experts_per_block_min": int(distinct.min()), "distinct_experts_per_block_max": int(distinct.max()),
+        "distinct_experts_all_blocks": int(distinct.sum()),
+        "compressed_bytes_streamed_per_token": int(layers * expert_bytes),
+        "note": "one expert per block and token; bytes = codes + row offsets + (min, max) of its two matrices"}
     kernel_times = None
     if args.kernel_times and world == 1:
         # five eager single-token steps under the torch profiler, after the timed samples
@@ -874,7 +905,9 @@ def run_generate(args):
                        "setup_s": round(setup_s, 1),
                        "execution": "eager" if args.no_graph else "cuda-graph replay of the decode step"},
             "data": "synthetic (seeded dense bf16 weights N(0,0.02), seeded ternary experts, random prompt ids)",
-            "timing_last_sample": getattr(model, "last_timing", None),
+            "decode_input": args.decode_input, "experts_visited": experts_visited,
+            "decode_tokens_per_s": (timing["decode_steps"] / timing["decode_s"]) if timing.get("decode_s") else None,
+            "timing_last_sample": timing,
             "first_tokens": out[:8].tolist()}), flush=True)
     model.close()                      # the graph holds the NCCL communicator
     if world > 1:

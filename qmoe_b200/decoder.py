@@ -36,6 +36,7 @@ class ReplicatedTokenMoE:
         self.local = n_experts // world
         self.capacity = expert_capacity
         self.router = sub1.RouterClassifier(router_weight, store.device)
+        self.trace: Optional[torch.Tensor] = None   # int32[n_experts]: tokens routed to every expert in decode steps
 
     def decode_step(self, x: torch.Tensor, ln_weight: torch.Tensor) -> torch.Tensor:
         """``x + moe(rms_norm(x))`` for one token; the norm rides on the router's matrix-vector
@@ -51,10 +52,21 @@ class ReplicatedTokenMoE:
         n, d = hidden.shape
         if logits is None:
             logits = self.router(hidden).contiguous()
-        if self.world == 1 and n <= 32:
-            # a decode step: routing, ranking and permutation in one launch
+        if n <= 32:
+            # a decode step: routing, ranking and permutation in one launch (every rank does the same
+            # routing on the same replicated token)
             prob, offsets, slot, xs = sub1.route_small(logits, hidden, self.n_experts, self.capacity)
-            ys = sub1.grouped_ffn(self.store, offsets, xs, n)
+            if self.trace is not None:
+                self.trace += offsets[1:] - offsets[:-1]
+            if self.world == 1:
+                ys = sub1.grouped_ffn(self.store, offsets, xs, n)
+            else:
+                # This rank's experts are a window of the offsets; rows of other ranks' experts stay zero
+                # and arrive through the all-reduce (one rank holds the row, the sum is exact).
+                lo = self.rank * self.local
+                ys = torch.zeros_like(xs)
+                sub1.grouped_ffn_rows(self.store, offsets[lo:lo + self.local + 1], xs, None, ys, None, n)
+                dist.all_reduce(ys, group=self.group)
             if residual is not None:
                 return sub1.combine_add(ys, hidden, slot, prob, residual)
             return sub1.combine(ys, hidden, slot, prob)
@@ -170,8 +182,24 @@ class SwitchDecoderLM:
         return sub1.gemv(x, self.lm_head, ln_weight=self.final_norm, f32_out=True)
 
     @torch.no_grad()
-    def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True) -> torch.Tensor:
-        """Greedy generation: prefill the prompt, then ``n_new`` single-token steps."""
+    def trace_experts(self, on: bool) -> None:
+        """Start (zeroed) or stop counting, per block, the tokens every expert receives in decode
+        steps.  Adds two small launches per block: for untimed, eager passes."""
+        for b in self.blocks:
+            moe = b["moe"]
+            moe.trace = torch.zeros(moe.n_experts, dtype=torch.int32, device=self.dev) if on else None
+
+    def expert_trace(self) -> torch.Tensor:
+        """int32[n_layers, n_experts] of the counts since ``trace_experts(True)`` (a host copy)."""
+        return torch.stack([b["moe"].trace for b in self.blocks]).cpu()
+
+    def generate(self, prompt: torch.Tensor, n_new: int, use_graph: bool = True,
+                 forced: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Prefill the prompt, then ``n_new`` single-token steps.  Greedy by default: every step's
+        input is the previous step's argmax.  With ``forced`` (int64[n_new - 1]) step ``k`` is fed
+        ``forced[k]`` instead (teacher forcing: the returned argmax tokens are still computed), so that
+        a model with random weights, whose greedy output soon repeats one token, still visits different
+        experts from step to step as a trained model does."""
         import time
         p = prompt.shape[0]
         assert p + n_new <= self.max_len
@@ -204,8 +232,11 @@ class SwitchDecoderLM:
         self.last_generate_used_graph = graph is not None
         torch.cuda.synchronize(self.dev)
         t_capture = time.perf_counter()
-        for _ in range(n_new - 1):
-            step_ids.copy_(tok)
+        if forced is not None:
+            forced = forced.to(self.dev).reshape(-1, 1)
+            assert forced.shape[0] >= n_new - 1
+        for k in range(n_new - 1):
+            step_ids.copy_(tok if forced is None else forced[k])
             if graph is not None:
                 graph.static_in.copy_(step_ids)
                 tok = graph.replay().clone()

@@ -197,6 +197,21 @@ class ExpertStore:
         self.il_struct = _lib.InterleavedStore(il.data_ptr(), base.data_ptr(), self.il_table.data_ptr(),
                                                self.il_dec.data_ptr())
 
+    def aliased(self, n_experts: int) -> "ExpertStore":
+        """A store of ``n_experts`` experts whose expert ``e`` IS this store's expert
+        ``e % self.n_experts``: the same arrays and the same interleaved copy under a longer descriptor
+        table, nothing copied.  For measurements that need a full layer's routing pattern over weights
+        small enough to stay in L2."""
+        descs = [self.host_descs[2 * (e % self.n_experts) + k] for e in range(n_experts) for k in (0, 1)]
+        other = ExpertStore(self.codes, self.row_off, self.minmax, descs, self.d_model, self.d_ff,
+                            interleave=False, dec=self.dec)
+        if self.il_codes is not None:
+            for name in ("il_codes", "blk_base", "il_table", "il_dec", "il_struct"):
+                setattr(other, name, getattr(self, name))
+            if hasattr(self, "remap"):
+                other.remap = self.remap
+        return other
+
     @property
     def resident_bytes(self) -> int:
         """Device bytes held, including the interleaved copy."""

@@ -72,6 +72,17 @@ def test_decoder_blocks_match_dense_reference_and_graph_decoding():
     assert model.last_generate_used_graph
     assert torch.equal(eager, graphed)
     assert eager.shape == (10,) and int(eager.max()) < 512
+    # teacher-forced input (what the benchmark feeds): eager and graph replay agree, the forced ids
+    # are what the steps consume, and the trace counts one expert per block and decode step
+    forced = torch.randint(0, 512, (9,), generator=g)
+    f_eager = model.generate(ids, 10, use_graph=False, forced=forced)
+    assert torch.equal(model.generate(ids, 10, use_graph=True, forced=forced), f_eager)
+    assert torch.equal(f_eager[:1], eager[:1]) and not torch.equal(f_eager, eager)
+    model.trace_experts(True)
+    assert torch.equal(model.generate(ids, 10, use_graph=False, forced=forced), f_eager)
+    trace = model.expert_trace()
+    model.trace_experts(False)
+    assert trace.shape == (2, 8) and trace.sum(1).tolist() == [9, 9]
     # the same model holding only the interleaved copies of its experts (how the benchmark runs it)
     for b in model.blocks:
         b["moe"].store.drop_reference_layout()
