@@ -66,6 +66,9 @@ def parse_args():
     p.add_argument("--decode-input", default="forced", choices=["forced", "greedy"],
                    help="generate mode: what a decode step is fed (forced: seeded random ids, so that steps visit "
                         "different experts; greedy: the previous step's argmax)")
+    p.add_argument("--decode-routing", default="uniform", choices=["uniform", "model"],
+                   help="generate mode: uniform = every decode step is sent to a seeded random expert in every block "
+                        "(a balanced router); model = the random-init routers decide (a few experts per block)")
     p.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                    help="N > 1: how rows travel between ranks (peer: stored straight into the peers' memory over "
                         "NVLink; nccl: two all-to-all collectives; auto: peer where it can be set up)")
@@ -844,6 +847,12 @@ def run_generate(args):
     forced = None
     if args.decode_input == "forced":
         forced = torch.randint(0, 32128, (new_tokens,), generator=torch.Generator().manual_seed(SEED + 1))
+    if args.decode_routing == "uniform":
+        # every decode step visits a seeded random expert in every block: what a trained, balanced
+        # router does to a token stream (random weights send a whole sequence to a handful of experts
+        # per block, which then never leave L2)
+        model.set_forced_routing(torch.randint(0, n_experts, (new_tokens, layers),
+                                               generator=torch.Generator().manual_seed(SEED + 2)))
     times = []
     for it in range(max(args.steps, 1) + 1):                 # first sample is warm-up (sub1.py:382)
         if world > 1:
@@ -905,7 +914,8 @@ def run_generate(args):
                        "setup_s": round(setup_s, 1),
                        "execution": "eager" if args.no_graph else "cuda-graph replay of the decode step"},
             "data": "synthetic (seeded dense bf16 weights N(0,0.02), seeded ternary experts, random prompt ids)",
-            "decode_input": args.decode_input, "experts_visited": experts_visited,
+            "decode_input": args.decode_input, "decode_routing": args.decode_routing,
+            "experts_visited": experts_visited,
             "decode_tokens_per_s": (timing["decode_steps"] / timing["decode_s"]) if timing.get("decode_s") else None,
             "timing_last_sample": timing,
             "first_tokens": out[:8].tolist()}), flush=True)

@@ -37,6 +37,7 @@ class ReplicatedTokenMoE:
         self.capacity = expert_capacity
         self.router = sub1.RouterClassifier(router_weight, store.device)
         self.trace: Optional[torch.Tensor] = None   # int32[n_experts]: tokens routed to every expert in decode steps
+        self.force: Optional[torch.Tensor] = None   # int64[1] on the device: expert that decode steps are sent to
 
     def decode_step(self, x: torch.Tensor, ln_weight: torch.Tensor) -> torch.Tensor:
         """``x + moe(rms_norm(x))`` for one token; the norm rides on the router's matrix-vector
@@ -52,11 +53,14 @@ class ReplicatedTokenMoE:
         n, d = hidden.shape
         if logits is None:
             logits = self.router(hidden).contiguous()
+        if self.force is not None and n == 1:
+            # measurement aid: the step's expert is given (a large logit), whatever the router computed
+            logits = logits.index_fill(1, self.force, 1e4)
         if n <= 32:
             # a decode step: routing, ranking and permutation in one launch (every rank does the same
             # routing on the same replicated token)
             prob, offsets, slot, xs = sub1.route_small(logits, hidden, self.n_experts, self.capacity)
-            if self.trace is not None:
+            if self.trace is not None and n == 1:                # decode steps only, not a short prefill
                 self.trace += offsets[1:] - offsets[:-1]
             if self.world == 1:
                 ys = sub1.grouped_ffn(self.store, offsets, xs, n)
@@ -189,6 +193,24 @@ class SwitchDecoderLM:
             moe = b["moe"]
             moe.trace = torch.zeros(moe.n_experts, dtype=torch.int32, device=self.dev) if on else None
 
+    def set_forced_routing(self, schedule: Optional[torch.Tensor]) -> None:
+        """``schedule`` int64[steps, n_layers]: decode step ``k`` of :meth:`generate` sends its token
+        to expert ``schedule[k, i]`` in block ``i`` (its router probability becomes 1).  Random
+        weights route almost every token of a sequence to the same few experts per block, which then
+        stay in L2; a trained model does not.  ``None`` gives the routing back to the routers.  A
+        captured decode graph is dropped either way."""
+        self.close()
+        if schedule is None:
+            self._route_sched = None
+            for b in self.blocks:
+                b["moe"].force = None
+            return
+        assert schedule.dtype == torch.int64 and schedule.shape[1] == len(self.blocks)
+        self._route_sched = schedule.to(self.dev).contiguous()
+        self._route_now = torch.zeros(len(self.blocks), dtype=torch.int64, device=self.dev)
+        for i, b in enumerate(self.blocks):
+            b["moe"].force = self._route_now[i:i + 1]
+
     def expert_trace(self) -> torch.Tensor:
         """int32[n_layers, n_experts] of the counts since ``trace_experts(True)`` (a host copy)."""
         return torch.stack([b["moe"].trace for b in self.blocks]).cpu()
@@ -235,8 +257,12 @@ class SwitchDecoderLM:
         if forced is not None:
             forced = forced.to(self.dev).reshape(-1, 1)
             assert forced.shape[0] >= n_new - 1
+        sched = getattr(self, "_route_sched", None)
+        assert sched is None or sched.shape[0] >= n_new - 1
         for k in range(n_new - 1):
             step_ids.copy_(tok if forced is None else forced[k])
+            if sched is not None:
+                self._route_now.copy_(sched[k])
             if graph is not None:
                 graph.static_in.copy_(step_ids)
                 tok = graph.replay().clone()

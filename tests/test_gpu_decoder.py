@@ -83,6 +83,17 @@ def test_decoder_blocks_match_dense_reference_and_graph_decoding():
     trace = model.expert_trace()
     model.trace_experts(False)
     assert trace.shape == (2, 8) and trace.sum(1).tolist() == [9, 9]
+    # forced routing: every step goes where the schedule says, eager and graph replay agree
+    sched = torch.randint(0, 8, (9, 2), generator=g)
+    model.set_forced_routing(sched)
+    model.trace_experts(True)
+    r_eager = model.generate(ids, 10, use_graph=False, forced=forced)
+    want = torch.stack([torch.bincount(sched[:, i], minlength=8) for i in range(2)])
+    assert torch.equal(model.expert_trace().long(), want)
+    model.trace_experts(False)
+    assert torch.equal(model.generate(ids, 10, use_graph=True, forced=forced), r_eager)
+    model.set_forced_routing(None)
+    assert torch.equal(model.generate(ids, 10, use_graph=True, forced=forced), f_eager)
     # the same model holding only the interleaved copies of its experts (how the benchmark runs it)
     for b in model.blocks:
         b["moe"].store.drop_reference_layout()
