@@ -245,6 +245,12 @@ typedef struct qmoe_interleaved_store {
   const int64_t *blk_base; /* [total_rows / 32 + 1], device */
   const uint32_t *table;   /* uint32[65536] from qmoe_sub1_remap_tables, device */
   const int32_t *dec;      /* int32[131072] from qmoe_sub1_remap_tables, device */
+  const int32_t *rows;     /* NULL, or int32[total_rows], device: the row of its matrix whose stream sits at
+                              position p of the store (a permutation inside every matrix, the one given to
+                              qmoe_moe_interleave_count_rows / _emit_rows).  Blocks are made of 32 consecutive
+                              POSITIONS; putting rows of similar length side by side (sorted by code count
+                              inside every 1024 positions) lets the 32 lanes of a warp finish together and
+                              shrinks the padding.  Results do not depend on it. */
 } qmoe_interleaved_store;
 
 int qmoe_sub1_code_histogram(const uint16_t *codes_dev, int64_t n_codes, uint64_t *hist_dev /* [65536], added to */,
@@ -258,6 +264,13 @@ int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_d
                              const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
                              const uint32_t *remap_dev /* [65536] or NULL */, void *il_codes_dev, int device,
                              void *stream);
+int qmoe_moe_interleave_count_rows(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                                   const qmoe_matrix_desc *descs_host, int n_matrices, const int32_t *rows_dev,
+                                   int32_t *blk_units_dev, int device, void *stream);
+int qmoe_moe_interleave_emit_rows(const uint16_t *codes_dev, const int32_t *row_off_dev,
+                                  const qmoe_matrix_desc *descs_dev, int n_matrices, const int32_t *rows_dev,
+                                  const int64_t *blk_base_dev, const uint32_t *remap_dev /* [65536] or NULL */,
+                                  void *il_codes_dev, int device, void *stream);
 int qmoe_moe_grouped_ffn_interleaved(const int32_t *dec_dev, const uint16_t *codes_dev,
                                      const int32_t *row_off_dev, const void *minmax_dev,
                                      const qmoe_matrix_desc *descs_dev, const qmoe_interleaved_store *store,

@@ -52,7 +52,7 @@ class InterleavedStore(ctypes.Structure):
     """Mirror of ``qmoe_interleaved_store``."""
 
     _fields_ = [("codes", ctypes.c_void_p), ("blk_base", ctypes.c_void_p), ("table", ctypes.c_void_p),
-                ("dec", ctypes.c_void_p)]
+                ("dec", ctypes.c_void_p), ("rows", ctypes.c_void_p)]
 
 
 _P = ctypes.c_void_p
@@ -96,6 +96,8 @@ SIGNATURES = {
     "qmoe_moe_peer_barrier": (_I, [_P, _I, _I, _I, _L, _P, _I, _P]),
     "qmoe_moe_interleave_count": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "qmoe_moe_interleave_emit": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P]),
+    "qmoe_moe_interleave_count_rows": (_I, [_P, _P, _P, _I, _P, _P, _I, _P]),
+    "qmoe_moe_interleave_emit_rows": (_I, [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine_add": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "qmoe_moe_route_small": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _I, _P]),
     "qmoe_rms_norm": (_I, [_P, _P, _P, _I, _I, ctypes.c_float, _I, _P]),

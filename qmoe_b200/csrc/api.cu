@@ -134,11 +134,11 @@ int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const
 int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream);
 int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
                         int *scratch2, cudaStream_t stream);
-int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
+int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices, const int32_t *rows,
                             int32_t *blk_units, cudaStream_t stream);
 int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
-                           int n_matrices, const int64_t *blk_base, const uint32_t *remap, void *il,
-                           cudaStream_t stream);
+                           int n_matrices, const int32_t *rows, const int64_t *blk_base, const uint32_t *remap,
+                           void *il, cudaStream_t stream);
 int launch_pack_prepare(const int32_t *trie, int32_t *w_tern, int32_t *row_off, int height, int width,
                         cudaStream_t stream);
 int launch_pack_emit(const int32_t *w_tern, const int32_t *row_off, uint16_t *w_comp, int height, int width,
@@ -746,34 +746,73 @@ int qmoe_sub1_remap_tables(const int32_t *dec_dev, const uint32_t *remap_dev, ui
   return QMOE_OK;
 }
 
-int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
-                              const qmoe_matrix_desc *descs_host, int n_matrices, int32_t *blk_units_dev,
-                              int device, void *stream) {
-  QMOE_REQUIRE(row_off_dev && descs_dev && descs_host && blk_units_dev, "null pointer");
-  QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
+static int interleave_count_entry(const char *fn, const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                                  const qmoe_matrix_desc *descs_host, int n_matrices, const int32_t *rows_dev,
+                                  int32_t *blk_units_dev, int device, void *stream) {
+  if (!(row_off_dev && descs_dev && descs_host && blk_units_dev) || n_matrices < 1) {
+    set_error("%s: null pointer or bad matrix count", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
   int64_t rows = 0;
   for (int m = 0; m < n_matrices; m++) {
     if (descs_host[m].height % 32 != 0 || descs_host[m].minmax_base != rows) {
-      set_error("%s: matrix %d: heights must be multiples of 32 and rows must be stored back to back", __func__, m);
+      set_error("%s: matrix %d: heights must be multiples of 32 and rows must be stored back to back", fn, m);
       return QMOE_ERR_UNSUPPORTED;
     }
     rows += descs_host[m].height;
   }
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_interleave_count(row_off_dev, descs_dev, n_matrices, blk_units_dev, as_stream(stream));
+  return launch_interleave_count(row_off_dev, descs_dev, n_matrices, rows_dev, blk_units_dev, as_stream(stream));
+}
+
+int qmoe_moe_interleave_count(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                              const qmoe_matrix_desc *descs_host, int n_matrices, int32_t *blk_units_dev,
+                              int device, void *stream) {
+  return interleave_count_entry(__func__, row_off_dev, descs_dev, descs_host, n_matrices, nullptr, blk_units_dev,
+                                device, stream);
+}
+
+int qmoe_moe_interleave_count_rows(const int32_t *row_off_dev, const qmoe_matrix_desc *descs_dev,
+                                   const qmoe_matrix_desc *descs_host, int n_matrices, const int32_t *rows_dev,
+                                   int32_t *blk_units_dev, int device, void *stream) {
+  QMOE_REQUIRE(rows_dev != nullptr, "null row list");
+  return interleave_count_entry(__func__, row_off_dev, descs_dev, descs_host, n_matrices, rows_dev, blk_units_dev,
+                                device, stream);
+}
+
+static int interleave_emit_entry(const char *fn, const uint16_t *codes_dev, const int32_t *row_off_dev,
+                                 const qmoe_matrix_desc *descs_dev, int n_matrices, const int32_t *rows_dev,
+                                 const int64_t *blk_base_dev, const uint32_t *remap_dev, void *il_codes_dev,
+                                 int device, void *stream) {
+  if (!(codes_dev && row_off_dev && descs_dev && blk_base_dev && il_codes_dev) || n_matrices < 1) {
+    set_error("%s: null pointer or bad matrix count", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  if ((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) != 0) {
+    set_error("%s: interleaved store must be 16-byte aligned", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
+  DeviceGuard guard(device);
+  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
+  return launch_interleave_emit(codes_dev, row_off_dev, descs_dev, n_matrices, rows_dev, blk_base_dev, remap_dev,
+                                il_codes_dev, as_stream(stream));
 }
 
 int qmoe_moe_interleave_emit(const uint16_t *codes_dev, const int32_t *row_off_dev,
                              const qmoe_matrix_desc *descs_dev, int n_matrices, const int64_t *blk_base_dev,
                              const uint32_t *remap_dev, void *il_codes_dev, int device, void *stream) {
-  QMOE_REQUIRE(codes_dev && row_off_dev && descs_dev && blk_base_dev && il_codes_dev, "null pointer");
-  QMOE_REQUIRE(n_matrices >= 1, "bad matrix count");
-  QMOE_REQUIRE((reinterpret_cast<uintptr_t>(il_codes_dev) & 15u) == 0, "interleaved store must be 16-byte aligned");
-  DeviceGuard guard(device);
-  if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_interleave_emit(codes_dev, row_off_dev, descs_dev, n_matrices, blk_base_dev, remap_dev,
-                                il_codes_dev, as_stream(stream));
+  return interleave_emit_entry(__func__, codes_dev, row_off_dev, descs_dev, n_matrices, nullptr, blk_base_dev,
+                               remap_dev, il_codes_dev, device, stream);
+}
+
+int qmoe_moe_interleave_emit_rows(const uint16_t *codes_dev, const int32_t *row_off_dev,
+                                  const qmoe_matrix_desc *descs_dev, int n_matrices, const int32_t *rows_dev,
+                                  const int64_t *blk_base_dev, const uint32_t *remap_dev, void *il_codes_dev,
+                                  int device, void *stream) {
+  QMOE_REQUIRE(rows_dev != nullptr, "null row list");
+  return interleave_emit_entry(__func__, codes_dev, row_off_dev, descs_dev, n_matrices, rows_dev, blk_base_dev,
+                               remap_dev, il_codes_dev, device, stream);
 }
 
 int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev, const void *prob_dev,

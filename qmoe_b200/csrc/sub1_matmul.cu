@@ -177,6 +177,7 @@ struct MatmulArgs {
   const qmoe_matrix_desc *descs;  // grouped mode
   const uint4 *il;                // grouped mode, lane-interleaved streams (or null)
   const long long *blk_base;      // first uint4 of every 32-row block of `il`, plus the end
+  const int32_t *il_rows;         // optional: row of its matrix that position p of the interleaved store holds
   const uint32_t *il_tab;         // sparse table in the order of the interleaved store's code values
   const int32_t *il_dec;          // reference table words in that order
   int n_hot;                      // entries of il_tab kept in shared memory
@@ -284,7 +285,16 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
   __syncthreads();
 
   if (tid < nrows) {
-    const int row = row0 + tid;
+    // With an interleaved store whose rows were re-ordered (rows of similar length side by side), thread
+    // tid walks the stream at POSITION row0 + tid, which belongs to row il_rows[...] of the matrix.
+    const int pos = row0 + tid;
+    int row = pos;
+    if constexpr (IL) {
+      if (a.il_rows != nullptr) {
+        row = a.il_rows[d.minmax_base + pos];
+        row = row < 0 ? 0 : (row >= d.height ? d.height - 1 : row);
+      }
+    }
     const int32_t *ro = a.row_off + d.rowoff_base;
     long long b = ro[row], e = ro[row + 1];
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
@@ -295,11 +305,11 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
     if constexpr (IL) {
       // Row blocks of 32 rows start at multiples of 32 in every matrix and in the store.
-      const long long gblk = (d.minmax_base + row) >> 5;
+      const long long gblk = (d.minmax_base + pos) >> 5;
       const long long first = a.blk_base[gblk];
       const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;  // codes per row of this block
       const long long n = e - b < room ? e - b : room;
-      walk_row<GENERAL>(LaneFetch{a.il + first + (row & 31)}, 0, (int)n, lookup, a.il_dec, wlim, sink);
+      walk_row<GENERAL>(LaneFetch{a.il + first + (pos & 31)}, 0, (int)n, lookup, a.il_dec, wlim, sink);
     } else {
       const uint16_t *codes_m = a.codes + d.code_base;
       const int mis = (int)((reinterpret_cast<uintptr_t>(codes_m) & 15u) >> 1);
@@ -487,15 +497,20 @@ __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe
   const int wlim = (d.width + 1) & ~1;
   const int32_t *ro = a.row_off + d.rowoff_base;
   for (int r = warp; r < nrows; r += nwarps) {
-    const int row = row0 + r;
+    const int pos = row0 + r;  // position in the store; its row of the matrix may differ (il_rows)
+    int row = pos;
+    if (a.il_rows != nullptr) {
+      row = a.il_rows[d.minmax_base + pos];
+      row = row < 0 ? 0 : (row >= d.height ? d.height - 1 : row);
+    }
     long long b = ro[row], e = ro[row + 1];
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
     e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
-    const long long gblk = (d.minmax_base + row) >> 5;
+    const long long gblk = (d.minmax_base + pos) >> 5;
     const long long first = a.blk_base[gblk];
     const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;
     const int n = (int)(e - b < room ? e - b : room);
-    const uint16_t *src = reinterpret_cast<const uint16_t *>(a.il + first + (row & 31));
+    const uint16_t *src = reinterpret_cast<const uint16_t *>(a.il + first + (pos & 31));
     const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
     SinkT sink;
     sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
@@ -859,14 +874,23 @@ int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab
 // k * 32 + l, so the 32 lanes of a warp read 512 contiguous bytes per step instead of 32 separate
 // cache lines.  Every row of a block is padded with zero codes to the block's longest row, rounded
 // up to a whole chunk; the row lengths still come from row_off.  Heights must be multiples of 32.
+// `rows` (optional): the row of its matrix that every position of the store holds (a permutation of
+// the rows inside each matrix); blocks are then made of the rows at 32 consecutive positions.
+__device__ __forceinline__ int row_at(const int32_t *__restrict__ rows, const qmoe_matrix_desc &d, int pos) {
+  if (rows == nullptr) return pos;
+  const int r = rows[d.minmax_base + pos];
+  return r < 0 ? 0 : (r >= d.height ? d.height - 1 : r);
+}
+
 __global__ void k_interleave_count(const int32_t *__restrict__ row_off, const qmoe_matrix_desc *__restrict__ descs,
-                                   int32_t *__restrict__ blk_units) {
+                                   const int32_t *__restrict__ rows, int32_t *__restrict__ blk_units) {
   const qmoe_matrix_desc d = descs[blockIdx.x];
   const int32_t *ro = row_off + d.rowoff_base;
   for (int blk = threadIdx.x; blk < d.height / 32; blk += blockDim.x) {
     int longest = 0;
     for (int l = 0; l < 32; l++) {
-      const int n = ro[blk * 32 + l + 1] - ro[blk * 32 + l];
+      const int r = row_at(rows, d, blk * 32 + l);
+      const int n = ro[r + 1] - ro[r];
       longest = n > longest ? n : longest;
     }
     blk_units[d.minmax_base / 32 + blk] = (longest + 7) / 8 * 32;  // uint4 entries of this block
@@ -875,8 +899,8 @@ __global__ void k_interleave_count(const int32_t *__restrict__ row_off, const qm
 
 __global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int32_t *__restrict__ row_off,
                                   const qmoe_matrix_desc *__restrict__ descs,
-                                  const long long *__restrict__ blk_base, const uint32_t *__restrict__ remap,
-                                  uint4 *__restrict__ il) {
+                                  const int32_t *__restrict__ rows, const long long *__restrict__ blk_base,
+                                  const uint32_t *__restrict__ remap, uint4 *__restrict__ il) {
   const qmoe_matrix_desc d = descs[blockIdx.y];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int32_t *ro = row_off + d.rowoff_base;
@@ -885,7 +909,8 @@ __global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int3
     const long long gblk = d.minmax_base / 32 + blk;
     const long long first = blk_base[gblk];
     const int chunks = (int)((blk_base[gblk + 1] - first) >> 5);
-    long long b = ro[blk * 32 + lane], e = ro[blk * 32 + lane + 1];
+    const int r = row_at(rows, d, blk * 32 + lane);
+    long long b = ro[r], e = ro[r + 1];
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
     e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
     for (int k = 0; k < chunks; k++) {
@@ -903,19 +928,19 @@ __global__ void k_interleave_emit(const uint16_t *__restrict__ codes, const int3
 }
 
 int launch_interleave_count(const int32_t *row_off, const qmoe_matrix_desc *descs, int n_matrices,
-                            int32_t *blk_units, cudaStream_t stream) {
-  QMOE_LAUNCH(k_interleave_count, (unsigned)n_matrices, 256, 0, stream, row_off, descs, blk_units);
+                            const int32_t *rows, int32_t *blk_units, cudaStream_t stream) {
+  QMOE_LAUNCH(k_interleave_count, (unsigned)n_matrices, 256, 0, stream, row_off, descs, rows, blk_units);
   QMOE_CUDA(cudaGetLastError());
   return QMOE_OK;
 }
 
 int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const qmoe_matrix_desc *descs,
-                           int n_matrices, const int64_t *blk_base, const uint32_t *remap, void *il,
-                           cudaStream_t stream) {
+                           int n_matrices, const int32_t *rows, const int64_t *blk_base, const uint32_t *remap,
+                           void *il, cudaStream_t stream) {
   const int per_pass = 32768;  // grid.y limit is 65535
   for (int m0 = 0; m0 < n_matrices; m0 += per_pass) {
     const int n = n_matrices - m0 < per_pass ? n_matrices - m0 : per_pass;
-    QMOE_LAUNCH(k_interleave_emit, dim3(8, (unsigned)n), 256, 0, stream, codes, row_off, descs + m0,
+    QMOE_LAUNCH(k_interleave_emit, dim3(8, (unsigned)n), 256, 0, stream, codes, row_off, descs + m0, rows,
                 reinterpret_cast<const long long *>(blk_base), remap, reinterpret_cast<uint4 *>(il));
     QMOE_CUDA(cudaGetLastError());
   }
@@ -1273,6 +1298,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     a.blk_base = reinterpret_cast<const long long *>(ils->blk_base);
     a.il_tab = ils->table;
     a.il_dec = ils->dec;
+    a.il_rows = ils->rows;
   }
   cudaEvent_t *events = nullptr;
   const bool timed = profile_begin(device, &events);

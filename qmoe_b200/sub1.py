@@ -155,16 +155,44 @@ class ExpertStore:
             sub1_cuda.track_dec(dec)                     # the library's cache follows the tensor's life
         self.il_codes: Optional[torch.Tensor] = None     # lane-interleaved copy of the streams
         self.blk_base: Optional[torch.Tensor] = None     # int64, first 16-byte entry of every 32-row block
+        self.il_rows: Optional[torch.Tensor] = None      # int32, row of its matrix kept at every position of the copy
         if interleave and codes.is_cuda and d_model % 32 == 0 and d_ff % 32 == 0:
             self.interleave()
 
-    def interleave(self, renumber: bool = True) -> None:
+    def _rows_by_length(self) -> torch.Tensor:
+        """int32[total rows]: for every position of the interleaved store the row of its matrix that
+        is kept there -- inside every 1024 positions of a matrix (what one CTA of the grouped kernel
+        takes) the rows in decreasing order of their code count, stable."""
+        dev = self.device
+        total = sum(d.height for d in self.host_descs)
+        rows = torch.empty(total, dtype=torch.int32, device=dev)
+        by_height = {}
+        for m, d in enumerate(self.host_descs):
+            by_height.setdefault(d.height, []).append(m)
+        for h, ms in by_height.items():
+            for m0 in range(0, len(ms), 512):                     # bounded temporaries for large layers
+                part = ms[m0:m0 + 512]
+                ro_base = torch.tensor([self.host_descs[m].rowoff_base for m in part], dtype=torch.int64, device=dev)
+                mm_base = torch.tensor([self.host_descs[m].minmax_base for m in part], dtype=torch.int64, device=dev)
+                ro = self.row_off[ro_base[:, None] + torch.arange(h + 1, device=dev)[None, :]]
+                length = ro[:, 1:] - ro[:, :-1]
+                perm = torch.empty_like(length)
+                for s0 in range(0, h, 1024):
+                    seg = length[:, s0:s0 + 1024]
+                    perm[:, s0:s0 + seg.shape[1]] = torch.argsort(seg, dim=1, descending=True, stable=True) + s0
+                rows[(mm_base[:, None] + torch.arange(h, device=dev)[None, :]).reshape(-1)] = perm.reshape(-1).to(torch.int32)
+        return rows
+
+    def interleave(self, renumber: bool = True, sort_rows: bool = True) -> None:
         """Build the lane-interleaved copy of the code streams that the grouped kernel reads with
         coalesced loads (layout in include/qmoe_sub1.h), with code values renumbered by decreasing
         frequency so that the part of the table kept in shared memory serves as many lookups as
-        possible.  One-time cost when a store is created."""
+        possible, and with rows of similar length side by side (``sort_rows``) so that the 32 lanes of
+        a warp finish together.  One-time cost when a store is created."""
         L = _lib.load()
         dev = self.device
+        self.il_rows = self._rows_by_length() if sort_rows else None
+        rows_ptr = None if self.il_rows is None else self.il_rows.data_ptr()
         dec = self.dec if self.dec is not None else DEC(dev)
         remap_ptr = None
         if renumber:
@@ -183,19 +211,29 @@ class ExpertStore:
                                             self.il_dec.data_ptr(), dev.index, _s(dev)))
         rows = sum(d.height for d in self.host_descs)
         units = torch.empty(rows // 32, dtype=torch.int32, device=dev)
-        _lib.check(L.qmoe_moe_interleave_count(self.row_off.data_ptr(), self.descs.data_ptr(),
-                                               ctypes.addressof(self._desc_array), len(self.host_descs),
-                                               units.data_ptr(), dev.index, _s(dev)))
+        if rows_ptr is None:
+            _lib.check(L.qmoe_moe_interleave_count(self.row_off.data_ptr(), self.descs.data_ptr(),
+                                                   ctypes.addressof(self._desc_array), len(self.host_descs),
+                                                   units.data_ptr(), dev.index, _s(dev)))
+        else:
+            _lib.check(L.qmoe_moe_interleave_count_rows(self.row_off.data_ptr(), self.descs.data_ptr(),
+                                                        ctypes.addressof(self._desc_array), len(self.host_descs),
+                                                        rows_ptr, units.data_ptr(), dev.index, _s(dev)))
         base = torch.zeros(rows // 32 + 1, dtype=torch.int64, device=dev)
         base[1:] = torch.cumsum(units, 0, dtype=torch.int64)
         total = int(base[-1].item())
         il = torch.empty((max(total, 1), 4), dtype=torch.int32, device=dev)
-        _lib.check(L.qmoe_moe_interleave_emit(self.codes.data_ptr(), self.row_off.data_ptr(), self.descs.data_ptr(),
-                                              len(self.host_descs), base.data_ptr(), remap_ptr, il.data_ptr(),
-                                              dev.index, _s(dev)))
+        if rows_ptr is None:
+            _lib.check(L.qmoe_moe_interleave_emit(self.codes.data_ptr(), self.row_off.data_ptr(),
+                                                  self.descs.data_ptr(), len(self.host_descs), base.data_ptr(),
+                                                  remap_ptr, il.data_ptr(), dev.index, _s(dev)))
+        else:
+            _lib.check(L.qmoe_moe_interleave_emit_rows(self.codes.data_ptr(), self.row_off.data_ptr(),
+                                                       self.descs.data_ptr(), len(self.host_descs), rows_ptr,
+                                                       base.data_ptr(), remap_ptr, il.data_ptr(), dev.index, _s(dev)))
         self.il_codes, self.blk_base = il, base
         self.il_struct = _lib.InterleavedStore(il.data_ptr(), base.data_ptr(), self.il_table.data_ptr(),
-                                               self.il_dec.data_ptr())
+                                               self.il_dec.data_ptr(), rows_ptr)
 
     def aliased(self, n_experts: int) -> "ExpertStore":
         """A store of ``n_experts`` experts whose expert ``e`` IS this store's expert
@@ -206,7 +244,7 @@ class ExpertStore:
         other = ExpertStore(self.codes, self.row_off, self.minmax, descs, self.d_model, self.d_ff,
                             interleave=False, dec=self.dec)
         if self.il_codes is not None:
-            for name in ("il_codes", "blk_base", "il_table", "il_dec", "il_struct"):
+            for name in ("il_codes", "blk_base", "il_table", "il_dec", "il_struct", "il_rows"):
                 setattr(other, name, getattr(self, name))
             if hasattr(self, "remap"):
                 other.remap = self.remap
@@ -220,6 +258,8 @@ class ExpertStore:
             total += self.codes.numel() * 2
         if self.il_codes is not None:
             total += self.il_codes.numel() * 4 + self.blk_base.numel() * 8 + 3 * 4 * _lib.DICT_COUNT
+            if getattr(self, "il_rows", None) is not None:
+                total += self.il_rows.numel() * 4
         return total
 
     def drop_reference_layout(self) -> None:

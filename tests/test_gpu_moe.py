@@ -130,7 +130,8 @@ def _plain_copy(store, **kw):
 
 
 def test_interleaved_copy_holds_the_same_codes(dev, small_layer):
-    """Undo the lane interleaving and the renumbering on the host: every row's codes come back."""
+    """Undo the lane interleaving, the row order and the renumbering on the host: every row's codes
+    come back."""
     _, store = small_layer
     assert store.il_codes is not None
     il = store.il_codes.cpu().numpy().view(np.uint16).reshape(-1, 8)          # [16-byte entry, 8 codes]
@@ -139,10 +140,19 @@ def test_interleaved_copy_holds_the_same_codes(dev, small_layer):
     inverse[store.remap.cpu().numpy()] = np.arange(65536)
     codes = store.codes.cpu().numpy().view(np.uint16)
     row_off = store.row_off.cpu().numpy()
+    rows = store.il_rows.cpu().numpy()
     for d in store.host_descs:
-        for row in range(d.height):
+        # inside every 1024 positions the rows of the matrix, each once, longest first
+        mine_rows = rows[d.minmax_base:d.minmax_base + d.height]
+        lengths = np.diff(row_off[d.rowoff_base:d.rowoff_base + d.height + 1])
+        for s0 in range(0, d.height, 1024):
+            seg = mine_rows[s0:s0 + 1024]
+            assert sorted(seg.tolist()) == list(range(s0, min(s0 + 1024, d.height)))
+            assert (np.diff(lengths[seg]) <= 0).all()
+        for pos in range(d.height):
+            row = int(mine_rows[pos])
             b, e = row_off[d.rowoff_base + row], row_off[d.rowoff_base + row + 1]
-            gblk, lane = (d.minmax_base + row) // 32, row % 32
+            gblk, lane = (d.minmax_base + pos) // 32, pos % 32
             chunks = (base[gblk + 1] - base[gblk]) // 32
             mine = il[base[gblk] + lane:base[gblk] + 32 * chunks:32].reshape(-1)
             assert len(mine) >= e - b
@@ -164,7 +174,8 @@ def test_interleaved_and_row_by_row_stores_give_identical_results(dev, small_lay
         assert other.il_codes is None
     elif variant == "interleaved_plain_numbers":
         other = _plain_copy(store, interleave=False)
-        other.interleave(renumber=False)
+        other.interleave(renumber=False, sort_rows=False)
+        assert other.il_rows is None
     else:
         other = _plain_copy(store)
         other.drop_reference_layout()

@@ -79,10 +79,10 @@ def test_interleaved_store_arguments_are_validated_without_gpu():
     args = (fake, None, fake, fake, fake)
     tail = (fake, fake, fake, fake, fake, 4, 8)
     assert lib.qmoe_moe_grouped_ffn_interleaved(*args, None, *tail, 64, 96, 0, None) == _lib.ERR_INVALID_ARG
-    store = _lib.InterleavedStore(256, 256, 256, None)
+    store = _lib.InterleavedStore(256, 256, 256, None, None)
     assert lib.qmoe_moe_grouped_ffn_interleaved(*args, ctypes.addressof(store), *tail, 64, 96, 0, None) \
         == _lib.ERR_INVALID_ARG
-    store = _lib.InterleavedStore(256, 256, 256, 256)
+    store = _lib.InterleavedStore(256, 256, 256, 256, None)
     assert lib.qmoe_moe_grouped_ffn_interleaved(*args, ctypes.addressof(store), *tail, 64, 100, 0, None) \
         == _lib.ERR_UNSUPPORTED
     assert lib.qmoe_decode_attention(fake, fake, fake, fake, fake, 4, 512, 64, 0, None) == _lib.ERR_UNSUPPORTED
