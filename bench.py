@@ -906,6 +906,9 @@ def run_generate(args):
     if rank == 0:
         print(json.dumps({
             "mode": "generate", "metric": "generated_tokens_per_s", "value": new_tokens / secs, "unit": "tokens/s",
+            "model": "synthetic decoder: decoder-only stand-in with the switch-c-2048 MoE blocks (scaled dot-product "
+                     "attention, no relative position bias, no encoder / cross-attention); its tokens/s are not "
+                     "comparable with the reference's --gentokens timing of the real encoder-decoder",
             "decode_step_kernels": kernel_times,
             "n_gpus": world, "seconds_per_sample": secs, "samples": len(times),
             "config": {"workload": args.workload + " decoder", "layers": layers, "d_model": d_model, "d_ff": d_ff,
