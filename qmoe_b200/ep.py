@@ -110,6 +110,7 @@ class ExpertParallelMLP:
             try:
                 self._peer[key] = PeerBuffers.create(self.group, self.store.device, cap, d)
             except Exception as exc:  # no symmetric memory in this build, ranks sharing a GPU, ...
+                # (PeerBuffers makes every rank fail together, so all ranks take this branch)
                 if self.exchange == "peer":
                     raise
                 warnings.warn(f"expert-parallel exchange falls back to NCCL: {exc}")

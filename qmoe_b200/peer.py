@@ -48,11 +48,32 @@ class PeerBuffers:
         off_recv = _round_up(2 * G * 4)
         off_ret = off_recv + _round_up(rows * (d_model + 8) * 2)
         total = off_ret + _round_up(rows * d_model * 2)
-        self.buffer = symm.empty(total, dtype=torch.uint8, device=device)
-        self.handle = symm.rendezvous(self.buffer, self.group.group_name)
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        if len(ptrs) != G or any(p == 0 for p in ptrs):
-            raise RuntimeError("symmetric memory gave no peer addresses")
+
+        def agreed(step, fn):
+            """Run a step that can fail on one rank alone; every rank learns whether all succeeded
+            before anyone enters the next collective call."""
+            err, out = None, None
+            try:
+                out = fn()
+            except Exception as exc:  # noqa: BLE001
+                err = exc
+            ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            if int(ok.item()) == 0:
+                raise RuntimeError(f"peer exchange set-up failed at '{step}' on some rank"
+                                   + (f": {err}" if err is not None else ""))
+            return out
+
+        self.buffer = agreed("allocate", lambda: symm.empty(total, dtype=torch.uint8, device=device))
+        self.handle = agreed("rendezvous", lambda: symm.rendezvous(self.buffer, self.group.group_name))
+
+        def addresses():
+            got = [int(p) for p in self.handle.buffer_ptrs]
+            if len(got) != G or any(p == 0 for p in got):
+                raise RuntimeError("symmetric memory gave no peer addresses")
+            return got
+
+        ptrs = agreed("peer addresses", addresses)
         self.buffer.zero_()
         self.flags = self.buffer[: 2 * G * 4].view(torch.int32)
         self.recv = self.buffer[off_recv: off_recv + rows * (d_model + 8) * 2].view(torch.bfloat16).view(rows, d_model + 8)
