@@ -116,6 +116,7 @@ class ExpertParallelMLP:
                 warnings.warn(f"expert-parallel exchange falls back to NCCL: {exc}")
                 self.exchange = "nccl"
                 return None
+            self.exchange = "peer"
         return self._peer[key]
 
     def peer_timeouts(self) -> int:
