@@ -990,6 +990,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
   __shared__ int s_base;
   __shared__ int s_total;
   __shared__ unsigned long long s_best;
+  __shared__ int s_cls[kMaxGroup];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   auto group_count = [&](int e, int &first, int &count) {
     first = 0;
@@ -1002,15 +1003,27 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
     }
     return (count + kMaxGroup - 1) / kMaxGroup;
   };
-  // pass 1: total number of (expert, token group) pairs
+  // pass 1: total number of (expert, token group) pairs, and how many of them have 1, 2, 3, 4 tokens
   if (tid == 0) s_total = 0;
+  if (tid < kMaxGroup) s_cls[tid] = 0;
   __syncthreads();
   {
-    int mine = 0, first, count;
-    for (int e = tid; e < n_experts; e += blockDim.x) mine += group_count(e, first, count);
+    int mine = 0, first, count, per_cls[kMaxGroup] = {};
+    for (int e = tid; e < n_experts; e += blockDim.x) {
+      mine += group_count(e, first, count);
+      per_cls[kMaxGroup - 1] += count / kMaxGroup;
+      if (count % kMaxGroup) per_cls[count % kMaxGroup - 1] += 1;
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
     if (lane == 0 && mine) atomicAdd(&s_total, mine);
+#pragma unroll
+    for (int c = 0; c < kMaxGroup; c++) {
+      int v = per_cls[c];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0 && v) atomicAdd(&s_cls[c], v);
+    }
   }
   __syncthreads();
   const int total = min(s_total, max_slots);
@@ -1069,7 +1082,8 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
   // linears.
   if (tid == 0) s_base = 0;
   __syncthreads();
-  for (int cls = kMaxGroup; cls >= 1; cls--)
+  for (int cls = kMaxGroup; cls >= 1; cls--) {
+    if (s_cls[cls - 1] == 0) continue;  // no group of this size in the step (one token: three of four passes)
     for (int e0 = 0; e0 < n_experts; e0 += blockDim.x) {
       const int e = e0 + tid;
       int first, count;
@@ -1138,6 +1152,7 @@ __global__ void __launch_bounds__(1024) k_build_work(const int32_t *__restrict__
       if (tid == 0) s_base += s_warp[31];
       __syncthreads();
     }
+  }
   if (tid == 0) {
     const int groups_done = min(s_base, max_slots);
     for (int phase = 0; phase < 2; phase++) {
