@@ -395,6 +395,58 @@ def l2_resident_rate(dev, d_model, d_ff, n_experts, hidden, logits, lib):
     return (wi_ms.value + wo_ms.value) / max(calls.value, 1), real
 
 
+def run_smem_ceiling(args):
+    """Only the on-chip ceiling: the workload's step (seeded uniform routing) timed over the real layer
+    in HBM and over the same layer with its experts aliased onto eight real ones, which stay in L2.
+    One JSON line; single GPU."""
+    import ctypes
+    import torch
+    from qmoe_b200 import _lib, sub1, synth
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: there is no CPU path for the sub1 kernels")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    d_model, d_ff, n_experts, n_tokens = workload_dims(args)
+    store = synth.build_store(d_model, d_ff, list(range(n_experts)), SEED, dev)
+    hidden = synth.tokens(n_tokens, d_model, SEED + 1).to(dev)
+    logits = (forced_logits(n_tokens, n_experts) if args.tokens_per_expert > 0
+              else synth.router_logits(n_tokens, n_experts, SEED + 2)).to(dev)
+    layer = sub1.FasterMLP(None, store, expert_capacity=1024)
+    h, lg = hidden.unsqueeze(0), logits.unsqueeze(0)
+    for _ in range(max(args.warmup, 3)):
+        _, (_, index) = layer(h, router_logits=lg)
+    lib.qmoe_profile_enable(1)
+    for _ in range(max(args.steps, 1)):
+        layer(h, router_logits=lg)
+    torch.cuda.synchronize()
+    lib.qmoe_profile_enable(0)
+    wi_ms, wo_ms, calls = ctypes.c_float(), ctypes.c_float(), ctypes.c_int()
+    _lib.check(lib.qmoe_profile_read(ctypes.byref(wi_ms), ctypes.byref(wo_ms), ctypes.byref(calls)))
+    ms_hbm = (wi_ms.value + wo_ms.value) / max(calls.value, 1)
+    counts = torch.bincount(index.reshape(-1).long(), minlength=n_experts).cpu().tolist()
+    alg = sum(store.matrix_bytes(2 * e) + store.matrix_bytes(2 * e + 1) + 4 * c * (d_model + d_ff)
+              for e, c in enumerate(counts) if c > 0)
+    codes = sum(store.host_descs[2 * e].n_codes + store.host_descs[2 * e + 1].n_codes for e, c in enumerate(counts) if c > 0)
+    del layer, store
+    torch.cuda.empty_cache()
+    ms_l2, real = l2_resident_rate(dev, d_model, d_ff, n_experts, hidden, logits, lib)
+    peak, peak_kind = measured_hbm_peak()
+    sm_hz = 1965.0e6
+    print(json.dumps({
+        "mode": "smem-ceiling", "config": {"workload": args.workload, "experts": n_experts, "tokens": n_tokens},
+        "grouped_ms_per_step_hbm_resident": ms_hbm, "grouped_ms_per_step_l2_resident": ms_l2,
+        "frac_of_on_chip_ceiling": ms_l2 / ms_hbm if ms_hbm > 0 else None,
+        "algorithmic_bytes_per_step": alg,
+        "achieved_gbs": alg / (ms_hbm * 1e-3) / 1e9, "ceiling_gbs": alg / (ms_l2 * 1e-3) / 1e9,
+        "hbm_peak_gbs": peak, "hbm_peak_kind": peak_kind,
+        "codes_per_sm_per_clock_hbm_resident": codes / (ms_hbm * 1e-3) / (148 * sm_hz),
+        "codes_per_sm_per_clock_at_ceiling": codes / (ms_l2 * 1e-3) / (148 * sm_hz),
+        "what": f"ceiling = the same step (same tokens, routing, work list) on a layer whose {n_experts} experts "
+                f"alias the matrices of {real} real experts, so every code stream stays in L2: what the SMs' issue and "
+                "shared-memory pipes sustain for this decoder with the memory system out of the picture"}), flush=True)
+
+
 def run_ours(args):
     import ctypes
     import torch
@@ -934,6 +986,8 @@ def main():
     args = parse_args()
     if args.mode == "generate":
         run_generate(args)
+    elif args.mode == "smem-ceiling":
+        run_smem_ceiling(args)
     elif args.mode == "layers":
         run_layers(args)
     elif args.impl == "reference":
