@@ -323,9 +323,8 @@ def gpu_reference_leg(store, dev, d_model, d_ff, counts, hidden_dev, ours_tokens
         return {"unavailable": "the reference kernel handles its six hard-coded shapes only (sub1_cuda_kernel.cu:82-87)"}
     if store.codes is None:
         return {"unavailable": "the store dropped its row-by-row streams"}
-    sys.path.insert(0, os.path.join(ROOT, "oracle"))
     try:
-        import build_ref
+        from oracle import build_ref
         ref = build_ref.load()
     except Exception as exc:
         return {"unavailable": f"oracle/_ref could not be loaded: {exc}"}
@@ -806,8 +805,7 @@ def run_layers(args):
     dev = torch.device("cuda", 0)
     ref = None
     if args.impl == "reference":
-        sys.path.insert(0, os.path.join(ROOT, "oracle"))
-        import build_ref
+        from oracle import build_ref
         ref = build_ref.load()
         if ref is None:
             print(json.dumps({"impl": "reference", "mode": "layers",

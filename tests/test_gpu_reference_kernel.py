@@ -1,14 +1,12 @@
 """The new kernels against the REFERENCE's own CUDA kernels (built unmodified into oracle/_ref by
 oracle/build_ref.py) on the same device tensors.  Skipped when that build is absent."""
-import os
-import sys
 
 import numpy as np
 import pytest
 import torch
 
-sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
-import build_ref  # noqa: E402
+from oracle import build_ref  # noqa: E402  (as a package member: putting oracle/ itself on sys.path would
+                              # shadow the package with oracle/oracle.py in child processes of later tests)
 
 from qmoe_b200 import sub1, sub1_cuda  # noqa: E402
 from util import Matrix, randn_bf16, rel_err  # noqa: E402
