@@ -66,6 +66,20 @@ def _worker(rank, world, port, out_dir, exchange):
         assert layer.exchange == exchange
         assert torch.equal(out, out2) and torch.equal(out, out3)
         assert layer.peer_timeouts() == 0 and layer.overflow_count() == 0
+        # a pair capacity that is too small: tokens beyond it pass through and are counted; with
+        # exact=True the step is run again at the worst-case capacity and equals the full result
+        tight = ExpertParallelMLP(None, store, N_EXP, exchange=exchange, pair_capacity=8)
+        dropped, _ = tight(hidden, router_logits=logits)
+        n_over = tight.overflow_count()
+        total = torch.tensor([n_over], device=dev)
+        dist.all_reduce(total)
+        assert int(total.item()) > 0, "the seed no longer overflows a capacity of 8"
+        assert int((dropped != out).any(dim=1).sum()) == n_over
+        exact = ExpertParallelMLP(None, store, N_EXP, exchange=exchange, pair_capacity=8, exact=True)
+        for _ in range(2):
+            again, _ = exact(hidden, router_logits=logits)
+            assert torch.equal(again, out)
+        assert exact.peer_timeouts() == 0
         torch.save(out.cpu(), os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
