@@ -281,14 +281,17 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
 
-  stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs, second);
-  __syncthreads();
-
-  if (tid < nrows) {
-    // With an interleaved store whose rows were re-ordered (rows of similar length side by side), thread
-    // tid walks the stream at POSITION row0 + tid, which belongs to row il_rows[...] of the matrix.
-    const int pos = row0 + tid;
-    int row = pos;
+  // What a thread needs to know about its row is loaded BEFORE the activations are staged, so that
+  // these dependent global loads (row list -> offsets, block base) and the first lines of the row's
+  // code stream travel while the CTA stages x, not after the barrier.
+  // With an interleaved store whose rows were re-ordered (rows of similar length side by side), thread
+  // tid walks the stream at POSITION row0 + tid, which belongs to row il_rows[...] of the matrix.
+  const bool active = tid < nrows;
+  const int pos = row0 + tid;
+  int row = pos;
+  long long b = 0, e = 0, first = 0, n = 0;
+  __nv_bfloat162 mm = __floats2bfloat162_rn(0.f, 0.f);
+  if (active) {
     if constexpr (IL) {
       if (a.il_rows != nullptr) {
         row = a.il_rows[d.minmax_base + pos];
@@ -296,19 +299,30 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
       }
     }
     const int32_t *ro = a.row_off + d.rowoff_base;
-    long long b = ro[row], e = ro[row + 1];
+    b = ro[row];
+    e = ro[row + 1];
     b = b < 0 ? 0 : (b > d.n_codes ? d.n_codes : b);
     e = e < b ? b : (e > d.n_codes ? d.n_codes : e);
-
-    const __nv_bfloat162 mm = a.minmax[d.minmax_base + row];
-    SinkT sink;
-    sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
+    mm = a.minmax[d.minmax_base + row];
     if constexpr (IL) {
       // Row blocks of 32 rows start at multiples of 32 in every matrix and in the store.
       const long long gblk = (d.minmax_base + pos) >> 5;
-      const long long first = a.blk_base[gblk];
+      first = a.blk_base[gblk];
       const long long room = (a.blk_base[gblk + 1] - first) >> 5 << 3;  // codes per row of this block
-      const long long n = e - b < room ? e - b : room;
+      n = e - b < room ? e - b : room;
+      const uint4 *src = a.il + first + (pos & 31);
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src));
+      if (n > 8) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 32));
+    }
+  }
+
+  stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs, second);
+  __syncthreads();
+
+  if (active) {
+    SinkT sink;
+    sink.reset(__bfloat162float(mm.x), __bfloat162float(mm.y), (uint32_t)__cvta_generic_to_shared(xs));
+    if constexpr (IL) {
       walk_row<GENERAL>(LaneFetch{a.il + first + (pos & 31)}, 0, (int)n, lookup, a.il_dec, wlim, sink);
     } else {
       const uint16_t *codes_m = a.codes + d.code_base;
@@ -550,7 +564,9 @@ constexpr unsigned long long kFusedWaitNs = 2000000000ull;  // an item of the se
 template <bool GENERAL, bool IL>
 __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
-  __shared__ int s_item;
+  __shared__ int s_item[2];
+  __shared__ int4 s_it[2];
+  __shared__ qmoe_matrix_desc s_desc[2];
   uint32_t *hot = smem_u32;
   const uint32_t n_hot = IL ? (uint32_t)a.n_hot : kHotSlots;
   void *xs = smem_u32 + n_hot;
@@ -571,15 +587,33 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
       hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
     lookup = HotLookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
   }
-  for (;;) {
-    if (threadIdx.x == 0) s_item = atomicAdd(a.header + 1, 1);
-    __syncthreads();  // also orders the table fill before the first lookups
-    const int i = s_item;
+  // The next item's index, list entry and matrix descriptor are fetched while the current item is
+  // worked on, by the CTA's last thread (with rows sorted longest first it has the shortest row, or
+  // none): it issues the fetch-counter atomic at the start of an item and completes the dependent
+  // loads after its own row.  Everybody else finds the three in shared memory after the item's last
+  // barrier instead of waiting for an atomic and two dependent global loads per item.
+  auto fetch_index = [&]() { return atomicAdd(a.header + 1, 1); };
+  auto publish = [&](int slot, int i) {
+    s_item[slot] = i;
+    if (i < n_items) {
+      const bool sec = i >= n_first;
+      const int4 it = sec ? a.items2[i - n_first] : a.items[i];
+      s_it[slot] = it;
+      s_desc[slot] = a.descs[it.x];
+    }
+  };
+  const bool duty = threadIdx.x == blockDim.x - 1;
+  if (duty) publish(0, fetch_index());
+  __syncthreads();  // also orders the table fill before the first lookups
+  for (int slot = 0;; slot ^= 1) {
+    const int i = s_item[slot];
     if (i >= n_items) break;
+    int next_index = 0;
+    if (duty) next_index = fetch_index();
     const bool second = i >= n_first;
     const int j = second ? i - n_first : i;
-    const int4 it = second ? a.items2[j] : a.items[j];
-    const qmoe_matrix_desc d = a.descs[it.x];
+    const int4 it = s_it[slot];
+    const qmoe_matrix_desc d = s_desc[slot];
     const int nrows = it.w & 0x7fff, ntok = it.w >> 16;
     const int tail = (it.w & 0x8000) ? d.height - (it.y + nrows) : 0;
     if (second && per_pair_first > 0) {
@@ -617,7 +651,8 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     else
       process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
                                                       reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second);
-    __syncthreads();  // xs and s_item are rewritten by the next round; every row of the item is stored
+    if (duty) publish(slot ^ 1, next_index);
+    __syncthreads();  // xs is rewritten by the next round; every row of the item is stored; the next item is known
     if (a.fused && !second && threadIdx.x == 0) {
       __threadfence();  // the rows stored by the whole CTA (ordered by the barrier) before the count
       atomicAdd(a.done + j / per_pair_first, 1);
