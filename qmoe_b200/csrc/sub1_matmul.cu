@@ -207,6 +207,7 @@ struct MatmulArgs {
   int *done;
   int *wait_status;
   int fused;
+  unsigned x_half_bytes;  // grouped mode: bytes of the activations of a one- or two-token item (half the area)
   int chunks, rpc, tokens;  // uniform mode
   int flags;
 };
@@ -276,7 +277,8 @@ __device__ __forceinline__ void warp_rows_staged(const MatmulArgs &a, const qmoe
 template <int T, bool GENERAL, class SinkT, bool IL = false, class Lookup>
 __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_matrix_desc &d, int row0,
                                              int nrows, int tok0, int ntok, typename SinkT::elem *xs,
-                                             const Lookup &lookup, int tail_rows = 0, bool second = false) {
+                                             const Lookup &lookup, int tail_rows = 0, bool second = false,
+                                             bool staged = false) {
   const int tid = threadIdx.x;
   const int W = d.width;
   const int wlim = (W + 1) & ~1;
@@ -316,8 +318,10 @@ __device__ __forceinline__ void process_item(const MatmulArgs &a, const qmoe_mat
     }
   }
 
-  stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs, second);
-  __syncthreads();
+  if (!staged) {  // else xs was filled during the CTA's previous item, whose last barrier ordered it
+    stage_tokens<T, SinkT>(a, W, wlim, tok0, ntok, xs, second);
+    __syncthreads();
+  }
 
   if (active) {
     SinkT sink;
@@ -564,12 +568,12 @@ constexpr unsigned long long kFusedWaitNs = 2000000000ull;  // an item of the se
 template <bool GENERAL, bool IL>
 __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
-  __shared__ int s_item[2];
-  __shared__ int4 s_it[2];
-  __shared__ qmoe_matrix_desc s_desc[2];
+  __shared__ int s_item[3];
+  __shared__ int4 s_it[3];
+  __shared__ qmoe_matrix_desc s_desc[3];
   uint32_t *hot = smem_u32;
   const uint32_t n_hot = IL ? (uint32_t)a.n_hot : kHotSlots;
-  void *xs = smem_u32 + n_hot;
+  char *xs_base = reinterpret_cast<char *>(smem_u32 + n_hot);
   const int n_first = a.header[0];
   const int n_items = n_first + (a.fused ? a.header2[0] : 0);
   if (n_items <= 0) return;
@@ -587,11 +591,15 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
       hot[i] = __ldg(a.tab + (i < kHotLow ? i : i + (kHotHigh - kHotLow)));
     lookup = HotLookup{(uint32_t)__cvta_generic_to_shared(hot), a.tab};
   }
-  // The next item's index, list entry and matrix descriptor are fetched while the current item is
-  // worked on, by the CTA's last thread (with rows sorted longest first it has the shortest row, or
-  // none): it issues the fetch-counter atomic at the start of an item and completes the dependent
-  // loads after its own row.  Everybody else finds the three in shared memory after the item's last
-  // barrier instead of waiting for an atomic and two dependent global loads per item.
+  // The CTA knows its next TWO items: their index, list entry and matrix descriptor sit in a ring of
+  // three shared-memory slots.  They are fetched while the current item is worked on, by the CTA's
+  // last thread (with rows sorted longest first it has the shortest row, or none): it issues the
+  // fetch-counter atomic at the start of an item and completes the dependent loads after its own
+  // row, so nobody waits for an atomic and two dependent global loads per item.
+  // Knowing the next item also lets the threads that are done with their row stage its activations:
+  // the activations of an item of one or two tokens take half of the area that four tokens need, so
+  // two such items in a row (most of a step: items are ordered by token count) use the two halves in
+  // turn, and the second one starts without loads, conversions or a barrier.
   auto fetch_index = [&]() { return atomicAdd(a.header + 1, 1); };
   auto publish = [&](int slot, int i) {
     s_item[slot] = i;
@@ -603,19 +611,28 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     }
   };
   const bool duty = threadIdx.x == blockDim.x - 1;
-  if (duty) publish(0, fetch_index());
+  if (duty) {
+    publish(0, fetch_index());
+    publish(1, fetch_index());
+  }
   __syncthreads();  // also orders the table fill before the first lookups
-  for (int slot = 0;; slot ^= 1) {
+  bool staged = false;  // this item's activations were staged during the previous item
+  int half = 0;         // which half of the area they are in (items of one or two tokens)
+  for (int slot = 0;; slot = slot == 2 ? 0 : slot + 1) {
     const int i = s_item[slot];
     if (i >= n_items) break;
-    int next_index = 0;
-    if (duty) next_index = fetch_index();
+    const int slot1 = slot == 2 ? 0 : slot + 1, slot2 = slot1 == 2 ? 0 : slot1 + 1;
+    int later_index = 0;
+    if (duty) later_index = fetch_index();
     const bool second = i >= n_first;
     const int j = second ? i - n_first : i;
     const int4 it = s_it[slot];
     const qmoe_matrix_desc d = s_desc[slot];
     const int nrows = it.w & 0x7fff, ntok = it.w >> 16;
     const int tail = (it.w & 0x8000) ? d.height - (it.y + nrows) : 0;
+    const bool small = IL && ntok <= 2;
+    if (!staged) half = 0;
+    void *xs = xs_base + (small ? (size_t)half * a.x_half_bytes : 0);
     if (second && per_pair_first > 0) {
       // The hidden activations of this (expert, token group) come from the items of the first linear,
       // all of which were fetched before this one (one fetch order) by CTAs that are running: wait
@@ -644,19 +661,40 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     // is one 4- or 8-byte shared load (two 4-byte words per lane cost twice the bank cycles)
     if (ntok <= 1)
       process_item<1, GENERAL, MatSink<1, true>, IL>(a, d, it.y, nrows, it.z, ntok, reinterpret_cast<float *>(xs), lookup,
-                                                     tail, second);
+                                                     tail, second, staged);
     else if (ntok == 2)
       process_item<2, GENERAL, MatSink<2, false>, IL>(a, d, it.y, nrows, it.z, ntok,
-                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second);
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second, staged);
     else
       process_item<4, GENERAL, MatSink<4, false>, IL>(a, d, it.y, nrows, it.z, ntok,
-                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second);
-    if (duty) publish(slot ^ 1, next_index);
-    __syncthreads();  // xs is rewritten by the next round; every row of the item is stored; the next item is known
+                                                      reinterpret_cast<__nv_bfloat16 *>(xs), lookup, tail, second, staged);
+    // This thread's rows are stored.  If this item and the CTA's next one both take half of the area,
+    // help stage the next one's activations into the other half (its last reader was the item before
+    // this one, which ended with a barrier).  Items of the second linear of a fused launch have to
+    // wait for their input first and are staged when they start.
+    bool next_staged = false;
+    if (small) {
+      const int i1 = s_item[slot1];
+      if (i1 < n_first) {  // a valid item of the (first) linear
+        const int4 nx = s_it[slot1];
+        const int nt1 = nx.w >> 16;
+        if (nt1 <= 2) {
+          next_staged = true;
+          const int w1 = s_desc[slot1].width, wl1 = (w1 + 1) & ~1;
+          void *xn = xs_base + (size_t)(half ^ 1) * a.x_half_bytes;
+          if (nt1 <= 1) stage_tokens<1, MatSink<1, true>>(a, w1, wl1, nx.z, nt1, reinterpret_cast<float *>(xn));
+          else stage_tokens<2, MatSink<2, false>>(a, w1, wl1, nx.z, nt1, reinterpret_cast<__nv_bfloat16 *>(xn));
+        }
+      }
+    }
+    if (duty) publish(slot2, later_index);
+    __syncthreads();  // every row of the item is stored; the next item's activations and the one after's entry are in place
     if (a.fused && !second && threadIdx.x == 0) {
       __threadfence();  // the rows stored by the whole CTA (ordered by the barrier) before the count
       atomicAdd(a.done + j / per_pair_first, 1);
     }
+    if (next_staged) half ^= 1;
+    staged = next_staged;
   }
 }
 
@@ -1370,6 +1408,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
     p.items = ph[phase].items;
     p.header = header + 2 * phase;
     p.flags = phase == 0 ? QMOE_FLAG_RELU : 0;
+    p.x_half_bytes = (unsigned)(grouped_x_bytes(width, kMaxGroup) / 2);
     p.n_hot = hot_entries_for(width);
     smem_of[phase] = il ? sizeof(uint32_t) * p.n_hot + grouped_x_bytes(width, kMaxGroup)
                         : grouped_smem_bytes(width, kMaxGroup);
@@ -1448,6 +1487,7 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
       f.wait_status = tile_status_word(device);
       if (f.wait_status == nullptr) return cuda_fail(cudaGetLastError(), "status word");
       f.fused = 1;
+      f.x_half_bytes = (unsigned)(grouped_x_bytes(wide, kMaxGroup) / 2);
       f.n_hot = hot_entries_for(wide);
       if ((rc = launch_threads(f, sizeof(uint32_t) * f.n_hot + grouped_x_bytes(wide, kMaxGroup))) != QMOE_OK) return rc;
     }
