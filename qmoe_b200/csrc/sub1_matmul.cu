@@ -565,12 +565,18 @@ constexpr unsigned long long kFusedWaitNs = 2000000000ull;  // an item of the se
 // Persistent CTAs (one per SM) pulling items of a device-built work list.  Shared memory holds the
 // hot part of the sparse table (loaded once per CTA) followed by the bf16 activations of the
 // current item.
-template <bool GENERAL, bool IL>
+// AHEAD2: the CTA claims its items two ahead instead of one, which lets it stage the next item's
+// activations early (below).  Claiming ahead fixes who gets the launch's last items by launch order
+// instead of by who is free first: with a few items per SM that costs more than the staging saves
+// (160 pairs of c-2048, wo: 260 us against 226 us), with twenty and more it does not show.  The
+// host takes AHEAD2 for the large steps that run one launch per linear.
+template <bool GENERAL, bool IL, bool AHEAD2 = false>
 __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const MatmulArgs a) {
   extern __shared__ __align__(16) uint32_t smem_u32[];
-  __shared__ int s_item[3];
-  __shared__ int4 s_it[3];
-  __shared__ qmoe_matrix_desc s_desc[3];
+  constexpr int kAhead = AHEAD2 ? 2 : 1, kSlots = kAhead + 1;
+  __shared__ int s_item[kSlots];
+  __shared__ int4 s_it[kSlots];
+  __shared__ qmoe_matrix_desc s_desc[kSlots];
   uint32_t *hot = smem_u32;
   const uint32_t n_hot = IL ? (uint32_t)a.n_hot : kHotSlots;
   char *xs_base = reinterpret_cast<char *>(smem_u32 + n_hot);
@@ -613,15 +619,16 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
   const bool duty = threadIdx.x == blockDim.x - 1;
   if (duty) {
     publish(0, fetch_index());
-    publish(1, fetch_index());
+    if (AHEAD2) publish(1, fetch_index());
   }
   __syncthreads();  // also orders the table fill before the first lookups
   bool staged = false;  // this item's activations were staged during the previous item
   int half = 0;         // which half of the area they are in (items of one or two tokens)
-  for (int slot = 0;; slot = slot == 2 ? 0 : slot + 1) {
+  for (int slot = 0;; slot = slot == kSlots - 1 ? 0 : slot + 1) {
     const int i = s_item[slot];
     if (i >= n_items) break;
-    const int slot1 = slot == 2 ? 0 : slot + 1, slot2 = slot1 == 2 ? 0 : slot1 + 1;
+    const int slot1 = slot == kSlots - 1 ? 0 : slot + 1;            // the next item (known at once only with AHEAD2)
+    const int slot_new = AHEAD2 ? (slot1 == kSlots - 1 ? 0 : slot1 + 1) : slot1;  // where the item claimed now goes
     int later_index = 0;
     if (duty) later_index = fetch_index();
     const bool second = i >= n_first;
@@ -630,7 +637,7 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
     const qmoe_matrix_desc d = s_desc[slot];
     const int nrows = it.w & 0x7fff, ntok = it.w >> 16;
     const int tail = (it.w & 0x8000) ? d.height - (it.y + nrows) : 0;
-    const bool small = IL && ntok <= 2;
+    const bool small = AHEAD2 && IL && ntok <= 2;
     if (!staged) half = 0;
     void *xs = xs_base + (small ? (size_t)half * a.x_half_bytes : 0);
     if (second && per_pair_first > 0) {
@@ -687,8 +694,8 @@ __global__ void __launch_bounds__(kGroupedThreads, 1) k_matmul_grouped(const Mat
         }
       }
     }
-    if (duty) publish(slot2, later_index);
-    __syncthreads();  // every row of the item is stored; the next item's activations and the one after's entry are in place
+    if (duty) publish(slot_new, later_index);
+    __syncthreads();  // every row of the item is stored; the next item's activations and the newly claimed entry are in place
     if (a.fused && !second && threadIdx.x == 0) {
       __threadfence();  // the rows stored by the whole CTA (ordered by the barrier) before the count
       atomicAdd(a.done + j / per_pair_first, 1);
@@ -802,6 +809,9 @@ static int set_smem_limits() {
                                  (int)grouped_smem_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute(k_matmul_grouped<GENERAL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemPerCta));
+  if constexpr (!GENERAL)
+    QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped<false, true, true>), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)kSmemPerCta));
   QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped_warp<GENERAL, 4>), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)grouped_x_bytes(QMOE_MAX_WIDTH, kMaxGroup)));
   QMOE_CUDA(cudaFuncSetAttribute((k_matmul_grouped_warp<GENERAL, 9>), cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1422,8 +1432,10 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
                              p.y_rows, p.y_ptrs, phase == 0 ? tile_wi : tile_wo, header + 4 + phase, p.flags,
                              tile_cap_blocks(max_slots) * rows_blocks, device, stream);
   };
-  auto launch_threads = [&](const MatmulArgs &p, size_t smem) -> int {
-    if (tab.conforming && il)
+  auto launch_threads = [&](const MatmulArgs &p, size_t smem, bool ahead2) -> int {
+    if (tab.conforming && il && ahead2)
+      QMOE_LAUNCH((k_matmul_grouped<false, true, true>), grid, kGroupedThreads, smem, stream, p);
+    else if (tab.conforming && il)
       QMOE_LAUNCH((k_matmul_grouped<false, true>), grid, kGroupedThreads, smem, stream, p);
     else if (tab.conforming)
       QMOE_LAUNCH((k_matmul_grouped<false, false>), grid, kGroupedThreads, smem, stream, p);
@@ -1489,7 +1501,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
       f.fused = 1;
       f.x_half_bytes = (unsigned)(grouped_x_bytes(wide, kMaxGroup) / 2);
       f.n_hot = hot_entries_for(wide);
-      if ((rc = launch_threads(f, sizeof(uint32_t) * f.n_hot + grouped_x_bytes(wide, kMaxGroup))) != QMOE_OK) return rc;
+      if ((rc = launch_threads(f, sizeof(uint32_t) * f.n_hot + grouped_x_bytes(wide, kMaxGroup), false)) != QMOE_OK)
+        return rc;
     }
     if ((rc = launch_warps(1)) != QMOE_OK) return rc;
     if (timed) {
@@ -1504,7 +1517,8 @@ int launch_grouped_ffn(const SparseTable &tab, const int32_t *dec, const uint16_
   for (int phase = 0; phase < 2; phase++) {
     if ((rc = launch_tiles(phase)) != QMOE_OK) return rc;
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase], stream));
-    if (!all_small(phase) && (rc = launch_threads(pa[phase], smem_of[phase])) != QMOE_OK) return rc;
+    // steps of more than eight token slots per SM come here: claim two items ahead and stage early
+    if (!all_small(phase) && (rc = launch_threads(pa[phase], smem_of[phase], max_slots > 8 * sms)) != QMOE_OK) return rc;
     if ((rc = launch_warps(phase)) != QMOE_OK) return rc;
     if (timed) QMOE_CUDA(cudaEventRecord(events[2 * phase + 1], stream));
   }

@@ -96,6 +96,11 @@ def test_switch_c_2048_slice_grouped_path_against_the_oracle():
     finally:
         L.qmoe_moe_set_fused_phases(was)
     assert was == 1 and torch.equal(ys, ys_two), "one launch for both linears differs from one launch per linear"
+    # a step declared as large as the benchmark's (2048 token slots) takes one launch per linear whose
+    # CTAs claim their items two ahead and stage the next item's activations early: same bits
+    ys_big = sub1.grouped_ffn(store, offsets, xs, 2048)
+    torch.cuda.synchronize()
+    assert torch.equal(ys_big[:N_TOKENS], ys), "the large-step launches differ from the fused launch"
 
     # the same step on a store without the interleaved copy (row-by-row streams, one thread per row)
     plain = sub1.ExpertStore(store.codes, store.row_off, store.minmax, store.host_descs, d_model, d_ff,
