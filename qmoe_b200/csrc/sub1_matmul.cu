@@ -1032,10 +1032,12 @@ int launch_interleave_emit(const uint16_t *codes, const int32_t *row_off, const 
 
 // ---- grouped expert FFN -------------------------------------------------------------------------
 // Work buffer layout: int header[16] | int4 items_wi[cap] | int4 items_wo[cap] | tile items of wi |
-// tile items of wo | warp items of wi | warp items of wo.
-// header[0] = number of wi items, [1] = wi fetch counter, [2] = number of wo items, [3] = wo counter,
-// [4] / [5] = tile items of wi / wo, [10] .. [13] = counts
-// and fetch counters of the warp items of wi and wo.
+// tile items of wo | warp items of wi | warp items of wo | int done[max_slots] (finished wi items per
+// (expert, token group), for the launch that runs both linears).
+// header[0] = number of wi items, [1] = wi fetch counter (the only one of a fused launch), [2] = number
+// of wo items, [3] = wo counter, [4] / [5] = tile items of wi / wo, [6] / [7] = rows per item of wi /
+// wo, [9] = tokens decoded together, [10] .. [13] = counts and fetch counters of the warp items of wi
+// and wo, [14] / [15] = per-thread items per (expert, token group) of wi / wo.
 //
 // Who takes which rows is decided here, on the device, from the number of (expert, token group)
 // pairs.  A full layer (hundreds of pairs) is cut into items of up to 1024 rows for
