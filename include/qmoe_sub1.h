@@ -386,7 +386,11 @@ int qmoe_moe_combine(const void *ys_dev, const void *hidden_dev, const int32_t *
  *     of the token; caches bf16 [heads][max_len][head_dim]; *pos_dev (device int64) is the token's
  *     position: its key and value are written there, then
  *     out[head] = softmax(q . K[0..pos] / sqrt(head_dim)) V[0..pos] (fp32 arithmetic, bf16 result).
- *     head_dim <= 256. */
+ *     head_dim <= 256.  A position outside [0, max_len) is clamped (the last slot is overwritten).
+ *   qmoe_decode_attention_ex: the same with the score scale given (scale <= 0: 1 / sqrt(head_dim);
+ *     T5 / Switch attention uses 1), an optional additive bias bias_dev fp32 [heads][max_len] (the
+ *     relative-position bias of the query's row, per key position) and, when status_dev is not NULL,
+ *     a position outside [0, max_len) refused: *status_dev is incremented and nothing is written. */
 int qmoe_moe_combine_add(const void *ys_dev, const void *hidden_dev, const int32_t *slot_dev,
                          const void *prob_dev, const void *residual_dev, void *out_dev, int n_tokens,
                          int d_model, int device, void *stream);
@@ -399,6 +403,9 @@ int qmoe_gemv(const void *x_dev, const void *ln_weight_dev, const void *w_dev, c
               void *y_dev, void *normed_out_dev, int n, int k, float eps, int f32_out, int device, void *stream);
 int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
                           void *out_dev, int heads, int head_dim, int max_len, int device, void *stream);
+int qmoe_decode_attention_ex(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
+                             void *out_dev, int heads, int head_dim, int max_len, float scale, const float *bias_dev,
+                             int32_t *status_dev, int device, void *stream);
 
 /* Number of kernels this library has launched in the calling process (all devices, all entry points). */
 int64_t qmoe_launch_count(void);

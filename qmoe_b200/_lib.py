@@ -103,6 +103,7 @@ SIGNATURES = {
     "qmoe_rms_norm": (_I, [_P, _P, _P, _I, _I, ctypes.c_float, _I, _P]),
     "qmoe_gemv": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, ctypes.c_float, _I, _I, _P]),
     "qmoe_decode_attention": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "qmoe_decode_attention_ex": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, ctypes.c_float, _P, _P, _I, _P]),
     "qmoe_sub1_code_histogram": (_I, [_P, _L, _P, _I, _P]),
     "qmoe_sub1_remap_tables": (_I, [_P, _P, _P, _P, _I, _P]),
     "qmoe_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),

@@ -130,7 +130,8 @@ int launch_gemv(const void *x, const void *ln_w, const void *w, const void *resi
                 int n, int k, float eps, int f32_out, cudaStream_t stream);
 int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, float eps, cudaStream_t stream);
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
-                            int heads, int hd, int max_len, cudaStream_t stream);
+                            int heads, int hd, int max_len, float scale, const float *bias, int *status,
+                            cudaStream_t stream);
 int launch_code_histogram(const uint16_t *codes, int64_t n, uint64_t *hist, cudaStream_t stream);
 int launch_remap_tables(const int32_t *dec, const uint32_t *remap, uint32_t *tab_out, int32_t *dec_out,
                         int *scratch2, cudaStream_t stream);
@@ -879,18 +880,34 @@ int qmoe_gemv(const void *x_dev, const void *ln_weight_dev, const void *w_dev, c
                      as_stream(stream));
 }
 
-int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
-                          void *out_dev, int heads, int head_dim, int max_len, int device, void *stream) {
-  QMOE_REQUIRE(qkv_dev && k_cache_dev && v_cache_dev && pos_dev && out_dev, "null device pointer");
-  QMOE_REQUIRE(heads >= 1 && head_dim >= 1 && max_len >= 1, "bad shape");
+static int decode_attention_entry(const char *fn, const void *qkv_dev, void *k_cache_dev, void *v_cache_dev,
+                                  const int64_t *pos_dev, void *out_dev, int heads, int head_dim, int max_len,
+                                  float scale, const float *bias_dev, int32_t *status_dev, int device, void *stream) {
+  if (!(qkv_dev && k_cache_dev && v_cache_dev && pos_dev && out_dev) || heads < 1 || head_dim < 1 || max_len < 1) {
+    set_error("%s: null device pointer or bad shape", fn);
+    return QMOE_ERR_INVALID_ARG;
+  }
   if (head_dim > 256) {
-    set_error("%s: head_dim <= 256 is supported", __func__);
+    set_error("%s: head_dim <= 256 is supported", fn);
     return QMOE_ERR_UNSUPPORTED;
   }
   DeviceGuard guard(device);
   if (!guard.ok) return cuda_fail(cudaGetLastError(), "cudaSetDevice");
-  return launch_decode_attention(qkv_dev, k_cache_dev, v_cache_dev, pos_dev, out_dev, heads, head_dim, max_len,
-                                 as_stream(stream));
+  return launch_decode_attention(qkv_dev, k_cache_dev, v_cache_dev, pos_dev, out_dev, heads, head_dim, max_len, scale,
+                                 bias_dev, status_dev, as_stream(stream));
+}
+
+int qmoe_decode_attention(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
+                          void *out_dev, int heads, int head_dim, int max_len, int device, void *stream) {
+  return decode_attention_entry(__func__, qkv_dev, k_cache_dev, v_cache_dev, pos_dev, out_dev, heads, head_dim,
+                                max_len, 0.f, nullptr, nullptr, device, stream);
+}
+
+int qmoe_decode_attention_ex(const void *qkv_dev, void *k_cache_dev, void *v_cache_dev, const int64_t *pos_dev,
+                             void *out_dev, int heads, int head_dim, int max_len, float scale, const float *bias_dev,
+                             int32_t *status_dev, int device, void *stream) {
+  return decode_attention_entry(__func__, qkv_dev, k_cache_dev, v_cache_dev, pos_dev, out_dev, heads, head_dim,
+                                max_len, scale, bias_dev, status_dev, device, stream);
 }
 
 int64_t qmoe_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }

@@ -68,7 +68,8 @@ template <int J>  // ceil(head_dim / 32): values of a cache row per lane
 __global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __nv_bfloat16 *__restrict__ qkv,
                                    __nv_bfloat16 *__restrict__ k_cache,
                                    __nv_bfloat16 *__restrict__ v_cache, const long long *__restrict__ pos_ptr,
-                                   __nv_bfloat16 *__restrict__ out, int heads, int hd, int max_len) {
+                                   __nv_bfloat16 *__restrict__ out, int heads, int hd, int max_len,
+                                   float scale_in, const float *__restrict__ bias, int *status) {
   extern __shared__ float smem[];
   constexpr int kWarps = kAttentionThreads / 32;
   float *q = smem;                     // hd
@@ -77,7 +78,15 @@ __global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __
   float *part_s = part_m + kWarps;        // [kWarps]
   const int head = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   long long pos = *pos_ptr;
-  pos = pos < 0 ? 0 : (pos >= max_len ? max_len - 1 : pos);
+  if (pos < 0 || pos >= max_len) {
+    // With a status word the call is refused (counted, nothing written); without one the position is
+    // clamped, which overwrites the last cache slot.
+    if (status != nullptr) {
+      if (tid == 0 && head == 0) atomicAdd(status, 1);
+      return;
+    }
+    pos = pos < 0 ? 0 : max_len - 1;
+  }
   __nv_bfloat16 *kc = k_cache + (size_t)head * max_len * hd;
   __nv_bfloat16 *vc = v_cache + (size_t)head * max_len * hd;
   for (int i = tid; i < hd; i += blockDim.x) {
@@ -86,7 +95,9 @@ __global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __
     vc[pos * hd + i] = qkv[(size_t)(2 * heads + head) * hd + i];
   }
   __syncthreads();
-  const float scale = rsqrtf((float)hd);
+  // scale_in <= 0: 1 / sqrt(head_dim); T5 / Switch attention is unscaled (scale 1) with a position bias
+  const float scale = scale_in > 0.f ? scale_in : rsqrtf((float)hd);
+  const float *hb = bias != nullptr ? bias + (size_t)head * max_len : nullptr;  // added to the score of position t
   // 2 * U * J cache values per lane stay in registers (64 registers per thread at 1024 threads)
   constexpr int U = J <= 3 ? 4 : (J <= 4 ? 2 : 1);
   float m = -INFINITY, ssum = 0.f, acc[J];
@@ -115,7 +126,7 @@ __global__ void __launch_bounds__(kAttentionThreads) k_decode_attention(const __
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      sc[u] = t0 + u <= pos ? d * scale : -INFINITY;  // the same in every lane
+      sc[u] = t0 + u <= pos ? d * scale + (hb != nullptr ? hb[t0 + u] : 0.f) : -INFINITY;  // the same in every lane
       round_max = fmaxf(round_max, sc[u]);
     }
     // t0 <= pos: at least one score of the round is finite
@@ -163,7 +174,8 @@ int launch_rms_norm(const void *x, const void *w, void *out, int rows, int d, fl
 }
 
 int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const int64_t *pos, void *out,
-                            int heads, int hd, int max_len, cudaStream_t stream) {
+                            int heads, int hd, int max_len, float scale, const float *bias, int *status,
+                            cudaStream_t stream) {
   const size_t smem = sizeof(float) * ((size_t)hd + (size_t)(kAttentionThreads / 32) * (hd + 2));
   static bool limit_set[64][kMaxHeadDim / 32 + 1] = {};  // per device and instantiation
   int device = 0;
@@ -178,7 +190,8 @@ int launch_decode_attention(const void *qkv, void *k_cache, void *v_cache, const
     }
     QMOE_LAUNCH(kernel, (unsigned)heads, kAttentionThreads, smem, stream, reinterpret_cast<const __nv_bfloat16 *>(qkv),
                 reinterpret_cast<__nv_bfloat16 *>(k_cache), reinterpret_cast<__nv_bfloat16 *>(v_cache),
-                reinterpret_cast<const long long *>(pos), reinterpret_cast<__nv_bfloat16 *>(out), heads, hd, max_len);
+                reinterpret_cast<const long long *>(pos), reinterpret_cast<__nv_bfloat16 *>(out), heads, hd, max_len,
+                scale, bias, status);
     QMOE_CUDA(cudaGetLastError());
     return QMOE_OK;
   };

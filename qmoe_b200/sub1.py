@@ -670,15 +670,28 @@ def gemv(x: torch.Tensor, w: torch.Tensor, ln_weight: Optional[torch.Tensor] = N
     return (y, normed) if want_normed else y
 
 
-def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+def decode_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, pos: torch.Tensor,
+                     scale: float = 0.0, bias: Optional[torch.Tensor] = None,
+                     status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal self-attention of one new token (``qkv`` bf16 [3, heads, head_dim]) against caches
-    bf16 [heads, max_len, head_dim]; the token's key / value are stored at ``pos`` (device int64[1])."""
+    bf16 [heads, max_len, head_dim]; the token's key / value are stored at ``pos`` (device int64[1]).
+    ``scale`` multiplies the scores (0: 1 / sqrt(head_dim); T5 / Switch attention uses 1); ``bias``
+    fp32 [heads, max_len] is added to them (a relative-position bias); with ``status`` (int32[1]) a
+    position outside the cache is refused and counted instead of clamped."""
     heads, max_len, hd = k_cache.shape
     assert qkv.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous() and pos.dtype == torch.int64
     out = torch.empty((1, heads * hd), dtype=torch.bfloat16, device=qkv.device)
-    _lib.check(_lib.load().qmoe_decode_attention(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-                                                 pos.data_ptr(), out.data_ptr(), heads, hd, max_len,
-                                                 qkv.device.index, _s(qkv.device)))
+    if scale == 0.0 and bias is None and status is None:
+        _lib.check(_lib.load().qmoe_decode_attention(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                                     pos.data_ptr(), out.data_ptr(), heads, hd, max_len,
+                                                     qkv.device.index, _s(qkv.device)))
+        return out
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape == (heads, max_len))
+    assert status is None or status.dtype == torch.int32
+    _lib.check(_lib.load().qmoe_decode_attention_ex(
+        qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(), out.data_ptr(), heads, hd, max_len,
+        float(scale), None if bias is None else bias.data_ptr(), None if status is None else status.data_ptr(),
+        qkv.device.index, _s(qkv.device)))
     return out
 
 

@@ -134,6 +134,38 @@ def test_decode_attention_matches_masked_sdpa(hd, max_len):
         assert float((got.float() - want).abs().max()) <= 2e-2 * max(float(want.abs().max()), 1e-3)
 
 
+def test_decode_attention_unscaled_with_position_bias_and_position_status():
+    """T5 / Switch style: scores are not scaled and a per-head bias over the key positions is added;
+    a position outside the cache is refused and counted when a status word is given."""
+    import torch.nn.functional as F
+    from qmoe_b200 import sub1
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(8)
+    heads, hd, max_len = 4, 64, 40
+    k_cache = (0.3 * torch.randn(heads, max_len, hd, generator=g)).bfloat16().to(dev)
+    v_cache = torch.randn(heads, max_len, hd, generator=g).bfloat16().to(dev)
+    bias = torch.randn(heads, max_len, generator=g).to(dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for p in (0, 9, max_len - 1):
+        qkv = (0.3 * torch.randn(3, heads, hd, generator=g)).bfloat16().to(dev)
+        k_ref, v_ref = k_cache.clone(), v_cache.clone()
+        k_ref[:, p], v_ref[:, p] = qkv[1], qkv[2]
+        pos = torch.full((1,), p, dtype=torch.int64, device=dev)
+        got = sub1.decode_attention(qkv.contiguous(), k_cache, v_cache, pos, scale=1.0, bias=bias,
+                                    status=status).reshape(heads, hd)
+        assert torch.equal(k_cache, k_ref) and torch.equal(v_cache, v_ref)
+        want = F.scaled_dot_product_attention(qkv[0].float().unsqueeze(1), k_ref[:, :p + 1].float(),
+                                              v_ref[:, :p + 1].float(), attn_mask=bias[:, None, :p + 1],
+                                              scale=1.0)[:, 0]
+        assert float((got.float() - want).abs().max()) <= 2e-2 * max(float(want.abs().max()), 1e-3)
+    assert int(status.item()) == 0
+    before_k = k_cache.clone()
+    for bad in (-1, max_len):
+        sub1.decode_attention(qkv.contiguous(), k_cache, v_cache,
+                              torch.full((1,), bad, dtype=torch.int64, device=dev), scale=1.0, status=status)
+    assert int(status.item()) == 2 and torch.equal(k_cache, before_k)      # refused, nothing written
+
+
 def test_one_token_matrix_vector_kernel_variants():
     from qmoe_b200 import sub1
     from qmoe_b200.decoder import _rms_norm
